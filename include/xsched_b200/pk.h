@@ -1,0 +1,151 @@
+/*
+ * pk.h — C ABI of the preemptible persistent-kernel library (libxpk.so) for sm_100a.
+ *
+ * This is the device-side half of XSched's Level-2 ("deactivate") preemption on B200.
+ * The reference obtains Level-2 by patching a guardian prologue into every application
+ * kernel (platforms/cuda/hal/src/level2/instrument.cpp:15-231,
+ * platforms/cuda/hal/inject/inject.cu:43-140): each thread block checks a global exit
+ * flag, records exit/restore flags per block, and the host relaunches from `preempt_idx`
+ * (platforms/cuda/hal/src/level2/cuda_queue.cpp:29-41).  That guardian exists only as
+ * sm35/sm70/sm86 machine code (platforms/cuda/hal/src/arch/arch.cpp:26-39), so on B200 the
+ * reference has no Level-2 at all.  Here the same contract is provided cooperatively:
+ * every kernel below is persistent, claims its work tile by tile, polls a device-visible
+ * preempt flag at each tile boundary, and on preemption leaves a resumable cursor in a
+ * control block.  Relaunching the same task continues from the cursor; the output of a
+ * task preempted and resumed any number of times is bit-identical to an unpreempted run.
+ *
+ * All entry points take plain pointers and sizes.  Device pointers are raw CUDA device
+ * addresses; streams are CUstream/cudaStream_t passed as void*.  Every function returns
+ * an xpkResult; nothing here allocates behind the caller's back except xpkTaskCreate*
+ * (one 4 KiB device control block + one 64-byte mapped host mailbox per task).
+ */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    XPK_SUCCESS            = 0,
+    XPK_ERR_INVALID_VALUE  = 1,  /* null pointer, zero size, bad shape            */
+    XPK_ERR_ALIGNMENT      = 2,  /* a device pointer is not 16-byte aligned       */
+    XPK_ERR_CUDA           = 3,  /* a CUDA runtime/driver call failed             */
+    XPK_ERR_NOT_SUPPORTED  = 4,  /* shape outside what the kernel was built for   */
+    XPK_ERR_BUSY           = 5,  /* task still in flight                          */
+    XPK_ERR_DEVICE_TIMEOUT = 6,  /* a bounded device-side wait gave up            */
+    XPK_ERR_TOO_LARGE      = 7,  /* exceeds a static capacity                     */
+} xpkResult;
+
+/* Task status as published by the kernel in the mailbox. */
+typedef enum {
+    XPK_STATUS_IDLE      = 0,  /* created or reset, never launched                 */
+    XPK_STATUS_RUNNING   = 1,  /* launched, final CTA has not yet published        */
+    XPK_STATUS_COMPLETED = 2,  /* every tile done                                   */
+    XPK_STATUS_PREEMPTED = 3,  /* stopped on the preempt flag; cursor is resumable */
+    XPK_STATUS_ERROR     = 4,  /* a bounded wait expired; output undefined         */
+} xpkStatus;
+
+typedef enum {
+    XPK_KIND_TRIAD  = 1,  /* a[i] = fmaf(s, c[i], b[i]), fp32, 128-bit accesses   */
+    XPK_KIND_VECADD = 2,  /* c[i] = a[i] + b[i], fp32                              */
+    XPK_KIND_SORT   = 3,  /* int32 ascending LSD radix sort, 8-bit digits          */
+    XPK_KIND_GEMM   = 4,  /* bf16 C[M,N] = A[M,K] * B[N,K]^T, fp32 accumulate      */
+} xpkKind;
+
+/* Launch-time flags for xpkTaskCreate*. */
+enum {
+    XPK_FLAG_NONE           = 0,
+    XPK_FLAG_NON_PREEMPTIBLE = 1, /* build the twin: same tile loop, no flag poll, no
+                                     ticket atomics.  Used to measure the check's cost. */
+    XPK_FLAG_ABORT_INFLIGHT = 2, /* GEMM only: on preemption abandon tiles whose main
+                                     loop is still running and recompute them on resume
+                                     (keeps the preemption latency below one tile).     */
+};
+
+typedef struct xpkTask_st *xpkTask_t;
+
+/* Snapshot returned by xpkTaskQuery; mirrors the mailbox the final CTA writes. */
+typedef struct {
+    uint32_t status;       /* xpkStatus                                             */
+    uint32_t error;        /* 0, or a kernel-specific code naming the wait that expired */
+    uint64_t tiles_done;   /* tiles completed over the task's life (the cursor)     */
+    uint64_t tiles_total;  /* tiles in the task                                     */
+    uint64_t launches;     /* kernel launches issued for this task since reset      */
+    uint64_t preemptions;  /* launches that ended PREEMPTED                         */
+} xpkTaskInfo;
+
+/* ---- library / device --------------------------------------------------------------- */
+
+/* Number of SMs of the current device (the persistent grids are sized from it). */
+xpkResult xpkDeviceSmCount(int *sm_count);
+const char *xpkResultString(xpkResult r);
+
+/* ---- preempt flag -------------------------------------------------------------------
+ * A flag is one 32-bit word in device memory.  One flag is normally shared by all tasks
+ * of one hardware queue (that is what HwQueue::Deactivate raises — reference contract
+ * preempt/include/xsched/preempt/hal/hw_queue.h:36-44).  Raise/clear are enqueued as a
+ * 32-bit stream memory write on `ctrl_stream`, which should not be the stream the
+ * persistent kernel occupies.                                                          */
+xpkResult xpkFlagCreate(uint32_t **flag_dev);
+xpkResult xpkFlagDestroy(uint32_t *flag_dev);
+xpkResult xpkFlagSet(uint32_t *flag_dev, uint32_t value, void *ctrl_stream);
+
+/* ---- task creation ------------------------------------------------------------------
+ * `flag_dev` may be NULL: the task then owns a private flag (see xpkTaskFlag).
+ * `tile_elems`/tile shape 0 selects the default.                                        */
+
+/* a = b + s*c computed as one fused multiply-add per element.  n in elements. */
+xpkResult xpkTaskCreateTriad(xpkTask_t *task, float *a, const float *b, const float *c,
+                             float s, uint64_t n, uint32_t tile_elems, uint32_t flags,
+                             uint32_t *flag_dev);
+
+/* c = a + b. */
+xpkResult xpkTaskCreateVecAdd(xpkTask_t *task, float *c, const float *a, const float *b,
+                              uint64_t n, uint32_t tile_elems, uint32_t flags,
+                              uint32_t *flag_dev);
+
+/* Ascending sort of n int32 keys.  `keys` holds the input and, after completion, the
+ * sorted output (4 passes: the data ends in the buffer it started in).  `tmp` is a
+ * caller-provided buffer of n keys.  `scratch` is caller-provided device memory of at
+ * least xpkSortScratchBytes(n) bytes, 256-byte aligned; the library clears what it needs. */
+size_t    xpkSortScratchBytes(uint64_t n);
+xpkResult xpkTaskCreateSort(xpkTask_t *task, int32_t *keys, int32_t *tmp, void *scratch,
+                            uint64_t n, uint32_t flags, uint32_t *flag_dev);
+
+/* bf16 GEMM, C[M,N] (row-major, bf16) = A[M,K] (row-major) * B[N,K]^T (row-major, i.e.
+ * both operands K-major), fp32 accumulation in tensor memory.  M % 128 == 0,
+ * N % 256 == 0, K % 64 == 0.                                                            */
+xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void *B,
+                            uint32_t M, uint32_t N, uint32_t K, uint32_t flags,
+                            uint32_t *flag_dev);
+
+/* ---- task control ------------------------------------------------------------------- */
+
+/* Enqueue the task's kernel on `stream`.  A fresh or reset task starts at tile 0; a
+ * PREEMPTED task continues from its cursor; a COMPLETED task launches nothing.  Never
+ * blocks.  `sm_limit` > 0 caps the persistent grid to that many SMs (0 = all).          */
+xpkResult xpkTaskLaunch(xpkTask_t task, void *stream, int sm_limit);
+
+/* Read the mailbox (mapped host memory; no CUDA call, no synchronisation). */
+xpkResult xpkTaskQuery(xpkTask_t task, xpkTaskInfo *info);
+
+/* Spin (with back-off) on the mailbox until the launch issued most recently has
+ * published COMPLETED, PREEMPTED or ERROR, or `timeout_us` elapses (XPK_ERR_BUSY).      */
+xpkResult xpkTaskWait(xpkTask_t task, uint64_t timeout_us, xpkTaskInfo *info);
+
+/* Rewind the cursor to tile 0 (enqueued on `stream`, ordered after prior work on it). */
+xpkResult xpkTaskReset(xpkTask_t task, void *stream);
+
+/* The flag this task polls (its own, or the shared one given at creation). */
+xpkResult xpkTaskFlag(xpkTask_t task, uint32_t **flag_dev);
+xpkResult xpkTaskKind(xpkTask_t task, uint32_t *kind);
+xpkResult xpkTaskDestroy(xpkTask_t task);
+
+/* Kernels launched by this library in this process since load (all tasks). */
+uint64_t xpkLaunchCount(void);
+
+#ifdef __cplusplus
+}
+#endif

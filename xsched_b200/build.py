@@ -1,0 +1,151 @@
+"""In-tree build of every native artefact (no cmake, no JIT cache).
+
+    python -m xsched_b200.build            # build what is stale
+    python -m xsched_b200.build --force    # rebuild everything
+
+Targets land in xsched_b200/lib/ (product) and oracle/ (test-only checker).  CUDA sources are
+compiled for sm_100a only.  The oracle's compiled reference core (oracle/_ref/) is built by
+oracle/build_ref.py when the reference tree is present; that step is skipped elsewhere.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+PKG = ROOT / "xsched_b200"
+CSRC = PKG / "csrc"
+LIB = PKG / "lib"
+INC = ROOT / "include"
+ORACLE = ROOT / "oracle"
+
+NVCC = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+CXX = os.environ.get("CXX", "g++")
+CC = os.environ.get("CC", "gcc")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+NVCC_FLAGS = [
+    "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-Xcompiler", "-fPIC",
+]
+CXX_FLAGS = ["-std=c++20", "-O2", "-g", "-fPIC", "-Wall", "-Wextra", "-pthread"]
+
+
+def _stale(out: Path, deps: list[Path]) -> bool:
+    if not out.exists():
+        return True
+    t = out.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in deps if d.exists())
+
+
+def _run(cmd: list[str], verbose: bool) -> None:
+    if verbose:
+        print("+", " ".join(str(c) for c in cmd), flush=True)
+    r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError(f"build step failed: {' '.join(str(c) for c in cmd[:3])} ...")
+    if verbose and (r.stdout or r.stderr):
+        print(r.stdout + r.stderr)
+
+
+def _glob(d: Path, pats: tuple[str, ...]) -> list[Path]:
+    out: list[Path] = []
+    for p in pats:
+        out += sorted(d.rglob(p))
+    return out
+
+
+def build_xpk(force: bool = False, verbose: bool = False) -> Path:
+    """libxpk.so — the preemptible persistent kernels + their C ABI (include/xsched_b200/pk.h)."""
+    out = LIB / "libxpk.so"
+    kdir = CSRC / "kernels"
+    srcs = sorted(kdir.glob("*.cu"))
+    deps = srcs + sorted(kdir.glob("*.cuh")) + [INC / "xsched_b200" / "pk.h"]
+    if force or _stale(out, deps):
+        LIB.mkdir(parents=True, exist_ok=True)
+        _run([NVCC, *NVCC_FLAGS, "-shared", f"-I{INC}", "-o", out, *srcs], verbose)
+    return out
+
+
+def build_host(force: bool = False, verbose: bool = False) -> list[Path]:
+    """Host libraries: libpreempt.so, libhalcuda.so, libshimcuda.so, xserver and the host-only lane."""
+    outs: list[Path] = []
+    LIB.mkdir(parents=True, exist_ok=True)
+    hdrs = _glob(INC, ("*.h",)) + _glob(CSRC, ("*.h",))
+    incs = [f"-I{INC}", f"-I{CSRC}", f"-I{CUDA_HOME}/include"]
+
+    def so(name: str, subdirs: list[str], libs: list[str], extra: list[str] | None = None) -> None:
+        srcs: list[Path] = []
+        for sd in subdirs:
+            srcs += sorted((CSRC / sd).glob("*.cpp"))
+        if not srcs:
+            return
+        out = LIB / name
+        if force or _stale(out, srcs + hdrs):
+            _run([CXX, *CXX_FLAGS, "-shared", *incs, "-o", out, *srcs, f"-L{LIB}", f"-Wl,-rpath,$ORIGIN",
+                  *(extra or []), *libs], verbose)
+        outs.append(out)
+
+    so("libpreempt.so", ["utils", "sched", "preempt"], ["-ldl", "-lrt"])
+    so("libhalhost.so", ["hal_host"], ["-lpreempt"])
+    so("libhalcuda.so", ["hal_cuda"], ["-lpreempt", "-ldl"])
+    so("libshimcuda.so", ["shim"], ["-lhalcuda", "-lpreempt", "-ldl"],
+       extra=["-Wl,-soname,libcuda.so.1"])
+
+    server_srcs = sorted((CSRC / "server").glob("*.cpp"))
+    if server_srcs:
+        out = LIB / "xserver"
+        if force or _stale(out, server_srcs + hdrs + [LIB / "libpreempt.so"]):
+            _run([CXX, *CXX_FLAGS, "-fPIE", *incs, "-o", out, *server_srcs, f"-L{LIB}", "-Wl,-rpath,$ORIGIN",
+                  "-lpreempt", "-ldl", "-lrt"], verbose)
+        outs.append(out)
+    # libcuda.so.1 / libcuda.so names the dynamic loader looks for when the shim directory is put on
+    # LD_LIBRARY_PATH (same install layout as the reference: platforms/cuda/CMakeLists.txt:2-5).
+    shim = LIB / "libshimcuda.so"
+    if shim.exists():
+        d = LIB / "shim"
+        d.mkdir(exist_ok=True)
+        for alias in ("libcuda.so.1", "libcuda.so"):
+            link = d / alias
+            if link.is_symlink() or link.exists():
+                link.unlink()
+            link.symlink_to(Path("..") / "libshimcuda.so")
+    return outs
+
+
+def build_oracle(force: bool = False, verbose: bool = False) -> Path:
+    """oracle/liboracle_kernels.so — the CPU checker (test infrastructure, never shipped)."""
+    out = ORACLE / "liboracle_kernels.so"
+    src = ORACLE / "kernels_oracle.c"
+    if force or _stale(out, [src]):
+        _run([CC, "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-o", out, src, "-lm"], verbose)
+    return out
+
+
+def build_oracle_ref(force: bool = False, verbose: bool = False) -> Path | None:
+    """oracle/_ref/ — the reference's own host core compiled from its sources where they lie.
+    Only possible where the reference tree exists; elsewhere the prebuilt files are used."""
+    script = ORACLE / "build_ref.py"
+    if not script.exists():
+        return None
+    ref = Path(os.environ.get("XSCHED_REFERENCE_DIR", "/root/reference"))
+    if not ref.exists():
+        return None
+    cmd = [sys.executable, str(script)] + (["--force"] if force else [])
+    _run(cmd, verbose)
+    return ORACLE / "_ref"
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_xpk(force, verbose)
+    build_host(force, verbose)
+    build_oracle(force, verbose)
+    build_oracle_ref(force, verbose)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose=True)

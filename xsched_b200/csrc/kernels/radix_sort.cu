@@ -1,0 +1,313 @@
+// Preemptible persistent int32 LSD radix sort (8-bit digits, 4 passes, ascending).
+//
+// One persistent kernel walks a single ticket sequence of 5*T tiles (T = ceil(n / 8192)):
+//   phase 0, tickets [0,T):       digit histograms of all four bytes of every key, summed
+//                                 into hist[4][256] with integer atomics (order-free, exact);
+//   phase p=1..4, tickets [pT,(p+1)T): scatter pass p-1 over tile j = ticket - pT.
+// A tile of phase p starts only after all T tiles of phase p-1 have finished (a counter per
+// phase in the control block).  Tickets are claimed in increasing order by resident CTAs and
+// a claimed tile only ever waits on smaller tickets, so the waits cannot deadlock; they are
+// bounded all the same and raise an error instead of spinning forever.
+//
+// Inside a scatter tile (512 threads x 16 keys, keys held warp-striped so that load order is
+// preserved):
+//   * each warp ranks its keys digit by digit with __match_any_sync / __popc — the lanes that
+//     share a digit learn their order from the match mask, the lowest lane bumps the warp's
+//     counter in shared memory and __shfl_sync hands the base back (stable within the warp);
+//   * warp counters are prefix-summed across warps, giving stable ranks within the tile;
+//   * the tile's per-digit counts are published and the exclusive prefix over earlier tiles
+//     is obtained by decoupled look-back (one thread per digit);
+//   * keys are staged in shared memory in ranked order and written out so that consecutive
+//     threads write consecutive addresses of the same digit's run.
+//
+// HBM traffic: one read for the histograms plus a read and a write per pass:
+// (1 + 2*4) * 4n bytes.  Source keys are read with ld.global.cg: a buffer read in pass p is
+// rewritten by other CTAs in pass p+1 and read again in pass p+2 by this same kernel, so a
+// line cached in L1 would be stale.
+//
+// The cursor is the ticket counter: a preempted launch leaves every claimed tile finished,
+// the phase counters and look-back words stay in global memory, and the relaunch continues
+// with the next ticket.  Integer arithmetic only, so the result is bit-exact by construction.
+#include "pk_common.cuh"
+
+namespace xpk {
+
+constexpr int kSortThreads = 512;
+constexpr int kSortWarps   = kSortThreads / 32;
+constexpr int kSortItems   = 16;
+constexpr int kSortTile    = kSortThreads * kSortItems;   // 8192 keys
+constexpr int kRadix       = 256;
+constexpr uint32_t kFlagAgg  = 1u << 30;
+constexpr uint32_t kFlagInc  = 2u << 30;
+constexpr uint32_t kValMask  = (1u << 30) - 1u;
+constexpr unsigned long long kSpinLimitNs = 2000000000ull;   // 2 s per wait
+
+constexpr uint32_t kErrSortPhaseWait = 0x50000001u;
+constexpr uint32_t kErrSortLookback  = 0x50000002u;
+
+struct SortSmem {
+    uint32_t warp_hist[kSortWarps][kRadix];   // per-warp digit counters -> exclusive prefix over warps
+    uint32_t keys[kSortTile];                 // ranked staging / phase-0 histograms
+    uint32_t tile_off[kRadix];                // exclusive digit offsets inside the tile
+    uint32_t gbase[kRadix];                   // dst index = gbase[digit] + rank in tile (mod 2^32)
+    uint32_t scan_tmp[kSortWarps];
+    unsigned long long tile;
+    uint32_t bail;
+};
+
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t ld_relaxed(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed(uint32_t *p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Signed ascending order == unsigned order of the key with its sign bit flipped.
+__device__ __forceinline__ uint32_t twiddle(uint32_t k) { return k ^ 0x80000000u; }
+
+// Exclusive scan of 256 values held by threads 0..255 (one each); all 512 threads call.
+__device__ __forceinline__ uint32_t block_excl_scan256(uint32_t v, SortSmem &sm, uint32_t *total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) sm.scan_tmp[warp] = inc;
+    __syncthreads();
+    uint32_t add = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        uint32_t t = sm.scan_tmp[w];
+        if (w < warp) add += t;
+        tot += t;
+    }
+    __syncthreads();
+    if (total) *total = tot;
+    return inc - v + add;
+}
+
+// Wait until *counter >= target.  Thread 0 spins; returns false (and raises `code`) on timeout
+// or when another CTA has already raised an error.
+__device__ __forceinline__ bool wait_counter(Ctl *ctl, const unsigned long long *counter,
+                                             unsigned long long target, uint32_t code) {
+    if (ld_acquire64(counter) >= target) return true;
+    const unsigned long long t0 = gtime_ns();
+    uint32_t it = 0;
+    while (ld_acquire64(counter) < target) {
+        __nanosleep(64);
+        if ((++it & 255u) == 0) {
+            if (ld_relaxed(&ctl->error) != 0) return false;
+            if (gtime_ns() - t0 > kSpinLimitNs) { raise_error(ctl, code); return false; }
+        }
+    }
+    return true;
+}
+
+template <bool kPoll>
+__device__ __forceinline__ unsigned long long sort_claim(Ctl *ctl) {
+    if constexpr (kPoll) return claim_tile(ctl);
+    // Twin: same ticket order (the look-back needs it) but the flag is never read.
+    unsigned long long t = atomicAdd(&ctl->claim_seq, 1ull);
+    const unsigned long long fresh = ctl->total - ctl->base;
+    return t < fresh ? ctl->base + t : kNoTile;
+}
+
+template <bool kPoll>
+__global__ void __launch_bounds__(kSortThreads, 2)
+radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint32_t *state,
+                  unsigned long long n, unsigned long long T, unsigned long long launch_no) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    SortSmem &sm = *reinterpret_cast<SortSmem *>(smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned long long *phase_done = ctl->user;       // [0..4]
+    unsigned long long done = 0;
+
+    while (true) {
+        if (tid == 0) {
+            unsigned long long t = sort_claim<kPoll>(ctl);
+            uint32_t bail = 0;
+            if (t != kNoTile) {
+                const unsigned long long phase = t / T;
+                if (phase > 0 && !wait_counter(ctl, &phase_done[phase - 1], T, kErrSortPhaseWait))
+                    bail = 1;
+            }
+            sm.tile = t;
+            sm.bail = bail;
+        }
+        __syncthreads();
+        const unsigned long long ticket = sm.tile;
+        if (ticket == kNoTile || sm.bail) break;
+        const unsigned long long phase = ticket / T;
+        const unsigned long long j = ticket - phase * T;
+        const unsigned long long lo = j * (unsigned long long)kSortTile;
+        const uint32_t count = (uint32_t)((n - lo) < (unsigned long long)kSortTile ? (n - lo) : kSortTile);
+
+        if (phase == 0) {
+            // ---- histograms of all four digits of this tile's keys ----
+            uint32_t *h = sm.keys;                     // [4][256]
+            for (int i = tid; i < 4 * kRadix; i += kSortThreads) h[i] = 0;
+            __syncthreads();
+            for (uint32_t i = tid; i < count; i += kSortThreads) {
+                const uint32_t k = twiddle(__ldcg(keys + lo + i));
+                atomicAdd(&h[0 * kRadix + (k & 255u)], 1u);
+                atomicAdd(&h[1 * kRadix + ((k >> 8) & 255u)], 1u);
+                atomicAdd(&h[2 * kRadix + ((k >> 16) & 255u)], 1u);
+                atomicAdd(&h[3 * kRadix + (k >> 24)], 1u);
+            }
+            __syncthreads();
+            for (int i = tid; i < 4 * kRadix; i += kSortThreads) {
+                const uint32_t c = h[i];
+                if (c) atomicAdd(&hist[i], c);
+            }
+        } else {
+            const int pass = (int)phase - 1;
+            const int shift = pass * 8;
+            const uint32_t *src = (pass & 1) ? tmp : keys;
+            uint32_t *dst = (pass & 1) ? keys : tmp;
+            uint32_t *st = state + ((unsigned long long)pass * T + j) * kRadix;
+
+            // ---- load (warp-striped) ----
+            uint32_t key[kSortItems];
+            uint32_t rank[kSortItems];
+            const uint32_t wbase = warp * (32 * kSortItems);
+#pragma unroll
+            for (int i = 0; i < kSortItems; ++i) {
+                const uint32_t idx = wbase + i * 32 + lane;
+                key[i] = idx < count ? twiddle(__ldcg(src + lo + idx)) : 0xFFFFFFFFu;
+            }
+            for (int i = tid; i < kSortWarps * kRadix; i += kSortThreads) (&sm.warp_hist[0][0])[i] = 0;
+            __syncthreads();
+
+            // ---- stable rank inside the warp ----
+            uint32_t *wh = sm.warp_hist[warp];
+#pragma unroll
+            for (int i = 0; i < kSortItems; ++i) {
+                const uint32_t d = (key[i] >> shift) & 255u;
+                const uint32_t mask = __match_any_sync(0xffffffffu, d);
+                const int leader = __ffs(mask) - 1;
+                const uint32_t before = __popc(mask & ((1u << lane) - 1u));
+                uint32_t base = 0;
+                if (lane == leader) { base = wh[d]; wh[d] = base + __popc(mask); }
+                base = __shfl_sync(0xffffffffu, base, leader);
+                rank[i] = base + before;
+                __syncwarp();
+            }
+            __syncthreads();
+
+            // ---- per-digit totals, exclusive prefix over warps ----
+            uint32_t cnt = 0;
+            if (tid < kRadix) {
+#pragma unroll
+                for (int w = 0; w < kSortWarps; ++w) {
+                    const uint32_t c = sm.warp_hist[w][tid];
+                    sm.warp_hist[w][tid] = cnt;
+                    cnt += c;
+                }
+                // Publish early so later tiles can look back through this one.
+                st_relaxed(st + tid, (j == 0 ? kFlagInc : kFlagAgg) | cnt);
+            }
+            const uint32_t toff = block_excl_scan256(tid < kRadix ? cnt : 0u, sm, nullptr);
+            // Global start of each digit in this pass.
+            const uint32_t hval = tid < kRadix ? __ldcg(hist + pass * kRadix + tid) : 0u;
+            const uint32_t goff = block_excl_scan256(hval, sm, nullptr);
+
+            if (tid < kRadix) {
+                // ---- decoupled look-back over earlier tiles of this pass ----
+                uint32_t excl = 0;
+                bool ok = true;
+                if (j > 0) {
+                    long long k = (long long)j - 1;
+                    const unsigned long long t0 = gtime_ns();
+                    uint32_t it = 0;
+                    while (true) {
+                        const uint32_t s = ld_relaxed(state + ((unsigned long long)pass * T + k) * kRadix + tid);
+                        const uint32_t f = s & ~kValMask;
+                        if (f == 0) {
+                            __nanosleep(32);
+                            if ((++it & 255u) == 0) {
+                                if (ld_relaxed(&ctl->error) != 0) { ok = false; break; }
+                                if (gtime_ns() - t0 > kSpinLimitNs) { raise_error(ctl, kErrSortLookback); ok = false; break; }
+                            }
+                            continue;
+                        }
+                        excl += s & kValMask;
+                        if (f == kFlagInc) break;
+                        --k;
+                    }
+                    if (ok) st_relaxed(st + tid, kFlagInc | ((excl + cnt) & kValMask));
+                }
+                sm.tile_off[tid] = toff;
+                sm.gbase[tid] = goff + excl - toff;
+                if (!ok) sm.bail = 1;
+            }
+            __syncthreads();
+            if (sm.bail) break;
+
+            // ---- stage in ranked order ----
+#pragma unroll
+            for (int i = 0; i < kSortItems; ++i) {
+                const uint32_t d = (key[i] >> shift) & 255u;
+                sm.keys[sm.tile_off[d] + sm.warp_hist[warp][d] + rank[i]] = key[i];
+            }
+            __syncthreads();
+
+            // ---- write out: consecutive threads -> consecutive addresses per digit run ----
+            for (uint32_t idx = tid; idx < count; idx += kSortThreads) {
+                const uint32_t k = sm.keys[idx];
+                const uint32_t d = (k >> shift) & 255u;
+                dst[sm.gbase[d] + idx] = twiddle(k);
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            atomicAdd(&phase_done[phase], 1ull);
+        }
+        ++done;
+    }
+    __syncthreads();
+    if (tid == 0) cta_exit(ctl, done, launch_no);
+}
+
+size_t sort_smem_bytes() { return sizeof(SortSmem); }
+
+cudaError_t sort_prepare() {
+    cudaError_t e = cudaFuncSetAttribute(radix_sort_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(radix_sort_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
+}
+
+int sort_ctas_per_sm() {
+    int a = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&a, radix_sort_kernel<true>, kSortThreads, sizeof(SortSmem));
+    return a < 1 ? 1 : a;
+}
+
+unsigned long long sort_tiles(unsigned long long n) { return (n + kSortTile - 1) / kSortTile; }
+
+cudaError_t launch_sort(bool preemptible, Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist,
+                        uint32_t *state, unsigned long long n, unsigned long long launch_no,
+                        int grid, cudaStream_t stream) {
+    const unsigned long long T = sort_tiles(n);
+    if (preemptible)
+        radix_sort_kernel<true><<<grid, kSortThreads, sizeof(SortSmem), stream>>>(ctl, keys, tmp, hist, state, n, T, launch_no);
+    else
+        radix_sort_kernel<false><<<grid, kSortThreads, sizeof(SortSmem), stream>>>(ctl, keys, tmp, hist, state, n, T, launch_no);
+    return cudaGetLastError();
+}
+
+} // namespace xpk
