@@ -47,6 +47,7 @@ struct xpkTask_st {
     unsigned long long total = 0;
     unsigned long long launches = 0;        // launch counter echoed by the mailbox
     unsigned long long reset_at = 0;        // value of `launches` at the last reset
+    cudaStream_t last_stream = nullptr;     // stream of the most recent launch
     // operands
     void *p0 = nullptr; const void *p1 = nullptr; const void *p2 = nullptr;
     float s = 0.f;
@@ -317,6 +318,7 @@ xpkResult xpkTaskLaunch(xpkTask_t t, void *stream, int sm_limit) {
         return XPK_ERR_INVALID_VALUE;
     }
     if (e != cudaSuccess) return XPK_ERR_CUDA;
+    t->last_stream = s;
     g_launches.fetch_add(1);
     return XPK_SUCCESS;
 }
@@ -354,6 +356,9 @@ xpkResult xpkTaskWait(xpkTask_t t, uint64_t timeout_us, xpkTaskInfo *info) {
         if (++spins > 2000) {
             std::this_thread::yield();
             if ((spins & 1023u) == 0) {
+                // A faulted context never publishes: surface the CUDA error instead of timing out.
+                const cudaError_t qe = cudaStreamQuery(t->last_stream);
+                if (qe != cudaSuccess && qe != cudaErrorNotReady) return XPK_ERR_CUDA;
                 const auto us = std::chrono::duration_cast<std::chrono::microseconds>(
                                     std::chrono::steady_clock::now() - t0).count();
                 if ((uint64_t)us > timeout_us) return XPK_ERR_BUSY;
