@@ -1,0 +1,33 @@
+// Same-host message channel between scheduling agents and the server: a datagram per record, in order,
+// over abstract-namespace Unix sockets named "<namespace>xsched.ipc.<key>" (key 1 = server, otherwise
+// the client's pid — the reference's key assignment, protocol/include/xsched/protocol/def.h:35-37).
+// The reference uses its un-vendored `ipc` library here, whose transport is not part of its tree.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <vector>
+
+namespace xsched::sched {
+
+class IpcEndpoint {
+public:
+    IpcEndpoint() = default;
+    ~IpcEndpoint();
+    IpcEndpoint(const IpcEndpoint &) = delete;
+    IpcEndpoint &operator=(const IpcEndpoint &) = delete;
+
+    bool Bind(uint64_t key);                       // become the receiver of `key`
+    bool OpenSender();                             // unbound socket for SendTo
+    bool SendTo(uint64_t key, const void *data, size_t size);
+    /// Blocks.  Returns bytes received, 0 after Close(), -1 on error.
+    long Receive(void *buf, size_t cap);
+    void Close();                                  // wakes a blocked Receive
+    bool Ok() const { return fd_ >= 0; }
+private:
+    int fd_ = -1;
+    uint64_t key_ = 0;
+    bool bound_ = false;
+    volatile bool closed_ = false;
+};
+
+} // namespace xsched::sched

@@ -126,6 +126,20 @@ def build_oracle(force: bool = False, verbose: bool = False) -> Path:
     return out
 
 
+def build_lane_driver(force: bool = False, verbose: bool = False) -> Path | None:
+    """oracle/lane_driver_new — the scenario runner linked against this repository's libraries
+    (its twin linked against the reference core is built by oracle/build_ref.py)."""
+    src = ORACLE / "lane_driver.cpp"
+    out = ORACLE / "lane_driver_new"
+    deps = [src, LIB / "libpreempt.so", LIB / "libhalhost.so"]
+    if not src.exists() or not (LIB / "libhalhost.so").exists():
+        return None
+    if force or _stale(out, deps):
+        _run([CXX, "-std=c++20", "-O2", "-pthread", f"-I{INC}", "-o", out, src, f"-L{LIB}", f"-Wl,-rpath,{LIB}",
+              "-lhalhost", "-lpreempt"], verbose)
+    return out
+
+
 def build_oracle_ref(force: bool = False, verbose: bool = False) -> Path | None:
     """oracle/_ref/ — the reference's own host core compiled from its sources where they lie.
     Only possible where the reference tree exists; elsewhere the prebuilt files are used."""
@@ -144,6 +158,7 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
     build_xpk(force, verbose)
     build_host(force, verbose)
     build_oracle(force, verbose)
+    build_lane_driver(force, verbose)
     build_oracle_ref(force, verbose)
 
 

@@ -1,0 +1,74 @@
+#include "xsched/sched/ipc.h"
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <sys/socket.h>
+#include <sys/un.h>
+#include <unistd.h>
+#include "xsched/protocol/def.h"
+#include "xsched/utils/env.h"
+
+namespace xsched::sched {
+
+static socklen_t MakeAddr(uint64_t key, sockaddr_un &addr) {
+    std::memset(&addr, 0, sizeof(addr));
+    addr.sun_family = AF_UNIX;
+    const std::string ns = GetEnv(XSCHED_IPC_NAMESPACE_ENV_NAME);
+    const int n = std::snprintf(addr.sun_path + 1, sizeof(addr.sun_path) - 1, "%sxsched.ipc.%llu", ns.c_str(), (unsigned long long)key);
+    return (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
+}
+
+IpcEndpoint::~IpcEndpoint() {
+    if (fd_ >= 0) ::close(fd_);
+}
+
+bool IpcEndpoint::OpenSender() {
+    fd_ = ::socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
+    return fd_ >= 0;
+}
+
+bool IpcEndpoint::Bind(uint64_t key) {
+    if (!OpenSender()) return false;
+    int sz = 4 << 20;
+    ::setsockopt(fd_, SOL_SOCKET, SO_RCVBUF, &sz, sizeof(sz));
+    sockaddr_un addr;
+    const socklen_t len = MakeAddr(key, addr);
+    if (::bind(fd_, (sockaddr *)&addr, len) != 0) { ::close(fd_); fd_ = -1; return false; }
+    key_ = key;
+    bound_ = true;
+    return true;
+}
+
+bool IpcEndpoint::SendTo(uint64_t key, const void *data, size_t size) {
+    if (fd_ < 0 || closed_) return false;
+    sockaddr_un addr;
+    const socklen_t len = MakeAddr(key, addr);
+    return ::sendto(fd_, data, size, 0, (sockaddr *)&addr, len) == (ssize_t)size;
+}
+
+long IpcEndpoint::Receive(void *buf, size_t cap) {
+    if (fd_ < 0) return -1;
+    if (closed_) return 0;
+    const ssize_t n = ::recv(fd_, buf, cap, 0);
+    if (closed_) return 0;
+    return n < 0 ? -1 : (long)n;
+}
+
+void IpcEndpoint::Close() {
+    if (closed_) return;
+    closed_ = true;
+    if (fd_ >= 0 && bound_) {
+        // wake a blocked Receive with an empty datagram to ourselves
+        const int s = ::socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
+        if (s >= 0) {
+            sockaddr_un addr;
+            const socklen_t len = MakeAddr(key_, addr);
+            char z = 0;
+            ::sendto(s, &z, 0, 0, (sockaddr *)&addr, len);
+            ::close(s);
+        }
+    }
+}
+
+} // namespace xsched::sched
