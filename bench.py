@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the CUDA preemption path on B200.
+
+Workload (`config.workload` = "gemm8192_vs_vecadd64M"): a low-priority process runs a persistent,
+preemptible bf16 GEMM (M=N=K=8192, A,B ~ N(0,1), fp32 accumulate) in a loop through a level-2 XQueue;
+a high-priority process issues an fp32 vector add over 64 Mi elements ~ U(-1,1) every 10 ms through
+its own XQueue; one xserver with the HPF policy schedules both.  One "step" is one high-priority
+request.  Reported:
+
+  value              P99 latency of the high-priority request while co-running / its P99 standalone
+                     (lower is better; inputs resident in HBM)
+  preempt_latency_us wall time of XQueueSuspend(xq, SyncHwQueue) on the busy low-priority queue (P99)
+  bg_throughput_kept_pct   low-priority throughput while co-running / standalone, in percent
+  e2e                the same ratio when every request also copies its inputs from pinned host memory
+                     and its result back (through HwCommand callbacks on the XQueue)
+  roofline           the GEMM kernel against the measured bf16 tensor peak
+  cpu_baseline       the reference's own host core on the host-only lane (config 0), timed beside it
+
+`--impl reference` times the reference's host core alone (oracle/_ref, compiled from its sources).
+With N > 1 ranks (torchrun) every rank drives its own GPU; rank 0 runs the single xserver.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import signal
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+LIB = ROOT / "xsched_b200" / "lib"
+WORKER = LIB / "xbench_worker"
+XSERVER = LIB / "xserver"
+REF_DRIVER = ROOT / "oracle" / "_ref" / "lane_driver_ref"
+
+GEMM = dict(M=8192, N=8192, K=8192)
+HP_N = 1 << 26
+PERIOD_US = 10_000
+E2E_PERIOD_US = 60_000
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, gpu: int):
+        super().__init__(daemon=True)
+        self.gpu = gpu
+        self.samples: list[int] = []
+        self.max_mhz = 0
+        self.reasons: set[str] = set()
+        self._stop = threading.Event()
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().split(",")
+                self.samples.append(int(out[0]))
+                self.max_mhz = int(out[1])
+                for n, v in zip(names, out[2:]):
+                    if v.strip().lower().startswith("active"):
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def stop(self) -> dict:
+        self._stop.set()
+        self.join(timeout=6)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz or None, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def worker_cmd(role: str, device: int, **kw) -> list[str]:
+    cmd = [str(WORKER), "--role", role, "--device", str(device)]
+    for k, v in kw.items():
+        cmd += ["--" + k.replace("_", "-"), str(v)]
+    return cmd
+
+
+def run_json(cmd: list[str], env: dict, timeout: float) -> list[dict]:
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout)
+    if r.returncode != 0:
+        raise RuntimeError(f"{' '.join(cmd[:4])} failed rc={r.returncode}: {r.stderr[-1500:]}")
+    return [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+
+
+def base_env(ns: str, sched: str | None) -> dict:
+    env = dict(os.environ, XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns)
+    env.pop("XSCHED_POLICY", None)
+    if sched:
+        env["XSCHED_SCHEDULER"] = sched
+    else:
+        env.pop("XSCHED_SCHEDULER", None)
+    return env
+
+
+def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, period_us: int, lp_kw: dict) -> tuple[dict, dict]:
+    """LP process + HP process under the (already running) xserver.  Returns (hp_json, lp_json)."""
+    env = base_env(ns, "GLB")
+    lp = subprocess.Popen(worker_cmd("lp", device, level=level, prio=0, duration_s=3600, warmup_s=0.5, **lp_kw),
+                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+    try:
+        t0 = time.time()
+        while True:
+            line = lp.stdout.readline()
+            if line.startswith("READY"):
+                break
+            if not line and lp.poll() is not None:
+                raise RuntimeError("LP worker died: " + lp.stderr.read()[-1500:])
+            if time.time() - t0 > 120:
+                raise RuntimeError("LP worker did not become ready")
+        hp = run_json(worker_cmd("hp", device, level=level, prio=1, count=steps + warmup, period_us=period_us, hp_n=HP_N,
+                                 e2e=int(e2e)), env, timeout=600)[-1]
+    finally:
+        lp.send_signal(signal.SIGTERM)
+        out, err = lp.communicate(timeout=120)
+    lp_json = [json.loads(l) for l in out.splitlines() if l.startswith("{")]
+    if not lp_json:
+        raise RuntimeError("LP worker printed no result: " + err[-1500:])
+    return hp, lp_json[-1]
+
+
+def gemm_roofline(device: int) -> tuple[dict, int]:
+    """Average launch duration of the preemptible GEMM, CUDA events on the launching stream."""
+    import torch
+    from xsched_b200 import pk
+    torch.cuda.set_device(device)
+    M, N, K = GEMM["M"], GEMM["N"], GEMM["K"]
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16)
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    t = pk.Task.gemm(c, a, b, flags=pk.FLAG_ABORT_INFLIGHT)
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(5):
+        t.reset(s); t.launch(s)
+    torch.cuda.synchronize()
+    reps = 30
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for e0, e1 in evs:                 # inputs (256 MiB) + output exceed L2, so every launch streams from HBM
+        t.reset(s)
+        e0.record(); t.launch(s); e1.record()
+    torch.cuda.synchronize()
+    ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
+    avg = sum(ms) / len(ms)
+    pk_ = peaks()
+    achieved = 2.0 * M * N * K / (avg * 1e-3) / 1e12
+    t.destroy()
+    return ({"bound": "tensor", "kernel": "gemm_bf16_kernel<preemptible, abort>", "achieved": round(achieved, 1),
+             "peak": pk_["bf16_tflops"], "peak_source": pk_["source"] + " bf16_tflops (burst: kernel timed alone)", "unit": "TFLOP/s",
+             "frac": round(achieved / pk_["bf16_tflops"], 4), "avg_launch_ms": round(avg, 4), "median_launch_ms": round(ms[len(ms) // 2], 4),
+             "traffic": None}, reps + 5)
+
+
+def reference_config0(level: int, lp_count: int, threshold: int = 16, batch: int = 8, lp_us: int = 1000, hp_us: int = 2000,
+                      rate: int = 20, seed: int = 42) -> dict:
+    """The reference's own host core (oracle/_ref) on the host-only lane.  seed 0 = periodic arrivals."""
+    env = dict(os.environ, XLOG_LEVEL="ERRO")
+    r = subprocess.run([str(REF_DRIVER), "config0", str(level), str(lp_count), str(lp_us), str(hp_us), str(rate), str(seed),
+                        str(threshold), str(batch), "LCL"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    if r.returncode != 0:
+        raise RuntimeError("reference host run failed: " + r.stderr[-1000:])
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def dist_ctx():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    pg = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo")       # control-plane barrier/reduction only: the path has no collective
+        pg = dist
+    return rank, world, local, pg
+
+
+def impl_reference(args) -> None:
+    rank, world, _, pg = dist_ctx()
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    if not REF_DRIVER.exists():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/lane_driver_ref not built (needs the reference tree at build time)"}))
+        return
+    # The benchmark's own workload, replayed in time on the host-only lane: the reference core has no
+    # Blackwell kernel to run (its CUDA level 2 stops at sm_86), so each GEMM launch becomes an 800 us
+    # busy-spin command and each vector add a 160 us one, arriving every 10 ms, under the reference's stock
+    # level-1 path (threshold/batch 16/8).  K steps = K high-priority arrivals.
+    steps = max(20, min(args.steps + args.warmup, 1500))
+    lp_us, hp_us, period_us = 800, 160, PERIOD_US
+    lp_count = int(steps * period_us / lp_us)
+    t0 = time.time()
+    r = reference_config0(1, lp_count, lp_us=lp_us, hp_us=hp_us, rate=1_000_000 // period_us, seed=0)
+    wall = time.time() - t0
+    n = max(1, r["corun"]["n"])
+    line = {
+        "impl": "reference", "metric": "hp_p99_latency_vs_standalone", "value": round(r["p99_ratio"], 3), "unit": "x",
+        "n_gpus": args.gpus, "steps": n, "warmup": args.warmup, "ms_per_step": round(wall * 1e3 / n, 3), "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "n/a (host busy-spin commands)", "data": "synthetic",
+        "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "preempt_level": 1, "hp_period_us": period_us,
+                   "replay": f"host-only lane: {lp_count} LP commands of {lp_us} us back-to-back, HP commands of {hp_us} us every {period_us} us, "
+                             "reference core (LCL scheduler), threshold/batch 16/8"},
+        "hp_p50_us": r["corun"]["p50_us"], "hp_p99_us": r["corun"]["p99_us"], "hp_standalone_p99_us": r["standalone"]["p99_us"],
+        "bg_throughput_kept_pct": r["lp_kept_pct"],
+        "cpu_baseline": {"value": round(r["p99_ratio"], 3), "unit": "x", "cores": cores, "kind": "reference",
+                         "sample": f"{lp_count} LP + {n} HP busy-spin commands on one lane thread (reference core compiled from its sources)"},
+        "e2e": {"value": round(r["p99_ratio"], 3), "unit": "x", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--level1", action="store_true", help="also run the co-run phase at preemption level 1")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        impl_reference(args)
+        return
+    if not WORKER.exists() or not (LIB / "libxpk.so").exists():
+        raise SystemExit("native libraries missing: run `python -c 'import __graft_entry__ as g; g.build()'` (there is no fallback path)")
+    args.warmup = max(3, args.warmup)
+
+    rank, world, local, pg = dist_ctx()
+    device = local
+    ns = f"bench{os.environ.get('MASTER_PORT', os.getpid())}."
+    lp_kw = dict(kernel="gemm", abort=1, depth=8, **GEMM)
+    launches = 0
+
+    server = None
+    if rank == 0:
+        server = subprocess.Popen([str(XSERVER), "HPF", "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+                                  env=base_env(ns, None))
+        server.stdout.readline()
+    if pg:
+        pg.barrier()
+    try:
+        # ---- standalone phases (untimed with respect to the step clock) ----
+        env_alone = base_env(ns, "APP")
+        hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(100, args.steps // 2), period_us=PERIOD_US, hp_n=HP_N), env_alone, 300)[-1]
+        lp_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **lp_kw), env_alone, 300)[-1]
+        launches += hp_alone["xpk_launches"] + lp_alone["xpk_launches"]
+        lat = run_json(worker_cmd("preempt-latency", device, level=2, count=300, abort=1, depth=8, kernel="gemm", **GEMM), env_alone, 300)[-1]
+        roof, roof_launches = gemm_roofline(device)
+        launches += roof_launches
+
+        # ---- timed region: K high-priority steps against the running low-priority loop ----
+        if pg:
+            pg.barrier()
+        sampler = ClockSampler(device)
+        sampler.start()
+        t0 = time.time()
+        hp_co, lp_co = corun(device, ns, 2, args.steps, args.warmup, False, PERIOD_US, lp_kw)
+        elapsed = time.time() - t0
+        clocks = sampler.stop()
+        launches += hp_co["xpk_launches"] + lp_co["xpk_launches"]
+        if pg:
+            pg.barrier()
+
+        extra = {}
+        if args.level1:
+            hp_l1, lp_l1 = corun(device, ns, 1, args.steps, args.warmup, False, PERIOD_US, lp_kw)
+            extra["level1"] = {"hp_p99_us": hp_l1["p99_us"], "ratio": round(hp_l1["p99_us"] / hp_alone["p99_us"], 3),
+                               "bg_kept_pct": round(100 * lp_l1["rate"] / lp_alone["rate"], 2)}
+        e2e = None
+        if not args.no_e2e:
+            n_e2e = max(30, args.steps // 6)
+            hp_e_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=n_e2e, period_us=E2E_PERIOD_US, hp_n=HP_N, e2e=1), env_alone, 600)[-1]
+            hp_e, lp_e = corun(device, ns, 2, n_e2e, 5, True, E2E_PERIOD_US, lp_kw)
+            launches += hp_e_alone["xpk_launches"] + hp_e["xpk_launches"] + lp_e["xpk_launches"]
+            e2e = {"value": round(hp_e["p99_us"] / hp_e_alone["p99_us"], 4), "unit": "x", "h2d_bytes_per_step": int(hp_e["h2d_bytes"]),
+                   "d2h_bytes_per_step": int(hp_e["d2h_bytes"]), "hp_p99_us": hp_e["p99_us"], "hp_standalone_p99_us": hp_e_alone["p99_us"],
+                   "period_us": E2E_PERIOD_US, "bg_throughput_kept_pct": round(100 * lp_e["rate"] / lp_alone["rate"], 2),
+                   "note": "request = H2D of both inputs from pinned memory + vector add + D2H of the result, as XQueue callback commands"}
+    finally:
+        if pg:
+            pg.barrier()
+        if server:
+            server.send_signal(signal.SIGTERM)
+            try:
+                server.wait(timeout=10)
+            except subprocess.TimeoutExpired:
+                server.kill()
+
+    ratio = hp_co["p99_us"] / hp_alone["p99_us"]
+    kept = 100.0 * lp_co["rate"] / lp_alone["rate"]
+    mine = {"ratio": ratio, "kept": kept, "lp_rate": lp_co["rate"], "preempt_p99": lat["preempt_p99_us"], "elapsed": elapsed,
+            "bit_exact": lp_co["bit_exact"] and lat["bit_exact"], "hp_p99": hp_co["p99_us"], "alone_p99": hp_alone["p99_us"]}
+    allr = [mine]
+    if pg:
+        allr = [None] * world
+        pg.all_gather_object(allr, mine)
+    if rank != 0:
+        return
+
+    cpu_baseline = None
+    if not args.no_cpu_baseline and REF_DRIVER.exists():
+        r1 = reference_config0(1, 3000)
+        cpu_baseline = {"value": round(r1["p99_ratio"], 3), "unit": "x", "cores": os.cpu_count(), "kind": "reference",
+                        "sample": "config 0 on the host-only lane: 3000 x 1 ms LP commands + 2 ms HP commands Poisson 20/s (seed 42), "
+                                  "reference core compiled from its sources, LCL scheduler + HPF, level 1, threshold/batch 16/8",
+                        "hp_p99_us": r1["corun"]["p99_us"], "hp_standalone_p99_us": r1["standalone"]["p99_us"], "lp_kept_pct": r1["lp_kept_pct"]}
+
+    worst = max(allr, key=lambda r: r["ratio"])
+    line = {
+        "metric": "hp_p99_latency_vs_standalone", "value": round(worst["ratio"], 4), "unit": "x", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(max(r["elapsed"] for r in allr) * 1e3 / (args.steps + args.warmup), 3),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate) LP GEMM; f32 HP vector add",
+        "data": "synthetic", "impl": "ours",
+        "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "processes_per_gpu": 2, "preempt_level": 2, "hp_period_us": PERIOD_US,
+                   "lp": "persistent preemptible bf16 GEMM 8192^3 in a loop", "hp": "fp32 vector add, 64 Mi elements",
+                   "l2": "LP operands+output 384 MiB and HP arrays 768 MiB both exceed the 126 MB L2 (no flush needed)", "xserver": 1},
+        "hp_p99_us": round(worst["hp_p99"], 2), "hp_standalone_p99_us": round(worst["alone_p99"], 2),
+        "preempt_latency_us": round(max(r["preempt_p99"] for r in allr), 2),
+        "preempt_latency": {"p50_us": lat["preempt_p50_us"], "p95_us": lat["preempt_p95_us"], "p99_us": lat["preempt_p99_us"],
+                            "definition": "wall time of XQueueSuspend(xq, kQueueSuspendFlagSyncHwQueue), 300 samples at random moments"},
+        "bg_throughput_kept_pct": round(min(r["kept"] for r in allr), 2),
+        "bg_tflops_aggregate": round(sum(r["lp_rate"] for r in allr), 1), "bg_tflops_standalone": lp_alone["rate"],
+        "bit_exact": all(r["bit_exact"] for r in allr),
+        "per_gpu": [{"ratio": round(r["ratio"], 4), "kept_pct": round(r["kept"], 2), "preempt_p99_us": r["preempt_p99"]} for r in allr],
+        "roofline": roof, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        "deactivations": lp_co["deactivations"], "relaunches": lp_co["relaunches"],
+    }
+    line.update(extra)
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -9,8 +9,8 @@
 //   lane_driver window   <threshold> <batch> <count> <spin_us>
 //   lane_driver suspend  <level> <count> <spin_us>
 //   lane_driver drop     <level> <count> <spin_us>
-//   lane_driver hpf      <level> <lp_count> <lp_us> <hp_count> <hp_us> <hp_gap_us> <threshold> <batch>
-//   lane_driver config0  <level> <lp_count> <lp_us> <hp_us> <hp_rate_per_s> <seed> <threshold> <batch> <sched:APP|LCL>
+//   lane_driver hpf      <level> <lp_count> <lp_us> <hp_count> <hp_us> <hp_gap_us> <threshold> <batch> [LCL|GLB]
+//   lane_driver config0  <level> <lp_count> <lp_us> <hp_us> <hp_rate_per_s> <seed (0 = periodic)> <threshold> <batch> <sched:APP|LCL>
 #include <algorithm>
 #include <atomic>
 #include <chrono>
@@ -299,8 +299,10 @@ static void PrintHp(const char *name, const HpResult &r) {
                 r.lat_us.size(), Pct(r.lat_us, 0.50), Pct(r.lat_us, 0.99), Pct(r.lat_us, 1.0), r.lp_total_ms);
 }
 
-static int Hpf(int64_t level, int lp_count, int64_t lp_us, int hp_count, int64_t hp_us, int64_t hp_gap_us, int64_t th, int64_t bs) {
-    CHECK(XHintSetScheduler(kSchedulerLocal, kPolicyHighestPriorityFirst));
+static int Hpf(int64_t level, int lp_count, int64_t lp_us, int hp_count, int64_t hp_us, int64_t hp_gap_us, int64_t th, int64_t bs,
+               const std::string &sched) {
+    if (sched == "GLB") CHECK(XHintSetScheduler(kSchedulerGlobal, kPolicyUnknown));      // needs a running xserver
+    else CHECK(XHintSetScheduler(kSchedulerLocal, kPolicyHighestPriorityFirst));
     std::vector<int64_t> arrivals;
     for (int i = 0; i < hp_count; ++i) arrivals.push_back((i + 1) * hp_gap_us);
     HpResult r = RunTwoQueues(level, lp_count, lp_us, arrivals, hp_us, th, bs, true);
@@ -320,7 +322,8 @@ static int Config0(int64_t level, int lp_count, int64_t lp_us, int64_t hp_us, do
     std::vector<int64_t> arrivals;
     double t = 0;
     const double horizon_us = (double)lp_count * lp_us * 1.5 + 1e6;
-    while (t < horizon_us) { t += gap(rng) * 1e6; arrivals.push_back((int64_t)t); }
+    // seed 0 selects a fixed period of 1/rate instead of Poisson arrivals
+    while (t < horizon_us) { t += (seed == 0 ? 1.0 / hp_rate : gap(rng)) * 1e6; arrivals.push_back((int64_t)t); }
     // standalone: the same arrivals (first 200 at most) with no low-priority work
     std::vector<int64_t> solo(arrivals.begin(), arrivals.begin() + std::min<size_t>(arrivals.size(), 50));
     for (size_t i = 0; i < solo.size(); ++i) solo[i] = (int64_t)(i + 1) * (hp_us + 3000);
@@ -346,7 +349,7 @@ int main(int argc, char **argv) {
     if (s == "window") return Window(I(2, 4), I(3, 2), (int)I(4, 40), I(5, 300));
     if (s == "suspend") return Suspend(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "drop") return Drop(I(2, 1), (int)I(3, 40), I(4, 500));
-    if (s == "hpf") return Hpf(I(2, 1), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8));
+    if (s == "hpf") return Hpf(I(2, 1), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL");
     if (s == "config0") return Config0(I(2, 1), (int)I(3, 3000), I(4, 1000), I(5, 2000), (double)I(6, 20), (uint64_t)I(7, 42), I(8, 16), I(9, 8),
                                        argc > 10 ? argv[10] : "LCL");
     std::fprintf(stderr, "unknown scenario %s\n", s.c_str());

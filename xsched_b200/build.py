@@ -92,7 +92,7 @@ def build_host(force: bool = False, verbose: bool = False) -> list[Path]:
 
     so("libpreempt.so", ["utils", "sched", "preempt"], ["-ldl", "-lrt"])
     so("libhalhost.so", ["hal_host"], ["-lpreempt"])
-    so("libhalcuda.so", ["hal_cuda"], ["-lpreempt", "-ldl"])
+    so("libhalcuda.so", ["hal_cuda"], ["-lpreempt", "-lxpk", "-ldl"])
     so("libshimcuda.so", ["shim"], ["-lhalcuda", "-lpreempt", "-ldl"],
        extra=["-Wl,-soname,libcuda.so.1"])
 
@@ -123,6 +123,19 @@ def build_oracle(force: bool = False, verbose: bool = False) -> Path:
     src = ORACLE / "kernels_oracle.c"
     if force or _stale(out, [src]):
         _run([CC, "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-o", out, src, "-lm"], verbose)
+    return out
+
+
+def build_bench_worker(force: bool = False, verbose: bool = False) -> Path | None:
+    """xbench_worker — the native workload driver bench.py launches (one process per role)."""
+    src = CSRC / "bench" / "xbench_worker.cu"
+    out = LIB / "xbench_worker"
+    deps = [src, LIB / "libpreempt.so", LIB / "libhalcuda.so", LIB / "libxpk.so"] + _glob(INC, ("*.h",))
+    if not src.exists() or not (LIB / "libhalcuda.so").exists():
+        return None
+    if force or _stale(out, deps):
+        _run([NVCC, "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", f"-I{INC}", "-o", out, src,
+              f"-L{LIB}", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lhalcuda", "-lpreempt", "-lxpk"], verbose)
     return out
 
 
@@ -157,6 +170,7 @@ def build_oracle_ref(force: bool = False, verbose: bool = False) -> Path | None:
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_xpk(force, verbose)
     build_host(force, verbose)
+    build_bench_worker(force, verbose)
     build_oracle(force, verbose)
     build_lane_driver(force, verbose)
     build_oracle_ref(force, verbose)

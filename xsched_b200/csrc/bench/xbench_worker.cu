@@ -1,0 +1,478 @@
+// xbench_worker — native workload driver for the preemption benchmarks.  One process = one role:
+//
+//   --role lp    a low-priority loop of preemptible tasks (gemm | triad | sort) submitted through an
+//                XQueue at the given preemption level until --duration-s elapses (or SIGTERM);
+//   --role hp    a high-priority request every --period-us (vecadd | sort), latency = submit -> wait;
+//   --role both  the two roles as two threads / two XQueues of ONE process (in-process scheduler);
+//   --role preempt-latency
+//                the reference's preemption-latency experiment (platforms/cuda/test/main/level.cu:37-86):
+//                a background thread keeps the queue full while the main thread times
+//                XQueueSuspend(xq, kQueueSuspendFlagSyncHwQueue) / XQueueResume pairs at random moments.
+//
+// Everything goes through the public C ABI (XQueue*, XHint*, CudaQueue*, xpk*).  Results are printed as
+// one JSON line on stdout; "READY" is printed once the role has warmed up.
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cinttypes>
+#include <csignal>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <string>
+#include <thread>
+#include <vector>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include "xsched/xsched.h"
+#include "xsched/cuda/hal.h"
+#include "xsched_b200/pk.h"
+
+#define CK(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { std::fprintf(stderr, "%s -> %s\n", #x, cudaGetErrorString(e_)); std::exit(3); } } while (0)
+#define XK(x) do { XResult r_ = (x); if (r_ != kXSchedSuccess) { std::fprintf(stderr, "%s -> %d\n", #x, (int)r_); std::exit(4); } } while (0)
+#define PK(x) do { xpkResult r_ = (x); if (r_ != XPK_SUCCESS) { std::fprintf(stderr, "%s -> %s\n", #x, xpkResultString(r_)); std::exit(5); } } while (0)
+
+static std::atomic<bool> g_stop{false};
+static void OnTerm(int) { g_stop.store(true); }
+static int64_t NowNs() { return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
+static void SleepUs(int64_t us) { if (us > 0) std::this_thread::sleep_for(std::chrono::microseconds(us)); }
+static double Pct(std::vector<double> v, double p) {
+    if (v.empty()) return 0;
+    std::sort(v.begin(), v.end());
+    return v[std::min(v.size() - 1, (size_t)(p * (v.size() - 1) + 0.5))];
+}
+
+struct Args {
+    std::string role = "lp", kernel = "gemm", hp_kernel = "vecadd";
+    int level = 2, prio = 0, threshold = 16, batch = 8, depth = 8, abort_inflight = 1, count = 500, device = 0, e2e = 0;
+    int M = 8192, N = 8192, K = 8192;
+    uint64_t n = 1ull << 26, hp_n = 1ull << 26, seed = 1;
+    double duration_s = 5, warmup_s = 0.5;
+    int64_t period_us = 10000, kernel_us = 500, laxity_us = -1;
+    int poisson = 0;
+    std::string samples_path;
+};
+
+static Args Parse(int argc, char **argv) {
+    Args a;
+    for (int i = 1; i + 1 < argc; i += 2) {
+        const std::string k = argv[i], v = argv[i + 1];
+        if (k == "--role") a.role = v; else if (k == "--kernel") a.kernel = v; else if (k == "--hp-kernel") a.hp_kernel = v;
+        else if (k == "--level") a.level = std::atoi(v.c_str()); else if (k == "--prio") a.prio = std::atoi(v.c_str());
+        else if (k == "--threshold") a.threshold = std::atoi(v.c_str()); else if (k == "--batch") a.batch = std::atoi(v.c_str());
+        else if (k == "--depth") a.depth = std::atoi(v.c_str()); else if (k == "--abort") a.abort_inflight = std::atoi(v.c_str());
+        else if (k == "--count") a.count = std::atoi(v.c_str()); else if (k == "--device") a.device = std::atoi(v.c_str());
+        else if (k == "--M") a.M = std::atoi(v.c_str()); else if (k == "--N") a.N = std::atoi(v.c_str()); else if (k == "--K") a.K = std::atoi(v.c_str());
+        else if (k == "--n") a.n = std::strtoull(v.c_str(), nullptr, 10); else if (k == "--hp-n") a.hp_n = std::strtoull(v.c_str(), nullptr, 10);
+        else if (k == "--seed") a.seed = std::strtoull(v.c_str(), nullptr, 10);
+        else if (k == "--duration-s") a.duration_s = std::atof(v.c_str()); else if (k == "--warmup-s") a.warmup_s = std::atof(v.c_str());
+        else if (k == "--period-us") a.period_us = std::atoll(v.c_str()); else if (k == "--kernel-us") a.kernel_us = std::atoll(v.c_str());
+        else if (k == "--laxity-us") a.laxity_us = std::atoll(v.c_str());
+        else if (k == "--poisson") a.poisson = std::atoi(v.c_str()); else if (k == "--e2e") a.e2e = std::atoi(v.c_str());
+        else if (k == "--samples") a.samples_path = v;
+        else { std::fprintf(stderr, "unknown option %s\n", k.c_str()); std::exit(2); }
+    }
+    return a;
+}
+
+// ---- deterministic device-side initialisation (synthetic inputs; no host copy of multi-GiB arrays) ----
+__device__ __forceinline__ uint32_t Mix(uint64_t x) {
+    x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;
+    return (uint32_t)x;
+}
+__global__ void FillUniform(float *p, uint64_t n, uint64_t seed) {           // U(-1, 1)
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        p[i] = (float)(Mix(i * 2654435761ull + seed) >> 8) * (2.0f / 16777216.0f) - 1.0f;
+}
+__global__ void FillNormalBf16(__nv_bfloat16 *p, uint64_t n, uint64_t seed, float std) {   // N(0, std) by Box-Muller
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float u1 = ((float)(Mix(i * 2 + seed) >> 8) + 1.0f) * (1.0f / 16777217.0f);
+        const float u2 = (float)(Mix(i * 2 + 1 + seed * 31) >> 8) * (1.0f / 16777216.0f);
+        p[i] = __float2bfloat16(std * sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2));
+    }
+}
+__global__ void FillKeys(int32_t *p, uint64_t n, uint64_t seed) {            // U[0, 2^31)
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        p[i] = (int32_t)(Mix(i + seed * 0x9E3779B97F4A7C15ull) & 0x7FFFFFFFu);
+}
+// Order-sensitive 64-bit checksum of 32-bit words (same formula as the CPU oracle's checksum).
+__global__ void Checksum(const uint32_t *p, uint64_t n, unsigned long long *out) {
+    unsigned long long h = 0;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        h += (unsigned long long)p[i] * ((i & 0xFFFFu) + 1u);
+    for (int o = 16; o; o >>= 1) h += __shfl_down_sync(0xffffffffu, h, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(out, h);
+}
+static unsigned long long DeviceChecksum(const void *p, uint64_t words, cudaStream_t s) {
+    unsigned long long *d, h = 0;
+    CK(cudaMalloc(&d, 8));
+    CK(cudaMemsetAsync(d, 0, 8, s));
+    Checksum<<<592, 256, 0, s>>>((const uint32_t *)p, words, d);
+    CK(cudaMemcpyAsync(&h, d, 8, cudaMemcpyDeviceToHost, s));
+    CK(cudaStreamSynchronize(s));
+    CK(cudaFree(d));
+    return h;
+}
+
+struct Queue {
+    cudaStream_t stream = nullptr;
+    HwQueueHandle hwq = 0;
+    XQueueHandle xq = 0;
+    uint32_t *flag = nullptr;
+};
+static Queue MakeQueue(const Args &a, int level, int prio) {
+    Queue q;
+    CK(cudaStreamCreateWithFlags(&q.stream, cudaStreamNonBlocking));
+    XK(CudaQueueCreate(&q.hwq, (CUstream)q.stream));
+    XK(XQueueCreate(&q.xq, q.hwq, level, kQueueCreateFlagNone));
+    XK(XQueueSetLaunchConfig(q.xq, a.threshold, a.batch));
+    XK(XHintPriority(q.xq, prio));
+    if (a.laxity_us >= 0 && prio > 0) XK(XHintLaxity(q.xq, a.laxity_us, 0, prio));
+    XK(CudaQueueGetPreemptFlag(q.hwq, &q.flag));
+    return q;
+}
+
+// ---- low-priority workload ------------------------------------------------------------------------
+struct LpWork {
+    std::vector<xpkTask_t> tasks;       // `depth` tasks over the same buffers
+    void *out = nullptr;
+    uint64_t out_words = 0;
+    double work_per_iter = 0;           // flop or bytes
+    const char *unit = "";
+    // sort needs its input restored before every iteration
+    int32_t *keys = nullptr, *keys0 = nullptr;
+    uint64_t nkeys = 0;
+};
+
+static LpWork BuildLp(const Args &a, const Queue &q, uint32_t task_flags) {
+    LpWork w;
+    cudaStream_t s = q.stream;
+    if (a.kernel == "gemm") {
+        __nv_bfloat16 *A, *B, *C;
+        CK(cudaMalloc(&A, (size_t)a.M * a.K * 2)); CK(cudaMalloc(&B, (size_t)a.N * a.K * 2)); CK(cudaMalloc(&C, (size_t)a.M * a.N * 2));
+        FillNormalBf16<<<1184, 256, 0, s>>>(A, (uint64_t)a.M * a.K, a.seed, 1.0f);
+        FillNormalBf16<<<1184, 256, 0, s>>>(B, (uint64_t)a.N * a.K, a.seed + 7, 1.0f);
+        CK(cudaStreamSynchronize(s));
+        for (int i = 0; i < a.depth; ++i) {
+            xpkTask_t t;
+            PK(xpkTaskCreateGemm(&t, C, A, B, a.M, a.N, a.K, task_flags | (a.abort_inflight ? XPK_FLAG_ABORT_INFLIGHT : 0), q.flag));
+            w.tasks.push_back(t);
+        }
+        w.out = C; w.out_words = (uint64_t)a.M * a.N / 2;
+        w.work_per_iter = 2.0 * a.M * a.N * a.K; w.unit = "TFLOP/s";
+    } else if (a.kernel == "triad") {
+        float *x, *y, *z;
+        CK(cudaMalloc(&x, a.n * 4)); CK(cudaMalloc(&y, a.n * 4)); CK(cudaMalloc(&z, a.n * 4));
+        FillUniform<<<1184, 256, 0, s>>>(y, a.n, a.seed);
+        FillUniform<<<1184, 256, 0, s>>>(z, a.n, a.seed + 11);
+        CK(cudaStreamSynchronize(s));
+        for (int i = 0; i < a.depth; ++i) {
+            xpkTask_t t;
+            PK(xpkTaskCreateTriad(&t, x, y, z, 1.5f, a.n, 0, task_flags, q.flag));
+            w.tasks.push_back(t);
+        }
+        w.out = x; w.out_words = a.n;
+        w.work_per_iter = 12.0 * a.n; w.unit = "GB/s";
+    } else if (a.kernel == "sort") {
+        int32_t *tmp; void *scratch;
+        CK(cudaMalloc(&w.keys, a.n * 4)); CK(cudaMalloc(&w.keys0, a.n * 4)); CK(cudaMalloc(&tmp, a.n * 4));
+        CK(cudaMalloc(&scratch, xpkSortScratchBytes(a.n)));
+        FillKeys<<<1184, 256, 0, s>>>(w.keys0, a.n, a.seed);
+        CK(cudaStreamSynchronize(s));
+        xpkTask_t t;                     // one task: the scratch area is per task
+        PK(xpkTaskCreateSort(&t, w.keys, tmp, scratch, a.n, task_flags, q.flag));
+        w.tasks.push_back(t);
+        w.nkeys = a.n;
+        w.out = w.keys; w.out_words = a.n;
+        w.work_per_iter = 36.0 * a.n; w.unit = "GB/s";
+    } else {
+        std::fprintf(stderr, "unknown --kernel %s\n", a.kernel.c_str());
+        std::exit(2);
+    }
+    return w;
+}
+
+struct LpResult { uint64_t iters = 0; double seconds = 0, rate = 0; unsigned long long want = 0, got = 0; uint64_t preemptions = 0; CudaQueueStats stats{}; };
+
+static XResult RestoreKeys(HwQueueHandle hwq, void *data) {
+    LpWork *w = (LpWork *)data;
+    return cudaMemcpyAsync(w->keys, w->keys0, w->nkeys * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)(uintptr_t)hwq) == cudaSuccess
+               ? kXSchedSuccess : kXSchedErrorHardware;
+}
+
+static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool> *ready, double duration_s) {
+    LpResult r;
+    // Reference result: one straight run with the flag never raised, outside any XQueue.
+    if (w.keys) CK(cudaMemcpyAsync(w.keys, w.keys0, w.nkeys * 4, cudaMemcpyDeviceToDevice, q.stream));
+    PK(xpkTaskReset(w.tasks[0], q.stream));
+    PK(xpkTaskLaunch(w.tasks[0], q.stream, 0));
+    CK(cudaStreamSynchronize(q.stream));
+    r.want = DeviceChecksum(w.out, w.out_words, q.stream);
+    CK(cudaMemsetAsync(w.out, 0, w.out_words * 4, q.stream));
+    CK(cudaStreamSynchronize(q.stream));
+
+    std::vector<HwCommandHandle> ring(w.tasks.size(), 0);
+    auto submit = [&](size_t slot) {
+        if (w.keys) {                                   // sort: restore the unsorted input first
+            HwCommandHandle c;
+            XK(HwCommandCreateCallback(&c, RestoreKeys, &w));
+            XK(XQueueSubmit(q.xq, c));
+        }
+        HwCommandHandle c;
+        XK(CudaXpkCommandCreate(&c, w.tasks[slot], 1));
+        XK(XQueueSubmit(q.xq, c));
+    };
+    const size_t depth = w.tasks.size();
+    int64_t t_begin = 0;
+    uint64_t submitted = 0, counted_from = 0;
+    const int64_t t_start = NowNs();
+    while (!g_stop.load()) {
+        const double el = (NowNs() - t_start) / 1e9;
+        if (t_begin == 0 && el >= a.warmup_s) {
+            XK(XQueueWaitAll(q.xq));
+            counted_from = submitted;
+            t_begin = NowNs();
+            if (ready) ready->store(true);
+            std::printf("READY\n"); std::fflush(stdout);
+        }
+        if (t_begin && (NowNs() - t_begin) / 1e9 >= duration_s) break;
+        // A task object may be re-submitted only after its previous command completed: with `depth`
+        // tasks in rotation, wait for everything once per rotation.
+        if (submitted && submitted % depth == 0) XK(XQueueWaitAll(q.xq));
+        submit(submitted % depth);
+        ++submitted;
+    }
+    XK(XQueueWaitAll(q.xq));
+    r.seconds = t_begin ? (NowNs() - t_begin) / 1e9 : 0;
+    r.iters = submitted - counted_from;
+    r.rate = r.seconds > 0 ? r.iters * w.work_per_iter / r.seconds : 0;
+    r.got = DeviceChecksum(w.out, w.out_words, q.stream);
+    for (auto t : w.tasks) { xpkTaskInfo info; PK(xpkTaskQuery(t, &info)); r.preemptions += info.preemptions; }
+    CudaQueueGetStats(q.hwq, &r.stats);
+    return r;
+}
+
+static void PrintLp(const Args &a, const LpWork &w, const LpResult &r) {
+    const double scale = std::strcmp(w.unit, "TFLOP/s") == 0 ? 1e12 : 1e9;
+    std::printf("{\"role\": \"lp\", \"kernel\": \"%s\", \"level\": %d, \"iters\": %" PRIu64 ", \"seconds\": %.4f, \"rate\": %.3f, \"unit\": \"%s\", "
+                "\"bit_exact\": %s, \"checksum\": \"%llx\", \"deactivations\": %" PRIu64 ", \"relaunches\": %" PRIu64 ", \"launched\": %" PRIu64 ", "
+                "\"xpk_launches\": %" PRIu64 "}\n",
+                a.kernel.c_str(), a.level, r.iters, r.seconds, r.rate / scale, w.unit, r.want == r.got ? "true" : "false", r.got,
+                (uint64_t)r.stats.deactivations, (uint64_t)r.stats.relaunches, (uint64_t)r.stats.launched, (uint64_t)xpkLaunchCount());
+    std::fflush(stdout);
+}
+
+// ---- high-priority workload -----------------------------------------------------------------------
+struct HpWork {
+    xpkTask_t task = nullptr;
+    float *a = nullptr, *b = nullptr, *c = nullptr, *ha = nullptr, *hb = nullptr, *hc = nullptr;
+    int32_t *keys = nullptr, *keys0 = nullptr;
+    uint64_t n = 0;
+    bool e2e = false;
+    cudaStream_t stream = nullptr;
+    double bytes_algo = 0;
+};
+
+static XResult HpCopyIn(HwQueueHandle hwq, void *data) {
+    HpWork *w = (HpWork *)data;
+    cudaStream_t s = (cudaStream_t)(uintptr_t)hwq;
+    if (w->keys) return cudaMemcpyAsync(w->keys, w->keys0, w->n * 4, cudaMemcpyDeviceToDevice, s) == cudaSuccess ? kXSchedSuccess : kXSchedErrorHardware;
+    if (cudaMemcpyAsync(w->a, w->ha, w->n * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) return kXSchedErrorHardware;
+    if (cudaMemcpyAsync(w->b, w->hb, w->n * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) return kXSchedErrorHardware;
+    return kXSchedSuccess;
+}
+static XResult HpCopyOut(HwQueueHandle hwq, void *data) {
+    HpWork *w = (HpWork *)data;
+    return cudaMemcpyAsync(w->hc, w->c, w->n * 4, cudaMemcpyDeviceToHost, (cudaStream_t)(uintptr_t)hwq) == cudaSuccess ? kXSchedSuccess : kXSchedErrorHardware;
+}
+
+static HpWork BuildHp(const Args &a, const Queue &q) {
+    HpWork w;
+    w.n = a.hp_n; w.e2e = a.e2e != 0; w.stream = q.stream;
+    if (a.hp_kernel == "vecadd") {
+        CK(cudaMalloc(&w.a, w.n * 4)); CK(cudaMalloc(&w.b, w.n * 4)); CK(cudaMalloc(&w.c, w.n * 4));
+        FillUniform<<<1184, 256, 0, q.stream>>>(w.a, w.n, a.seed + 100);
+        FillUniform<<<1184, 256, 0, q.stream>>>(w.b, w.n, a.seed + 101);
+        if (w.e2e) {
+            CK(cudaMallocHost(&w.ha, w.n * 4)); CK(cudaMallocHost(&w.hb, w.n * 4)); CK(cudaMallocHost(&w.hc, w.n * 4));
+            CK(cudaMemcpyAsync(w.ha, w.a, w.n * 4, cudaMemcpyDeviceToHost, q.stream));
+            CK(cudaMemcpyAsync(w.hb, w.b, w.n * 4, cudaMemcpyDeviceToHost, q.stream));
+        }
+        CK(cudaStreamSynchronize(q.stream));
+        // The high-priority kernel is the non-preemptible form: nothing ever needs to stop it.
+        PK(xpkTaskCreateVecAdd(&w.task, w.c, w.a, w.b, w.n, 0, XPK_FLAG_NON_PREEMPTIBLE, nullptr));
+        w.bytes_algo = 12.0 * w.n;
+    } else if (a.hp_kernel == "sort") {
+        int32_t *tmp; void *scratch;
+        CK(cudaMalloc(&w.keys, w.n * 4)); CK(cudaMalloc(&w.keys0, w.n * 4)); CK(cudaMalloc(&tmp, w.n * 4));
+        CK(cudaMalloc(&scratch, xpkSortScratchBytes(w.n)));
+        FillKeys<<<1184, 256, 0, q.stream>>>(w.keys0, w.n, a.seed + 5);
+        CK(cudaStreamSynchronize(q.stream));
+        PK(xpkTaskCreateSort(&w.task, w.keys, tmp, scratch, w.n, XPK_FLAG_NON_PREEMPTIBLE, nullptr));
+        w.bytes_algo = 36.0 * w.n;
+    } else {
+        std::fprintf(stderr, "unknown --hp-kernel %s\n", a.hp_kernel.c_str());
+        std::exit(2);
+    }
+    return w;
+}
+
+static double HpOnce(const Queue &q, HpWork &w) {
+    const int64_t t0 = NowNs();
+    HwCommandHandle c;
+    if (w.e2e || w.keys) { XK(HwCommandCreateCallback(&c, HpCopyIn, &w)); XK(XQueueSubmit(q.xq, c)); }
+    XK(CudaXpkCommandCreate(&c, w.task, 1));
+    XK(XQueueSubmit(q.xq, c));
+    if (w.e2e && !w.keys) { XK(HwCommandCreateCallback(&c, HpCopyOut, &w)); XK(XQueueSubmit(q.xq, c)); }
+    XK(XQueueWaitAll(q.xq));
+    return (NowNs() - t0) / 1e3;
+}
+
+struct HpResult { std::vector<double> lat_us; double seconds = 0; };
+
+static HpResult RunHp(const Args &a, const Queue &q, HpWork &w, int count, std::atomic<bool> *stop_early) {
+    HpResult r;
+    for (int i = 0; i < 5; ++i) HpOnce(q, w);                 // warm-up
+    std::mt19937_64 rng(a.seed);
+    std::exponential_distribution<double> gap(1e6 / (double)a.period_us);
+    const int64_t t_begin = NowNs();
+    int64_t next = t_begin;
+    for (int i = 0; i < count && !g_stop.load() && !(stop_early && stop_early->load()); ++i) {
+        next += a.poisson ? (int64_t)(gap(rng) * 1e9) : a.period_us * 1000;
+        while (NowNs() < next) {
+            const int64_t left = next - NowNs();
+            if (left > 200000) SleepUs(left / 2000); else std::this_thread::yield();
+        }
+        r.lat_us.push_back(HpOnce(q, w));
+        if (NowNs() > next + a.period_us * 1000) next = NowNs();      // overrun: do not accumulate a backlog
+    }
+    r.seconds = (NowNs() - t_begin) / 1e9;
+    return r;
+}
+
+static void PrintHp(const Args &a, const HpWork &w, const HpResult &r, bool verify_ok) {
+    std::printf("{\"role\": \"hp\", \"kernel\": \"%s\", \"n\": %zu, \"e2e\": %d, \"p50_us\": %.2f, \"p90_us\": %.2f, \"p99_us\": %.2f, \"max_us\": %.2f, "
+                "\"mean_us\": %.2f, \"seconds\": %.3f, \"verified\": %s, \"h2d_bytes\": %.0f, \"d2h_bytes\": %.0f, \"xpk_launches\": %" PRIu64 "}\n",
+                a.hp_kernel.c_str(), r.lat_us.size(), a.e2e, Pct(r.lat_us, 0.5), Pct(r.lat_us, 0.9), Pct(r.lat_us, 0.99), Pct(r.lat_us, 1.0),
+                r.lat_us.empty() ? 0.0 : std::accumulate(r.lat_us.begin(), r.lat_us.end(), 0.0) / r.lat_us.size(), r.seconds,
+                verify_ok ? "true" : "false", (w.e2e && !w.keys) ? 8.0 * w.n : 0.0, (w.e2e && !w.keys) ? 4.0 * w.n : 0.0, (uint64_t)xpkLaunchCount());
+    std::fflush(stdout);
+    if (!a.samples_path.empty()) {
+        if (FILE *f = std::fopen(a.samples_path.c_str(), "w")) {
+            for (double v : r.lat_us) std::fprintf(f, "%.2f\n", v);
+            std::fclose(f);
+        }
+    }
+}
+
+static bool VerifyHp(const Queue &q, HpWork &w) {
+    if (w.keys) {               // sorted and same multiset size; exact content is covered by the parity tests
+        std::vector<int32_t> h(std::min<uint64_t>(w.n, 1 << 20));
+        CK(cudaMemcpy(h.data(), w.keys, h.size() * 4, cudaMemcpyDeviceToHost));
+        return std::is_sorted(h.begin(), h.end());
+    }
+    std::vector<float> ha(4096), hb(4096), hc(4096);
+    const uint64_t off = w.n > 8192 ? w.n / 2 : 0;
+    const size_t cnt = (size_t)std::min<uint64_t>(4096, w.n - off);
+    CK(cudaMemcpy(ha.data(), w.a + off, cnt * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(hb.data(), w.b + off, cnt * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(hc.data(), w.c + off, cnt * 4, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < cnt; ++i) if (hc[i] != ha[i] + hb[i]) return false;
+    (void)q;
+    return true;
+}
+
+// ---- preemption latency (reference experiment) ----------------------------------------------------
+static int PreemptLatency(const Args &a) {
+    Queue q = MakeQueue(a, a.level, 0);
+    Args la = a;
+    LpWork w = BuildLp(la, q, 0);
+    std::atomic<bool> stop{false};
+    std::thread bg([&] {
+        size_t i = 0;
+        const size_t depth = w.tasks.size();
+        while (!stop.load()) {
+            if (i && i % depth == 0) XK(XQueueWaitAll(q.xq));
+            HwCommandHandle c;
+            XK(CudaXpkCommandCreate(&c, w.tasks[i % depth], 1));
+            XK(XQueueSubmit(q.xq, c));
+            ++i;
+        }
+        XK(XQueueWaitAll(q.xq));
+    });
+    SleepUs(300000);
+    std::mt19937 rng((unsigned)a.seed);
+    std::vector<double> pre, res;
+    for (int i = 0; i < a.count; ++i) {
+        SleepUs(rng() % 800);
+        int64_t t0 = NowNs();
+        XK(XQueueSuspend(q.xq, kQueueSuspendFlagSyncHwQueue));
+        pre.push_back((NowNs() - t0) / 1e3);
+        SleepUs(800 + rng() % 800);
+        t0 = NowNs();
+        XK(XQueueResume(q.xq, kQueueResumeFlagNone));
+        res.push_back((NowNs() - t0) / 1e3);
+    }
+    stop.store(true);
+    bg.join();
+    const unsigned long long got = DeviceChecksum(w.out, w.out_words, q.stream);
+    PK(xpkTaskReset(w.tasks[0], q.stream));
+    PK(xpkTaskLaunch(w.tasks[0], q.stream, 0));
+    CK(cudaStreamSynchronize(q.stream));
+    const unsigned long long want = DeviceChecksum(w.out, w.out_words, q.stream);
+    CudaQueueStats st{};
+    CudaQueueGetStats(q.hwq, &st);
+    std::printf("{\"role\": \"preempt-latency\", \"kernel\": \"%s\", \"level\": %d, \"abort\": %d, \"n\": %zu, \"preempt_avg_us\": %.2f, \"preempt_p50_us\": %.2f, "
+                "\"preempt_p95_us\": %.2f, \"preempt_p99_us\": %.2f, \"preempt_max_us\": %.2f, \"resume_avg_us\": %.2f, \"resume_p99_us\": %.2f, "
+                "\"bit_exact\": %s, \"deactivations\": %" PRIu64 ", \"relaunches\": %" PRIu64 "}\n",
+                a.kernel.c_str(), a.level, a.abort_inflight, pre.size(), std::accumulate(pre.begin(), pre.end(), 0.0) / std::max<size_t>(1, pre.size()),
+                Pct(pre, 0.5), Pct(pre, 0.95), Pct(pre, 0.99), Pct(pre, 1.0), std::accumulate(res.begin(), res.end(), 0.0) / std::max<size_t>(1, res.size()),
+                Pct(res, 0.99), got == want ? "true" : "false", (uint64_t)st.deactivations, (uint64_t)st.relaunches);
+    return 0;
+}
+
+#include <numeric>
+
+int main(int argc, char **argv) {
+    Args a = Parse(argc, argv);
+    std::signal(SIGTERM, OnTerm);
+    std::signal(SIGINT, OnTerm);
+    CK(cudaSetDevice(a.device));
+    CK(cudaFree(0));
+    if (a.role == "preempt-latency") return PreemptLatency(a);
+    if (a.role == "lp") {
+        Queue q = MakeQueue(a, a.level, a.prio);
+        LpWork w = BuildLp(a, q, 0);
+        LpResult r = RunLp(a, q, w, nullptr, a.duration_s);
+        PrintLp(a, w, r);
+        return r.want == r.got ? 0 : 6;
+    }
+    if (a.role == "hp") {
+        Queue q = MakeQueue(a, a.level, a.prio);
+        HpWork w = BuildHp(a, q);
+        std::printf("READY\n"); std::fflush(stdout);
+        HpResult r = RunHp(a, q, w, a.count, nullptr);
+        PrintHp(a, w, r, VerifyHp(q, w));
+        return 0;
+    }
+    if (a.role == "both") {
+        XK(XHintSetScheduler(kSchedulerLocal, a.laxity_us >= 0 ? kPolicyLaxity : kPolicyHighestPriorityFirst));
+        Queue ql = MakeQueue(a, a.level, 0), qh = MakeQueue(a, a.level, 1);
+        LpWork lw = BuildLp(a, ql, 0);
+        HpWork hw = BuildHp(a, qh);
+        std::atomic<bool> ready{false}, lp_done{false};
+        LpResult lr;
+        std::thread lp([&] { lr = RunLp(a, ql, lw, &ready, a.duration_s); lp_done.store(true); });
+        while (!ready.load()) SleepUs(1000);
+        HpResult hr = RunHp(a, qh, hw, a.count, &lp_done);
+        g_stop.store(true);
+        lp.join();
+        PrintHp(a, hw, hr, VerifyHp(qh, hw));
+        PrintLp(a, lw, lr);
+        return lr.want == lr.got ? 0 : 6;
+    }
+    std::fprintf(stderr, "unknown --role %s\n", a.role.c_str());
+    return 2;
+}

@@ -1,0 +1,142 @@
+#include "hal_cuda/cuda_command.h"
+
+#include <chrono>
+#include <cstring>
+#include <thread>
+#include <immintrin.h>
+#include "hal_cuda/driver.h"
+#include "xsched/utils/xassert.h"
+#include "xsched_b200/pk.h"
+
+namespace xsched::cuda {
+
+void CompletionCounter::Wait(uint64_t ticket) const {
+    // Phase 1: pure spin (a completion is usually microseconds away); phase 2: yield; phase 3: sleep
+    // in short slices so that a long kernel does not burn a core.
+    for (int i = 0; i < 4000; ++i) {
+        if (*host >= ticket) return;
+        _mm_pause();
+    }
+    for (int i = 0; i < 200; ++i) {
+        if (*host >= ticket) return;
+        std::this_thread::yield();
+    }
+    while (*host < ticket) std::this_thread::sleep_for(std::chrono::microseconds(20));
+}
+
+uint64_t CompletionCounter::Issue(CUstream stream, CUresult *res) {
+    std::lock_guard<std::mutex> lk(issue_mu);
+    const uint64_t t = next_ticket.load(std::memory_order_relaxed) + 1;
+    const CUresult r = Driver().cuStreamWriteValue64(stream, dev, t, CU_STREAM_WRITE_VALUE_DEFAULT);
+    if (res) *res = r;
+    if (r != CUDA_SUCCESS) return 0;
+    next_ticket.store(t, std::memory_order_relaxed);
+    return t;
+}
+
+void CudaCommand::Synchronize() {
+    XASSERT(counter_ != nullptr && ticket_.load() != 0, "Synchronize() on a command that was not launched as waitable");
+    counter_->Wait(ticket_.load(std::memory_order_acquire));
+}
+
+CUresult CudaCommand::LaunchOn(CUstream stream, const std::shared_ptr<CompletionCounter> &counter) {
+    CUresult r = Enqueue(stream);
+    if (r != CUDA_SUCCESS) return r;
+    if (want_sync_) {
+        // A relaunch after a flush takes a fresh ticket: the old write already executed behind the
+        // flushed kernel and proves nothing.
+        counter_ = counter;
+        const uint64_t t = counter->Issue(stream, &r);
+        if (t) ticket_.store(t, std::memory_order_release);
+    }
+    return r;
+}
+
+// ------------------------------------------------------------------------------------ kernel launch
+CudaKernelLaunchCommand::CudaKernelLaunchCommand(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by,
+                                                 unsigned bz, unsigned shmem, void **params, void **extra)
+    : CudaCommand(preempt::kCommandPropertyNone), f_(f), g_{gx, gy, gz}, b_{bx, by, bz}, shmem_(shmem) {
+    if (params != nullptr) {
+        // Argument layout comes from the driver: offset and size of parameter i until it says "no more".
+        std::vector<std::pair<size_t, size_t>> layout;
+        size_t total = 0;
+        for (size_t i = 0;; ++i) {
+            size_t off = 0, sz = 0;
+            if (Driver().cuFuncGetParamInfo(f, i, &off, &sz) != CUDA_SUCCESS) break;
+            layout.emplace_back(off, sz);
+            total = std::max(total, off + sz);
+        }
+        arg_bytes_.resize(total);
+        arg_ptrs_.resize(layout.size());
+        for (size_t i = 0; i < layout.size(); ++i) {
+            std::memcpy(arg_bytes_.data() + layout[i].first, params[i], layout[i].second);
+            arg_ptrs_[i] = arg_bytes_.data() + layout[i].first;
+        }
+    } else if (extra != nullptr) {
+        // CU_LAUNCH_PARAM_BUFFER_POINTER / _SIZE / _END triple list.
+        void *buf = nullptr;
+        size_t size = 0;
+        for (int i = 0; extra[i] != CU_LAUNCH_PARAM_END && i < 16; i += 2) {
+            if (extra[i] == CU_LAUNCH_PARAM_BUFFER_POINTER) buf = extra[i + 1];
+            else if (extra[i] == CU_LAUNCH_PARAM_BUFFER_SIZE) size = *(size_t *)extra[i + 1];
+        }
+        if (buf == nullptr) { ok_ = false; return; }
+        extra_bytes_.assign((unsigned char *)buf, (unsigned char *)buf + size);
+        use_extra_ = true;
+    }
+}
+
+CUresult CudaKernelLaunchCommand::Enqueue(CUstream stream) {
+    if (use_extra_) {
+        size_t size = extra_bytes_.size();
+        extra_[0] = CU_LAUNCH_PARAM_BUFFER_POINTER; extra_[1] = extra_bytes_.data();
+        extra_[2] = CU_LAUNCH_PARAM_BUFFER_SIZE;    extra_[3] = &size;
+        extra_[4] = CU_LAUNCH_PARAM_END;
+        return Driver().cuLaunchKernel(f_, g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, stream, nullptr, extra_);
+    }
+    return Driver().cuLaunchKernel(f_, g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, stream,
+                                   arg_ptrs_.empty() ? nullptr : arg_ptrs_.data(), nullptr);
+}
+
+// ------------------------------------------------------------------------------------ copies, sets
+CUresult CudaMemcpyCommand::Enqueue(CUstream stream) {
+    const DriverApi &d = Driver();
+    switch (kind_) {
+    case CopyKind::kHtoD: return d.cuMemcpyHtoDAsync(dst_, (const void *)src_, bytes_, stream);
+    case CopyKind::kDtoH: return d.cuMemcpyDtoHAsync((void *)dst_, src_, bytes_, stream);
+    case CopyKind::kDtoD: return d.cuMemcpyDtoDAsync(dst_, src_, bytes_, stream);
+    default: return d.cuMemcpyAsync(dst_, src_, bytes_, stream);
+    }
+}
+
+CUresult CudaMemsetCommand::Enqueue(CUstream stream) {
+    if (width_ == 1) return Driver().cuMemsetD8Async(dst_, (unsigned char)value_, count_, stream);
+    return Driver().cuMemsetD32Async(dst_, value_, count_, stream);
+}
+
+CUresult CudaEventRecordCommand::Enqueue(CUstream stream) { return Driver().cuEventRecord(ev_, stream); }
+
+void CudaEventWaitCommand::BeforeLaunch() {
+    if (record_) record_->WaitUntil(preempt::kCommandStateInFlight);
+}
+CUresult CudaEventWaitCommand::Enqueue(CUstream stream) { return Driver().cuStreamWaitEvent(stream, ev_, flags_); }
+
+CUresult CudaHostFuncCommand::Enqueue(CUstream stream) { return Driver().cuLaunchHostFunc(stream, fn_, data_); }
+
+// ------------------------------------------------------------------------------------ xpk task
+bool CudaXpkCommand::TaskCompleted() const {
+    xpkTaskInfo info;
+    if (xpkTaskQuery((xpkTask_t)task_, &info) != XPK_SUCCESS) return false;
+    return info.status == XPK_STATUS_COMPLETED;
+}
+
+CUresult CudaXpkCommand::Enqueue(CUstream stream) {
+    xpkTask_t t = (xpkTask_t)task_;
+    if (!launched_once_ && rewind_) {
+        if (xpkTaskReset(t, stream) != XPK_SUCCESS) return CUDA_ERROR_LAUNCH_FAILED;
+    }
+    launched_once_ = true;
+    return xpkTaskLaunch(t, stream, 0) == XPK_SUCCESS ? CUDA_SUCCESS : CUDA_ERROR_LAUNCH_FAILED;
+}
+
+} // namespace xsched::cuda

@@ -1,0 +1,149 @@
+// HwCommands of the CUDA backend.  Completion of a command is observed through a per-queue counter in
+// mapped pinned host memory that the GPU front-end bumps with a 64-bit stream memory write placed
+// right behind the command: waiting for a command is a load loop on a host word, not a driver call.
+// (The reference waits with cuEventSynchronize on pooled blocking events:
+// platforms/cuda/hal/src/common/cuda_command.cpp:39-52, event_pool.cpp:5-43.)
+#pragma once
+#include <atomic>
+#include <cstdint>
+#include <memory>
+#include <mutex>
+#include <vector>
+#include <cuda.h>
+#include "xsched/preempt/hal/hw_command.h"
+
+namespace xsched::cuda {
+
+class CudaQueue;
+
+/// Shared between a queue and its commands: the counter the GPU writes and the ticket dispenser.
+struct CompletionCounter {
+    volatile uint64_t *host = nullptr;     // mapped pinned host word
+    CUdeviceptr dev = 0;                   // its device address
+    std::atomic<uint64_t> next_ticket{0};
+    std::mutex issue_mu;                   // ticket order must equal stream order of the writes
+    /// Take the next ticket and enqueue its write on `stream`; returns the ticket (0 on failure).
+    uint64_t Issue(CUstream stream, CUresult *res);
+    /// Spin briefly, then back off, until *host >= ticket.
+    void Wait(uint64_t ticket) const;
+};
+
+class CudaCommand : public preempt::HwCommand {
+public:
+    explicit CudaCommand(preempt::XCommandProperties props) : HwCommand(props) {}
+    ~CudaCommand() override = default;
+
+    void Synchronize() override;
+    bool Synchronizable() override { return want_sync_; }
+    bool EnableSynchronization() override { want_sync_ = true; return true; }
+
+    /// Enqueue the work on `stream`, then (if waitable) the counter write that marks its completion.
+    CUresult LaunchOn(CUstream stream, const std::shared_ptr<CompletionCounter> &counter);
+
+protected:
+    virtual CUresult Enqueue(CUstream stream) = 0;
+
+private:
+    bool want_sync_ = false;
+    std::shared_ptr<CompletionCounter> counter_;
+    std::atomic<uint64_t> ticket_{0};      // 0 = not issued yet
+};
+
+/// cuLaunchKernel with a private copy of the argument block (the caller's argument array is only
+/// valid during the call that was intercepted).  Not deactivatable: an arbitrary kernel cannot be
+/// stopped cooperatively.
+class CudaKernelLaunchCommand final : public CudaCommand {
+public:
+    CudaKernelLaunchCommand(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
+                            unsigned shmem, void **params, void **extra);
+    bool ParamsCopied() const { return ok_; }
+protected:
+    CUresult Enqueue(CUstream stream) override;
+private:
+    CUfunction f_;
+    unsigned g_[3], b_[3], shmem_;
+    std::vector<unsigned char> arg_bytes_;
+    std::vector<void *> arg_ptrs_;
+    std::vector<unsigned char> extra_bytes_;
+    void *extra_[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool use_extra_ = false;
+    bool ok_ = true;
+};
+
+enum class CopyKind { kHtoD, kDtoH, kDtoD, kGeneric };
+class CudaMemcpyCommand final : public CudaCommand {
+public:
+    CudaMemcpyCommand(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t bytes)
+        : CudaCommand(preempt::kCommandPropertyNone), kind_(kind), dst_(dst), src_(src), bytes_(bytes) {}
+protected:
+    CUresult Enqueue(CUstream stream) override;
+private:
+    CopyKind kind_;
+    CUdeviceptr dst_, src_;
+    size_t bytes_;
+};
+
+class CudaMemsetCommand final : public CudaCommand {
+public:
+    CudaMemsetCommand(CUdeviceptr dst, unsigned value, size_t count, int width)
+        : CudaCommand(preempt::kCommandPropertyNone), dst_(dst), value_(value), count_(count), width_(width) {}
+protected:
+    CUresult Enqueue(CUstream stream) override;
+private:
+    CUdeviceptr dst_;
+    unsigned value_;
+    size_t count_;
+    int width_;
+};
+
+/// cuEventRecord: re-executable, always individually waitable.
+class CudaEventRecordCommand final : public CudaCommand {
+public:
+    explicit CudaEventRecordCommand(CUevent ev) : CudaCommand(preempt::kCommandPropertyIdempotent), ev_(ev) { EnableSynchronization(); }
+protected:
+    CUresult Enqueue(CUstream stream) override;
+private:
+    CUevent ev_;
+};
+
+/// cuStreamWaitEvent: before it is launched, the command that records the event must have been
+/// launched (it may sit in another XQueue's pending list).
+class CudaEventWaitCommand final : public CudaCommand {
+public:
+    CudaEventWaitCommand(CUevent ev, unsigned flags, std::shared_ptr<preempt::HwCommand> record_cmd)
+        : CudaCommand(preempt::kCommandPropertyIdempotent), ev_(ev), flags_(flags), record_(std::move(record_cmd)) {}
+    void BeforeLaunch() override;
+protected:
+    CUresult Enqueue(CUstream stream) override;
+private:
+    CUevent ev_;
+    unsigned flags_;
+    std::shared_ptr<preempt::HwCommand> record_;
+};
+
+class CudaHostFuncCommand final : public CudaCommand {
+public:
+    CudaHostFuncCommand(CUhostFn fn, void *data) : CudaCommand(preempt::kCommandPropertyNone), fn_(fn), data_(data) {}
+protected:
+    CUresult Enqueue(CUstream stream) override;
+private:
+    CUhostFn fn_;
+    void *data_;
+};
+
+/// A task of the preemptible-kernel library: the deactivatable command of this backend.
+class CudaXpkCommand final : public CudaCommand {
+public:
+    CudaXpkCommand(void *task, bool rewind) : CudaCommand(preempt::kCommandPropertyDeactivatable), task_(task), rewind_(rewind) {}
+    /// Completed on the device (valid once the stream has drained).
+    bool TaskCompleted() const;
+    void *Task() const { return task_; }
+protected:
+    CUresult Enqueue(CUstream stream) override;
+private:
+    void *task_;
+    bool rewind_;
+    bool launched_once_ = false;
+};
+
+} // namespace xsched::cuda

@@ -1,0 +1,179 @@
+// CUDA HwQueue.
+//   Level 1  Launch = enqueue on the stream (+ completion-counter write when waitable);
+//            Synchronize = take a ticket, write it behind everything, wait for it on the host word.
+//   Level 2  Deactivate = raise the queue's preempt flag (one 32-bit stream memory write on a separate
+//            high-priority stream): running xpk kernels stop at their next tile boundary, xpk kernels
+//            queued behind them start, see the flag and return at once.  Reactivate = wait for the
+//            stream to drain, lower the flag, relaunch from the first unfinished xpk command on; each
+//            xpk task continues from its tile cursor.
+// Contract: preempt/include/xsched/preempt/hal/hw_queue.h:19-77 (reference); the level-1 behaviour
+// corresponds to platforms/cuda/hal/src/level1/cuda_queue.cpp:15-98 and the level-2 flush/replay to
+// platforms/cuda/hal/src/level2/cuda_queue.cpp:8-72 + instrument.cpp:181-222.
+#include <chrono>
+#include <mutex>
+#include "hal_cuda/cuda_command.h"
+#include "hal_cuda/driver.h"
+#include "xsched/cuda/hal.h"
+#include "xsched/preempt/hal/hw_queue.h"
+#include "xsched/preempt/xqueue/xqueue.h"
+#include "xsched/protocol/names.h"
+#include "xsched/utils/xassert.h"
+
+namespace xsched::cuda {
+
+using namespace xsched::preempt;
+
+static int64_t NowNs() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+class CudaQueue final : public HwQueue {
+public:
+    explicit CudaQueue(CUstream stream) : stream_(stream) {
+        const DriverApi &d = Driver();
+        CUcontext cur = nullptr, sctx = nullptr;
+        CUDA_ASSERT(d.cuCtxGetCurrent(&cur));
+        CUDA_ASSERT(d.cuStreamGetCtx(stream, &sctx));
+        XASSERT(cur == sctx, "CudaQueueCreate: the current context (%p) is not the stream's context (%p)", (void *)cur, (void *)sctx);
+        ctx_ = sctx;
+        CUdevice dev;
+        CUDA_ASSERT(d.cuCtxGetDevice(&dev));
+        int dom = 0, bus = 0, devid = 0;
+        CUDA_ASSERT(d.cuDeviceGetAttribute(&dom, CU_DEVICE_ATTRIBUTE_PCI_DOMAIN_ID, dev));
+        CUDA_ASSERT(d.cuDeviceGetAttribute(&bus, CU_DEVICE_ATTRIBUTE_PCI_BUS_ID, dev));
+        CUDA_ASSERT(d.cuDeviceGetAttribute(&devid, CU_DEVICE_ATTRIBUTE_PCI_DEVICE_ID, dev));
+        xdevice_ = protocol::MakeDevice(kDeviceTypeGPU, protocol::MakePciId((uint32_t)dom, (uint32_t)bus, (uint32_t)devid, 0));
+
+        counter_ = std::make_shared<CompletionCounter>();
+        void *host = nullptr;
+        CUDA_ASSERT(d.cuMemHostAlloc(&host, 64, CU_MEMHOSTALLOC_DEVICEMAP | CU_MEMHOSTALLOC_PORTABLE));
+        *(volatile uint64_t *)host = 0;
+        counter_->host = (volatile uint64_t *)host;
+        CUDA_ASSERT(d.cuMemHostGetDevicePointer(&counter_->dev, host, 0));
+
+        CUDA_ASSERT(d.cuMemAlloc(&flag_, 256));
+        CUDA_ASSERT(d.cuMemsetD32(flag_, 0, 64));
+        int lo = 0, hi = 0;
+        CUDA_ASSERT(d.cuCtxGetStreamPriorityRange(&lo, &hi));
+        CUDA_ASSERT(d.cuStreamCreateWithPriority(&ctrl_, CU_STREAM_NON_BLOCKING, hi));
+        CUDA_ASSERT(d.cuStreamSynchronize(stream_));     // nothing may be running on the stream yet
+    }
+    ~CudaQueue() override {
+        const DriverApi &d = Driver();
+        d.cuStreamDestroy(ctrl_);
+        d.cuMemFree(flag_);
+        d.cuMemFreeHost((void *)counter_->host);
+    }
+
+    void Launch(std::shared_ptr<HwCommand> hw_cmd) override {
+        auto c = std::dynamic_pointer_cast<CudaCommand>(hw_cmd);
+        XASSERT(c != nullptr, "a command that is not a CudaCommand was submitted to a CUDA queue");
+        CUDA_ASSERT(c->LaunchOn(stream_, counter_));
+        stats_.launched.fetch_add(1, std::memory_order_relaxed);
+    }
+
+    void Synchronize() override {
+        CUresult r = CUDA_SUCCESS;
+        const uint64_t t = counter_->Issue(stream_, &r);
+        CUDA_ASSERT(r);
+        counter_->Wait(t);
+        const int64_t t0 = deactivate_ns_.exchange(0);
+        if (t0) stats_.last_preempt_ns.store((uint64_t)(NowNs() - t0));
+    }
+
+    void Deactivate() override {
+        deactivate_ns_.store(NowNs());
+        CUDA_ASSERT(Driver().cuStreamWriteValue32(ctrl_, flag_, 1, CU_STREAM_WRITE_VALUE_DEFAULT));
+        stats_.deactivations.fetch_add(1, std::memory_order_relaxed);
+    }
+
+    void Reactivate(const CommandLog &log) override {
+        const DriverApi &d = Driver();
+        CUDA_ASSERT(d.cuStreamSynchronize(stream_));      // flushed kernels have published their cursors
+        CUDA_ASSERT(d.cuStreamWriteValue32(ctrl_, flag_, 0, CU_STREAM_WRITE_VALUE_DEFAULT));
+        CUDA_ASSERT(d.cuStreamSynchronize(ctrl_));        // the flag is down before anything relaunches
+        bool replay = false;
+        for (const auto &hc : log) {
+            auto c = std::dynamic_pointer_cast<CudaCommand>(hc);
+            if (!c) continue;
+            auto x = std::dynamic_pointer_cast<CudaXpkCommand>(c);
+            if (!replay) {
+                if (!x || x->TaskCompleted()) continue;   // finished before the flush
+                replay = true;                            // first unfinished preemptible command
+            } else if (x && x->TaskCompleted()) {
+                continue;
+            }
+            CUDA_ASSERT(c->LaunchOn(stream_, counter_));
+            stats_.relaunches.fetch_add(1, std::memory_order_relaxed);
+        }
+    }
+
+    XDevice GetDevice() override { return xdevice_; }
+    HwQueueHandle GetHandle() override { return (HwQueueHandle)(uintptr_t)stream_; }
+    bool SupportDynamicLevel() override { return true; }
+    XPreemptLevel GetMaxSupportedLevel() override { return kPreemptLevelDeactivate; }
+    void OnXQueueCreate() override { CUDA_ASSERT(Driver().cuCtxSetCurrent(ctx_)); }
+
+    CUdeviceptr Flag() const { return flag_; }
+    CUstream Stream() const { return stream_; }
+    void FillStats(CudaQueueStats *s) const {
+        s->launched = stats_.launched.load(); s->completed = *counter_->host; s->window_stalls = 0;
+        s->deactivations = stats_.deactivations.load(); s->relaunches = stats_.relaunches.load();
+        s->last_preempt_ns = stats_.last_preempt_ns.load();
+    }
+
+private:
+    CUstream stream_;
+    CUcontext ctx_ = nullptr;
+    XDevice xdevice_ = 0;
+    std::shared_ptr<CompletionCounter> counter_;
+    CUdeviceptr flag_ = 0;
+    CUstream ctrl_ = nullptr;
+    std::atomic<int64_t> deactivate_ns_{0};
+    struct { std::atomic<uint64_t> launched{0}, deactivations{0}, relaunches{0}, last_preempt_ns{0}; } stats_;
+};
+
+} // namespace xsched::cuda
+
+using namespace xsched::cuda;
+using namespace xsched::preempt;
+
+static inline HwQueueHandle HandleOf(CUstream s) { return (HwQueueHandle)(uintptr_t)s; }
+
+EXPORT_C_FUNC XResult CudaQueueCreate(HwQueueHandle *hwq, CUstream stream) {
+    if (hwq == nullptr) return kXSchedErrorInvalidValue;
+    if (stream == nullptr) { XWARN("CudaQueueCreate: the default stream is not supported"); return kXSchedErrorNotSupported; }
+    const XResult r = HwQueueManager::Add(HandleOf(stream), [&]() -> std::shared_ptr<HwQueue> { return std::make_shared<CudaQueue>(stream); });
+    if (r == kXSchedSuccess) *hwq = HandleOf(stream);
+    return r;
+}
+
+EXPORT_C_FUNC XResult CudaQueueGet(HwQueueHandle *hwq, CUstream stream) {
+    if (hwq == nullptr) return kXSchedErrorInvalidValue;
+    if (stream == nullptr) return kXSchedErrorNotSupported;
+    if (HwQueueManager::Get(HandleOf(stream)) == nullptr) return kXSchedErrorNotFound;
+    *hwq = HandleOf(stream);
+    return kXSchedSuccess;
+}
+
+EXPORT_C_FUNC XResult CudaQueueGetPreemptFlag(HwQueueHandle hwq, uint32_t **flag_dev) {
+    if (flag_dev == nullptr) return kXSchedErrorInvalidValue;
+    auto q = std::dynamic_pointer_cast<CudaQueue>(HwQueueManager::Get(hwq));
+    if (!q) return kXSchedErrorNotFound;
+    *flag_dev = (uint32_t *)(uintptr_t)q->Flag();
+    return kXSchedSuccess;
+}
+
+EXPORT_C_FUNC XResult CudaXpkCommandCreate(HwCommandHandle *hw_cmd, void *xpk_task, int rewind) {
+    if (hw_cmd == nullptr || xpk_task == nullptr) return kXSchedErrorInvalidValue;
+    *hw_cmd = HwCommandManager::Add(std::make_shared<CudaXpkCommand>(xpk_task, rewind != 0));
+    return kXSchedSuccess;
+}
+
+EXPORT_C_FUNC XResult CudaQueueGetStats(HwQueueHandle hwq, CudaQueueStats *stats) {
+    if (stats == nullptr) return kXSchedErrorInvalidValue;
+    auto q = std::dynamic_pointer_cast<CudaQueue>(HwQueueManager::Get(hwq));
+    if (!q) return kXSchedErrorNotFound;
+    q->FillStats(stats);
+    return kXSchedSuccess;
+}
