@@ -61,13 +61,13 @@ class ClockSampler(threading.Thread):
         self.samples: list[int] = []
         self.max_mhz = 0
         self.reasons: set[str] = set()
-        self._stop = threading.Event()
+        self._halt = threading.Event()
 
     def run(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        while not self._stop.is_set():
+        while not self._halt.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={q}", "--format=csv,noheader,nounits"],
                                      capture_output=True, text=True, timeout=5).stdout.strip().split(",")
@@ -78,10 +78,10 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(n)
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._halt.wait(0.2)
 
     def stop(self) -> dict:
-        self._stop.set()
+        self._halt.set()
         self.join(timeout=6)
         s = sorted(self.samples)
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz or None, "reasons": sorted(self.reasons),
@@ -103,7 +103,7 @@ def run_json(cmd: list[str], env: dict, timeout: float) -> list[dict]:
 
 
 def base_env(ns: str, sched: str | None) -> dict:
-    env = dict(os.environ, XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns)
+    env = dict(os.environ, XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns, XSCHED_IPC_SPIN="ON")
     env.pop("XSCHED_POLICY", None)
     if sched:
         env["XSCHED_SCHEDULER"] = sched
@@ -250,7 +250,7 @@ def main() -> None:
     rank, world, local, pg = dist_ctx()
     device = local
     ns = f"bench{os.environ.get('MASTER_PORT', os.getpid())}."
-    lp_kw = dict(kernel="gemm", abort=1, depth=8, **GEMM)
+    lp_kw = dict(kernel="gemm", abort=1, depth=3, threshold=2, batch=1, **GEMM)
     launches = 0
 
     server = None
@@ -266,8 +266,9 @@ def main() -> None:
         hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(100, args.steps // 2), period_us=PERIOD_US, hp_n=HP_N), env_alone, 300)[-1]
         lp_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **lp_kw), env_alone, 300)[-1]
         launches += hp_alone["xpk_launches"] + lp_alone["xpk_launches"]
-        lat = run_json(worker_cmd("preempt-latency", device, level=2, count=300, abort=1, depth=8, kernel="gemm", **GEMM), env_alone, 300)[-1]
+        lat = run_json(worker_cmd("preempt-latency", device, level=2, count=300, **lp_kw), env_alone, 300)[-1]
         roof, roof_launches = gemm_roofline(device)
+        print(f"[bench] standalone hp={hp_alone} lp={lp_alone} lat={lat} roof={roof}", file=sys.stderr, flush=True)
         launches += roof_launches
 
         # ---- timed region: K high-priority steps against the running low-priority loop ----
@@ -279,6 +280,7 @@ def main() -> None:
         hp_co, lp_co = corun(device, ns, 2, args.steps, args.warmup, False, PERIOD_US, lp_kw)
         elapsed = time.time() - t0
         clocks = sampler.stop()
+        print(f"[bench] corun hp={hp_co} lp={lp_co}", file=sys.stderr, flush=True)
         launches += hp_co["xpk_launches"] + lp_co["xpk_launches"]
         if pg:
             pg.barrier()
@@ -333,7 +335,7 @@ def main() -> None:
         "warmup": args.warmup, "ms_per_step": round(max(r["elapsed"] for r in allr) * 1e3 / (args.steps + args.warmup), 3),
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate) LP GEMM; f32 HP vector add",
         "data": "synthetic", "impl": "ours",
-        "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "processes_per_gpu": 2, "preempt_level": 2, "hp_period_us": PERIOD_US,
+        "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "processes_per_gpu": 2, "preempt_level": 2, "lp_window": "threshold 2 / batch 1", "ipc": "polling receivers (XSCHED_IPC_SPIN=ON)", "hp_period_us": PERIOD_US,
                    "lp": "persistent preemptible bf16 GEMM 8192^3 in a loop", "hp": "fp32 vector add, 64 Mi elements",
                    "l2": "LP operands+output 384 MiB and HP arrays 768 MiB both exceed the 126 MB L2 (no flush needed)", "xserver": 1},
         "hp_p99_us": round(worst["hp_p99"], 2), "hp_standalone_p99_us": round(worst["alone_p99"], 2),

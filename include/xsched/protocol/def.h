@@ -57,3 +57,6 @@
 #define XSCHED_POLICY_SCOPE_ENV_NAME      "XSCHED_POLICY_SCOPE"     // GLOBAL | DEVICE
 // Namespace prefix of the rendezvous sockets, so that several servers can share one host.
 #define XSCHED_IPC_NAMESPACE_ENV_NAME     "XSCHED_IPC_NAMESPACE"
+// ON: the receivers of the agent <-> server channel poll instead of sleeping (one busy core per receiver,
+// a few microseconds per hop instead of a thread wake-up).  Default OFF.
+#define XSCHED_IPC_SPIN_ENV_NAME          "XSCHED_IPC_SPIN"

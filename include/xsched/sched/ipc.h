@@ -21,6 +21,12 @@ public:
     bool SendTo(uint64_t key, const void *data, size_t size);
     /// Blocks.  Returns bytes received, 0 after Close(), -1 on error.
     long Receive(void *buf, size_t cap);
+    /// Non-blocking: bytes received, -2 when nothing is queued, 0 after Close(), -1 on error.  A thread
+    /// that polls this in a loop sees a record a few microseconds after it was sent, instead of after a
+    /// scheduler wake-up; XSCHED_IPC_SPIN=ON selects that mode for the agent's and the server's receivers.
+    long TryReceive(void *buf, size_t cap);
+    /// Receive with the mode chosen by XSCHED_IPC_SPIN (spinning TryReceive or blocking Receive).
+    long ReceiveAuto(void *buf, size_t cap);
     void Close();                                  // wakes a blocked Receive
     bool Ok() const { return fd_ >= 0; }
 private:

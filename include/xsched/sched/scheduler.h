@@ -66,6 +66,12 @@ public:
     void WaitAllOperations();
     uint64_t Rounds() const { return rounds_.load(); }
 
+    /// Threadless operation (used by the server's polling loop instead of Run()): apply `n` events and
+    /// run one policy round on the calling thread.  With n == 0 only due timers are served.
+    void StepInline(const Event *events, size_t n);
+    /// Earliest pending policy timer (epoch us), or INT64_MAX.
+    int64_t NextTimerUs() const;
+
 private:
     void Worker();
     void Apply(const Event &e);

@@ -24,6 +24,7 @@
 #include <thread>
 #include <vector>
 #include <cuda_runtime.h>
+#include <sys/prctl.h>
 #include <cuda_bf16.h>
 
 #include "xsched/xsched.h"
@@ -225,6 +226,20 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
         XK(XQueueSubmit(q.xq, c));
     };
     const size_t depth = w.tasks.size();
+    std::vector<uint64_t> uses(depth, 0);
+    // A task object may be re-submitted only after its previous command completed.  That is read from
+    // the task's mailbox (no queue drain): the slot's k-th command is done once the task has been
+    // launched at least k times and its newest launch reports COMPLETED.
+    auto wait_slot = [&](size_t slot) {
+        if (uses[slot] == 0) return;
+        while (!g_stop.load()) {
+            xpkTaskInfo info;
+            PK(xpkTaskQuery(w.tasks[slot], &info));
+            if (info.launches >= uses[slot] && info.status == XPK_STATUS_COMPLETED) return;
+            if (info.status == XPK_STATUS_ERROR) { std::fprintf(stderr, "task error %#x\n", info.error); std::exit(7); }
+            SleepUs(20);
+        }
+    };
     int64_t t_begin = 0;
     uint64_t submitted = 0, counted_from = 0;
     const int64_t t_start = NowNs();
@@ -238,10 +253,11 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
             std::printf("READY\n"); std::fflush(stdout);
         }
         if (t_begin && (NowNs() - t_begin) / 1e9 >= duration_s) break;
-        // A task object may be re-submitted only after its previous command completed: with `depth`
-        // tasks in rotation, wait for everything once per rotation.
-        if (submitted && submitted % depth == 0) XK(XQueueWaitAll(q.xq));
-        submit(submitted % depth);
+        const size_t slot = submitted % depth;
+        wait_slot(slot);
+        if (g_stop.load()) break;
+        submit(slot);
+        ++uses[slot];
         ++submitted;
     }
     XK(XQueueWaitAll(q.xq));
@@ -441,6 +457,7 @@ int main(int argc, char **argv) {
     std::signal(SIGINT, OnTerm);
     CK(cudaSetDevice(a.device));
     CK(cudaFree(0));
+    prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);
     if (a.role == "preempt-latency") return PreemptLatency(a);
     if (a.role == "lp") {
         Queue q = MakeQueue(a, a.level, a.prio);

@@ -11,13 +11,18 @@
 namespace xsched::cuda {
 
 void CompletionCounter::Wait(uint64_t ticket) const {
-    // Phase 1: pure spin (a completion is usually microseconds away); phase 2: yield; phase 3: sleep
-    // in short slices so that a long kernel does not burn a core.
-    for (int i = 0; i < 4000; ++i) {
-        if (*host >= ticket) return;
-        _mm_pause();
+    // Phase 1: spin with pause for ~100 us (a completion is usually that close); phase 2: yield the core
+    // between looks for up to ~2 ms; phase 3: sleep in 20 us slices so a long kernel does not burn a core.
+    const auto t0 = std::chrono::steady_clock::now();
+    auto elapsed_us = [&] { return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count(); };
+    while (true) {
+        for (int i = 0; i < 64; ++i) {
+            if (*host >= ticket) return;
+            _mm_pause();
+        }
+        if (elapsed_us() > 100) break;
     }
-    for (int i = 0; i < 200; ++i) {
+    while (elapsed_us() < 2000) {
         if (*host >= ticket) return;
         std::this_thread::yield();
     }

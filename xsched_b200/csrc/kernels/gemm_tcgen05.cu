@@ -180,6 +180,18 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
     const unsigned long long total_tiles = (unsigned long long)m_tiles * n_tiles;
     volatile uint32_t *v_abort = &sh->abort;
 
+    if constexpr (kPreemptible) {
+        // A kernel that starts with the flag already raised (it was queued behind the one being flushed)
+        // leaves before setting up barriers or tensor memory, so a flush of several queued launches costs
+        // little more than their launch overhead.
+        __shared__ uint32_t s_stop;
+        if (threadIdx.x == 0) s_stop = ld_flag(ctl->flag);
+        __syncthreads();
+        if (s_stop != 0) {
+            if (threadIdx.x == 0) cta_exit(ctl, 0, launch_no);
+            return;
+        }
+    }
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
         for (int i = 0; i < kAccBufs; ++i) { mbar_init(&sh->tmem_full[i], 1); mbar_init(&sh->tmem_empty[i], 4); }

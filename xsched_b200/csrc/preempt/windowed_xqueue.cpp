@@ -1,5 +1,7 @@
 #include "preempt/windowed_xqueue.h"
 
+#include <sys/prctl.h>
+
 #include "xsched/preempt/sched/agent.h"
 #include "xsched/sched/wire.h"
 #include "xsched/utils/xassert.h"
@@ -20,6 +22,7 @@ WindowedXQueue::WindowedXQueue(std::shared_ptr<HwQueue> hwq, XPreemptLevel level
     tail_marker_ = std::make_shared<XQueueWaitAllCommand>();
     tail_marker_->SetState(kCommandStateCompleted);
     worker_ = std::thread([this] {
+        prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);   // 1 us timer slack: short sleeps in waits stay short
         kHwQueue->OnXQueueCreate();        // on the launching thread: a CUDA queue binds its context here
         WorkerMain();
     });

@@ -25,6 +25,11 @@ void XCommand::SetState(XCommandState state) {
 }
 
 void XCommand::WaitUntil(XCommandState state) {
+    // Short spin first: most waits end within tens of microseconds and a futex sleep + wake costs that much.
+    for (int i = 0; i < 2000; ++i) {
+        if (state_.load(std::memory_order_acquire) >= (int32_t)state) return;
+        __builtin_ia32_pause();
+    }
     int32_t cur = state_.load(std::memory_order_acquire);
     while (cur < (int32_t)state) {
         state_.wait(cur, std::memory_order_acquire);

@@ -28,7 +28,7 @@ void GlobalScheduler::Run() {
     impl_->worker = std::thread([this] {
         alignas(8) unsigned char buf[65536];
         while (true) {
-            const long n = impl_->recv.Receive(buf, sizeof(buf));
+            const long n = impl_->recv.ReceiveAuto(buf, sizeof(buf));
             if (n <= 0) return;
             Operation op;
             if (!op.Assign(buf, (size_t)n)) { XWARN("malformed operation of %ld bytes dropped", n); continue; }

@@ -1,5 +1,6 @@
 #include "xsched/sched/ipc.h"
 
+#include <cerrno>
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -53,6 +54,25 @@ long IpcEndpoint::Receive(void *buf, size_t cap) {
     const ssize_t n = ::recv(fd_, buf, cap, 0);
     if (closed_) return 0;
     return n < 0 ? -1 : (long)n;
+}
+
+long IpcEndpoint::TryReceive(void *buf, size_t cap) {
+    if (fd_ < 0) return -1;
+    if (closed_) return 0;
+    const ssize_t n = ::recv(fd_, buf, cap, MSG_DONTWAIT);
+    if (closed_) return 0;
+    if (n < 0) return (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) ? -2 : -1;
+    return (long)n;
+}
+
+long IpcEndpoint::ReceiveAuto(void *buf, size_t cap) {
+    static const bool spin = GetEnvOption(XSCHED_IPC_SPIN_ENV_NAME, false);
+    if (!spin) return Receive(buf, cap);
+    while (true) {
+        const long n = TryReceive(buf, cap);
+        if (n != -2) return n;
+        for (int i = 0; i < 16; ++i) __builtin_ia32_pause();
+    }
 }
 
 void IpcEndpoint::Close() {

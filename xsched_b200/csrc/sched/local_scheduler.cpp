@@ -135,6 +135,34 @@ void LocalScheduler::Worker() {
     }
 }
 
+void LocalScheduler::StepInline(const Event *events, size_t n) {
+    std::lock_guard<std::mutex> sl(status_mtx_);
+    const int64_t now = NowEpochUs();
+    timers_.erase(timers_.begin(), std::upper_bound(timers_.begin(), timers_.end(), now));
+    for (size_t i = 0; i < n; ++i) {
+        const Event &e = events[i];
+        switch (e.Type()) {       // same bookkeeping RecvEvent does on the receiving thread
+        case kEventProcessCreate: { std::lock_guard<std::mutex> lk(op_mtx_); ops_.try_emplace(e.Pid()); break; }
+        case kEventProcessDestroy: { std::lock_guard<std::mutex> lk(op_mtx_); ops_.erase(e.Pid()); break; }
+        case kEventOperationComplete: {
+            std::lock_guard<std::mutex> lk(op_mtx_);
+            auto it = ops_.find(e.Pid());
+            if (it != ops_.end()) it->second.completed = std::max(it->second.completed, e.As<EvOpComplete>().op_id);
+            continue;
+        }
+        case kEventSchedulerTerminate: continue;
+        default: break;
+        }
+        Apply(e);
+    }
+    Decide();
+    rounds_.fetch_add(1);
+}
+
+int64_t LocalScheduler::NextTimerUs() const {
+    return timers_.empty() ? INT64_MAX : timers_.front();
+}
+
 XQueueStatus &LocalScheduler::Ensure(XQueueHandle h, PID pid) {
     auto it = status_.xqueues.find(h);
     if (it != status_.xqueues.end()) return it->second;

@@ -20,6 +20,7 @@
 #include <mutex>
 #include <string>
 #include <thread>
+#include <vector>
 #include <poll.h>
 #include <sys/syscall.h>
 #include <unistd.h>
@@ -55,28 +56,57 @@ public:
         }
         XASSERT(send_.OpenSender(), "cannot open the operation socket");
         g_recv = &recv_;
-        sched_.Run();
+        const bool spin = GetEnvOption(XSCHED_IPC_SPIN_ENV_NAME, false);
+        if (!spin) sched_.Run();
         std::thread watcher([this] { WatchClients(); });
         std::thread status;
         if (status_interval_ms > 0) status = std::thread([this, status_interval_ms] { PrintStatus(status_interval_ms); });
-        std::printf("xserver ready policy=%s pid=%d\n", xsched::protocol::GetPolicyTypeName(sched_.GetPolicy()), (int)getpid());
+        std::printf("xserver ready policy=%s pid=%d mode=%s\n", xsched::protocol::GetPolicyTypeName(sched_.GetPolicy()), (int)getpid(),
+                    spin ? "polling" : "blocking");
         std::fflush(stdout);
 
         alignas(8) unsigned char buf[4096];
-        while (!g_stop.load()) {
-            const long n = recv_.Receive(buf, sizeof(buf));
-            if (n <= 0) break;
-            Event e;
-            if (!e.Assign(buf, (size_t)n)) { XWARN("malformed event of %ld bytes dropped", n); continue; }
-            if (e.Type() == kEventProcessCreate) Track(e.Pid());
-            if (e.Type() == kEventProcessDestroy) Untrack(e.Pid());
-            if (e.Type() == kEventSchedulerTerminate) continue;      // clients cannot stop the server
-            sched_.RecvEvent(e);
+        if (spin) {
+            // Polling mode: one thread receives, updates the status, runs the policy and sends the
+            // operations — no hand-off to a worker thread, no sleep between a ready event and the suspend
+            // operation it causes.  Policy timers are served from the same loop.
+            std::vector<Event> batch;
+            while (!g_stop.load()) {
+                batch.clear();
+                while (batch.size() < 64) {
+                    const long n = recv_.TryReceive(buf, sizeof(buf));
+                    if (n == -2) break;
+                    if (n <= 0) { g_stop.store(true); break; }
+                    Event e;
+                    if (!e.Assign(buf, (size_t)n)) continue;
+                    if (e.Type() == kEventProcessCreate) Track(e.Pid());
+                    if (e.Type() == kEventProcessDestroy) Untrack(e.Pid());
+                    batch.push_back(e);
+                }
+                {
+                    std::lock_guard<std::mutex> lk(inject_mu_);
+                    for (auto &e : injected_) batch.push_back(e);
+                    injected_.clear();
+                }
+                if (!batch.empty() || NowEpochUs() >= sched_.NextTimerUs()) sched_.StepInline(batch.data(), batch.size());
+                else for (int i = 0; i < 16; ++i) __builtin_ia32_pause();
+            }
+        } else {
+            while (!g_stop.load()) {
+                const long n = recv_.Receive(buf, sizeof(buf));
+                if (n <= 0) break;
+                Event e;
+                if (!e.Assign(buf, (size_t)n)) { XWARN("malformed event of %ld bytes dropped", n); continue; }
+                if (e.Type() == kEventProcessCreate) Track(e.Pid());
+                if (e.Type() == kEventProcessDestroy) Untrack(e.Pid());
+                if (e.Type() == kEventSchedulerTerminate) continue;      // clients cannot stop the server
+                sched_.RecvEvent(e);
+            }
         }
         g_stop.store(true);
         watcher.join();
         if (status.joinable()) status.join();
-        sched_.Stop();
+        if (!spin) sched_.Stop();
         return 0;
     }
 
@@ -87,8 +117,16 @@ private:
             // The client is gone or not listening yet: acknowledge on its behalf so nobody waits for it.
             Event ack = Event::OperationComplete(op.Meta().id);
             reinterpret_cast<EventMeta *>(ack.bytes)->pid = pid;
-            sched_.RecvEvent(ack);
+            Deliver(ack);
         }
+    }
+
+    // Events produced inside the server (client death, acknowledgements on behalf of a dead client).
+    void Deliver(const Event &e) {
+        static const bool spin = GetEnvOption(XSCHED_IPC_SPIN_ENV_NAME, false);
+        if (!spin) { sched_.RecvEvent(e); return; }
+        std::lock_guard<std::mutex> lk(inject_mu_);
+        injected_.push_back(e);
     }
 
     void Track(int32_t pid) {
@@ -121,7 +159,7 @@ private:
                 if (!dead) continue;
                 XINFO("client %d is gone; removing its XQueues", pid);
                 Untrack(pid);
-                sched_.RecvEvent(Event::ProcessDestroy(pid));
+                Deliver(Event::ProcessDestroy(pid));
             }
         }
     }
@@ -151,6 +189,8 @@ private:
     IpcEndpoint recv_, send_;
     std::mutex mu_;
     std::map<int32_t, int> clients_;
+    std::mutex inject_mu_;
+    std::vector<Event> injected_;
 };
 
 } // namespace
