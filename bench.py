@@ -238,6 +238,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--level1", action="store_true", help="also run the co-run phase at preemption level 1")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-variants", action="store_true", help="skip the one-process and native-priority comparison runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -286,6 +287,20 @@ def main() -> None:
             pg.barrier()
 
         extra = {}
+        if not args.no_variants:
+            # Same workload with both XQueues in ONE process (in-process scheduler, one CUDA context: no
+            # inter-process context switch on the GPU), and the no-XSched baseline: native CUDA stream
+            # priorities with the non-preemptible twin of the GEMM.
+            both = run_json(worker_cmd("both", device, level=2, count=args.steps, period_us=PERIOD_US, hp_n=HP_N, duration_s=3600, **lp_kw),
+                            base_env(ns, None), 600)
+            hp_b, lp_b = both[0], both[1]
+            nat = run_json(worker_cmd("native-priority", device, count=args.steps, period_us=PERIOD_US, hp_n=HP_N, kernel="gemm", **GEMM),
+                           base_env(ns, None), 600)[-1]
+            launches += hp_b["xpk_launches"]
+            extra["one_process_two_queues"] = {"hp_p99_us": hp_b["p99_us"], "hp_p50_us": hp_b["p50_us"], "ratio": round(hp_b["p99_us"] / hp_alone["p99_us"], 3),
+                                               "bg_kept_pct": round(100 * lp_b["rate"] / lp_alone["rate"], 2), "bit_exact": lp_b["bit_exact"]}
+            extra["native_stream_priority"] = {"hp_p99_us": nat["p99_us"], "hp_p50_us": nat["p50_us"], "hp_standalone_p99_us": nat["standalone_p99_us"],
+                                               "ratio": nat["ratio_p99"]}
         if args.level1:
             hp_l1, lp_l1 = corun(device, ns, 1, args.steps, args.warmup, False, PERIOD_US, lp_kw)
             extra["level1"] = {"hp_p99_us": hp_l1["p99_us"], "ratio": round(hp_l1["p99_us"] / hp_alone["p99_us"], 3),

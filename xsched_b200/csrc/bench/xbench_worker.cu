@@ -451,6 +451,62 @@ static int PreemptLatency(const Args &a) {
 
 #include <numeric>
 
+// ---- baseline without XSched: native CUDA stream priorities, one process, two streams ----------------
+// LP: the non-preemptible twin of the low-priority kernel back-to-back on a least-priority stream (two
+// launches kept in flight); HP: the high-priority kernel every period on a greatest-priority stream.
+static int NativePriority(const Args &a) {
+    int lo = 0, hi = 0;
+    CK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    Queue ql, qh;                       // plain streams, no XQueue
+    CK(cudaStreamCreateWithPriority(&ql.stream, cudaStreamNonBlocking, lo));
+    CK(cudaStreamCreateWithPriority(&qh.stream, cudaStreamNonBlocking, hi));
+    Args la = a;
+    la.depth = 2;
+    LpWork lw = BuildLp(la, ql, XPK_FLAG_NON_PREEMPTIBLE);
+    HpWork hw = BuildHp(a, qh);
+    auto hp_once = [&]() {
+        const int64_t t0 = NowNs();
+        PK(xpkTaskReset(hw.task, qh.stream));
+        PK(xpkTaskLaunch(hw.task, qh.stream, 0));
+        CK(cudaStreamSynchronize(qh.stream));
+        return (NowNs() - t0) / 1e3;
+    };
+    std::vector<double> alone;
+    for (int i = 0; i < 5; ++i) hp_once();
+    for (int i = 0; i < 100; ++i) { alone.push_back(hp_once()); SleepUs(2000); }
+    std::atomic<bool> stop{false};
+    std::atomic<uint64_t> iters{0};
+    std::thread lp([&] {
+        cudaEvent_t ev[2];
+        CK(cudaEventCreateWithFlags(&ev[0], cudaEventDisableTiming)); CK(cudaEventCreateWithFlags(&ev[1], cudaEventDisableTiming));
+        uint64_t i = 0;
+        while (!stop.load()) {
+            if (i >= 2) CK(cudaEventSynchronize(ev[i & 1]));
+            PK(xpkTaskReset(lw.tasks[i & 1], ql.stream));
+            PK(xpkTaskLaunch(lw.tasks[i & 1], ql.stream, 0));
+            CK(cudaEventRecord(ev[i & 1], ql.stream));
+            ++i;
+        }
+        CK(cudaStreamSynchronize(ql.stream));
+        iters.store(i);
+    });
+    SleepUs(300000);
+    std::vector<double> lat;
+    const int64_t t_begin = NowNs();
+    int64_t next = t_begin;
+    for (int i = 0; i < a.count; ++i) {
+        next += a.period_us * 1000;
+        while (NowNs() < next) { const int64_t left = next - NowNs(); if (left > 200000) SleepUs(left / 2000); else std::this_thread::yield(); }
+        lat.push_back(hp_once());
+    }
+    stop.store(true);
+    lp.join();
+    std::printf("{\"role\": \"native-priority\", \"n\": %zu, \"standalone_p50_us\": %.2f, \"standalone_p99_us\": %.2f, \"p50_us\": %.2f, \"p99_us\": %.2f, "
+                "\"max_us\": %.2f, \"ratio_p99\": %.3f}\n", lat.size(), Pct(alone, 0.5), Pct(alone, 0.99), Pct(lat, 0.5), Pct(lat, 0.99), Pct(lat, 1.0),
+                Pct(lat, 0.99) / std::max(1.0, Pct(alone, 0.99)));
+    return 0;
+}
+
 int main(int argc, char **argv) {
     Args a = Parse(argc, argv);
     std::signal(SIGTERM, OnTerm);
@@ -459,6 +515,7 @@ int main(int argc, char **argv) {
     CK(cudaFree(0));
     prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);
     if (a.role == "preempt-latency") return PreemptLatency(a);
+    if (a.role == "native-priority") return NativePriority(a);
     if (a.role == "lp") {
         Queue q = MakeQueue(a, a.level, a.prio);
         LpWork w = BuildLp(a, q, 0);

@@ -11,8 +11,8 @@
 //
 // Inside a scatter tile (512 threads x 16 keys, keys held warp-striped so that load order is
 // preserved):
-//   * each warp ranks its keys digit by digit with __match_any_sync / __popc — the lanes that
-//     share a digit learn their order from the match mask, the lowest lane bumps the warp's
+//   * each warp ranks its keys digit by digit with __ballot_sync / __popc — eight ballots give the
+//     mask of lanes that share a digit, those lanes learn their order from the mask, the lowest lane bumps the warp's
 //     counter in shared memory and __shfl_sync hands the base back (stable within the warp);
 //   * warp counters are prefix-summed across warps, giving stable ranks within the tile;
 //   * the tile's per-digit counts are published and the exclusive prefix over earlier tiles
@@ -76,6 +76,20 @@ __device__ __forceinline__ unsigned long long ld_acquire64(const unsigned long l
 
 // Signed ascending order == unsigned order of the key with its sign bit flipped.
 __device__ __forceinline__ uint32_t twiddle(uint32_t k) { return k ^ 0x80000000u; }
+
+// Lanes of the warp holding the same 8-bit digit as this lane: eight ballots, one per digit bit, each
+// keeping the lanes that agree with this lane on that bit.  (The single match.any instruction gives the
+// same mask but issues at a small fraction of the ballot rate.)
+__device__ __forceinline__ uint32_t match_digit(uint32_t d) {
+    uint32_t mask = 0xffffffffu;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        const bool bit = (d >> b) & 1u;
+        const uint32_t vote = __ballot_sync(0xffffffffu, bit);
+        mask &= bit ? vote : ~vote;
+    }
+    return mask;
+}
 
 // Exclusive scan of 256 values held by threads 0..255 (one each); all 512 threads call.
 __device__ __forceinline__ uint32_t block_excl_scan256(uint32_t v, SortSmem &sm, uint32_t *total) {
@@ -197,7 +211,7 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
 #pragma unroll
             for (int i = 0; i < kSortItems; ++i) {
                 const uint32_t d = (key[i] >> shift) & 255u;
-                const uint32_t mask = __match_any_sync(0xffffffffu, d);
+                const uint32_t mask = match_digit(d);
                 const int leader = __ffs(mask) - 1;
                 const uint32_t before = __popc(mask & ((1u << lane) - 1u));
                 uint32_t base = 0;
@@ -311,3 +325,4 @@ cudaError_t launch_sort(bool preemptible, Ctl *ctl, uint32_t *keys, uint32_t *tm
 }
 
 } // namespace xpk
+
