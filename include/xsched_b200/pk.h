@@ -143,6 +143,30 @@ xpkResult xpkTaskFlag(xpkTask_t task, uint32_t **flag_dev);
 xpkResult xpkTaskKind(xpkTask_t task, uint32_t *kind);
 xpkResult xpkTaskDestroy(xpkTask_t task);
 
+/* ---- sorting without any allocation ---------------------------------------------------
+ * (No counterpart in the reference, which has no sort kernel and no allocation-free entry points.)
+ *
+ * For callers that cannot allocate device or pinned memory at the point where they need a sort —
+ * code running while a memory pool is frozen, a plugin that was handed two buffers and a stream and
+ * nothing else, a latency-critical section where cudaMalloc's implicit device synchronisation is not
+ * acceptable.  xpkTaskCreateSort needs a control block, a mailbox and caller-provided scratch; this
+ * entry point needs none of them: its control block, digit histograms and look-back words live in a
+ * fixed array inside the library's device image (about 2.1 MB, held by every GPU that loads the
+ * library until the process exits).
+ *
+ * Sorts `n` int32 keys ascending, in place in `keys`, using `tmp` (n keys) as the second buffer, on
+ * `stream`; asynchronous, the result is ready when the stream reaches this point.  Not preemptible.
+ *   - n > XPK_SORT_NOALLOC_MAX_KEYS  -> XPK_ERR_TOO_LARGE; keys/tmp must be 16-byte aligned.
+ *   - Calls no cudaMalloc/cudaFree/cudaHostAlloc and no library routine that allocates.
+ *   - The first call on each device resolves the array's address (cudaGetSymbolAddress) and sets a
+ *     kernel attribute; make that first call outside any stream capture.
+ *   - All calls on one device share the one array.  It keeps the previous call's contents (the entry
+ *     point clears what it needs), and two calls whose kernels overlap on the GPU — different
+ *     streams, or different host threads without ordering between their streams — race on it:
+ *     serialise them.                                                                      */
+#define XPK_SORT_NOALLOC_MAX_KEYS (4ull << 20)
+xpkResult xpkSortNoAlloc(int32_t *keys, int32_t *tmp, uint64_t n, void *stream);
+
 /* Kernels launched by this library in this process since load (all tasks). */
 uint64_t xpkLaunchCount(void);
 

@@ -29,6 +29,9 @@
 // the phase counters and look-back words stay in global memory, and the relaunch continues
 // with the next ticket.  Integer arithmetic only, so the result is bit-exact by construction.
 #include "pk_common.cuh"
+#include "xsched_b200/pk.h"
+
+#include <mutex>
 
 namespace xpk {
 
@@ -326,3 +329,83 @@ cudaError_t launch_sort(bool preemptible, Ctl *ctl, uint32_t *keys, uint32_t *tm
 
 } // namespace xpk
 
+// ---------------------------------------------------------------------------------------------------
+// xpkSortNoAlloc: the same sort for callers that must not allocate.
+//
+// Everything the kernel needs beyond the caller's two key buffers — the control block, the four digit
+// histograms and the look-back words — lives in one statically sized array in device memory that is part
+// of this library's image.  The host side only ever handles its address, obtained once per device with
+// cudaGetSymbolAddress (the array's name is not a device pointer in host code).
+namespace {
+
+constexpr unsigned long long kNoAllocMaxKeys = XPK_SORT_NOALLOC_MAX_KEYS;
+constexpr unsigned long long kNoAllocMaxTiles = (kNoAllocMaxKeys + xpk::kSortTile - 1) / xpk::kSortTile;
+constexpr size_t kNoAllocCtlBytes = (sizeof(xpk::Ctl) + 255) / 256 * 256;
+constexpr size_t kNoAllocHistBytes = 4096;
+constexpr size_t kNoAllocStateBytes = (size_t)4 * kNoAllocMaxTiles * xpk::kRadix * sizeof(uint32_t);
+constexpr size_t kNoAllocBytes = kNoAllocCtlBytes + kNoAllocHistBytes + kNoAllocStateBytes;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// Prepares the control block in place: cursor at tile 0, private flag lowered, no mailbox.
+__global__ void noalloc_init_ctl(xpk::Ctl *ctl, unsigned long long total) {
+    unsigned long long *w = reinterpret_cast<unsigned long long *>(ctl);
+    for (unsigned i = threadIdx.x; i < 256 / 8; i += blockDim.x) w[i] = 0;     // bytes [0,256): state + header
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ctl->total = total;
+        ctl->own_flag = 0;
+        ctl->flag = &ctl->own_flag;
+        ctl->mailbox = nullptr;
+    }
+}
+
+struct NoAllocDevice {
+    unsigned char *base = nullptr;     // device address of g_noalloc_scratch on this device
+    int grid_limit = 0;                // SMs x resident CTAs per SM
+};
+std::mutex g_noalloc_mu;
+NoAllocDevice g_noalloc_dev[64];
+
+} // namespace
+
+extern "C" xpkResult xpkSortNoAlloc(int32_t *keys, int32_t *tmp, uint64_t n, void *stream) {
+    if (keys == nullptr || tmp == nullptr || n == 0) return XPK_ERR_INVALID_VALUE;
+    if (n > kNoAllocMaxKeys) return XPK_ERR_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(keys) & 15u) || (reinterpret_cast<uintptr_t>(tmp) & 15u)) return XPK_ERR_ALIGNMENT;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return XPK_ERR_CUDA;
+    NoAllocDevice d;
+    {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (g_noalloc_dev[dev].base == nullptr) {
+            // First call on this device: resolve the array's device address and size the grid.  None of
+            // these calls allocates, but they are not stream operations, so make this first call outside
+            // any stream capture.
+            void *p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return XPK_ERR_CUDA;
+            if (xpk::sort_prepare() != cudaSuccess) return XPK_ERR_CUDA;
+            int sms = 0;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return XPK_ERR_CUDA;
+            g_noalloc_dev[dev].grid_limit = sms * xpk::sort_ctas_per_sm();
+            g_noalloc_dev[dev].base = static_cast<unsigned char *>(p);
+        }
+        d = g_noalloc_dev[dev];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    xpk::Ctl *ctl = reinterpret_cast<xpk::Ctl *>(d.base);
+    uint32_t *hist = reinterpret_cast<uint32_t *>(d.base + kNoAllocCtlBytes);
+    uint32_t *state = reinterpret_cast<uint32_t *>(d.base + kNoAllocCtlBytes + kNoAllocHistBytes);
+    const unsigned long long T = xpk::sort_tiles(n);
+    // The array keeps whatever the previous call left: the histograms and the look-back words of the T
+    // tiles this call uses must start at zero.
+    if (cudaMemsetAsync(hist, 0, kNoAllocHistBytes + (size_t)4 * T * xpk::kRadix * sizeof(uint32_t), s) != cudaSuccess) return XPK_ERR_CUDA;
+    noalloc_init_ctl<<<1, 32, 0, s>>>(ctl, 5 * T);
+    if (cudaGetLastError() != cudaSuccess) return XPK_ERR_CUDA;
+    unsigned long long grid = (unsigned long long)d.grid_limit;
+    if (grid > 5 * T) grid = 5 * T;
+    if (xpk::launch_sort(/*preemptible=*/false, ctl, reinterpret_cast<uint32_t *>(keys), reinterpret_cast<uint32_t *>(tmp), hist, state, n,
+                         /*launch_no=*/1, (int)grid, s) != cudaSuccess)
+        return XPK_ERR_CUDA;
+    return XPK_SUCCESS;
+}

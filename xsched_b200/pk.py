@@ -26,7 +26,7 @@ EXPORTS = [
     "xpkDeviceSmCount", "xpkResultString", "xpkFlagCreate", "xpkFlagDestroy", "xpkFlagSet",
     "xpkTaskCreateTriad", "xpkTaskCreateVecAdd", "xpkSortScratchBytes", "xpkTaskCreateSort",
     "xpkTaskCreateGemm", "xpkTaskLaunch", "xpkTaskQuery", "xpkTaskWait", "xpkTaskReset",
-    "xpkTaskFlag", "xpkTaskKind", "xpkTaskDestroy", "xpkLaunchCount",
+    "xpkTaskFlag", "xpkTaskKind", "xpkTaskDestroy", "xpkLaunchCount", "xpkSortNoAlloc",
 ]
 
 
@@ -56,6 +56,8 @@ lib.xpkTaskFlag.argtypes = [_vp, C.POINTER(_vp)]
 lib.xpkTaskKind.argtypes = [_vp, C.POINTER(_u32)]
 lib.xpkTaskDestroy.argtypes = [_vp]
 lib.xpkLaunchCount.restype = _u64
+lib.xpkSortNoAlloc.argtypes = [_vp, _vp, _u64, _vp]
+SORT_NOALLOC_MAX_KEYS = 4 << 20
 
 
 class XpkError(RuntimeError):
@@ -81,6 +83,12 @@ def launch_count() -> int:
 
 def sort_scratch_bytes(n: int) -> int:
     return int(lib.xpkSortScratchBytes(n))
+
+
+def sort_no_alloc(keys, tmp, stream: int) -> None:
+    """In-place ascending sort of the int32 tensor `keys` through xpkSortNoAlloc (no allocation at all;
+    at most SORT_NOALLOC_MAX_KEYS keys; calls on one device must not overlap on the GPU)."""
+    _check(lib.xpkSortNoAlloc(keys.data_ptr(), tmp.data_ptr(), keys.numel(), stream), "xpkSortNoAlloc")
 
 
 class Flag:
