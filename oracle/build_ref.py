@@ -12,7 +12,7 @@ On top of the core this script builds, against the REFERENCE headers, the host-o
 the trace driver that tests and bench.py use to run the reference as the checker / CPU baseline:
     oracle/_ref/libhalhost_ref.so   from xsched_b200/csrc/hal_host/*.cpp
     oracle/_ref/lane_driver_ref     from oracle/lane_driver.cpp
-    oracle/_ref/policy_probe_ref    from oracle/policy_probe.cpp   (reference-only: drives Policy classes)
+    oracle/_ref/sched_probe_ref     from oracle/sched_probe_ref.cpp (drives the reference LocalScheduler + policies)
 
 Usage: python oracle/build_ref.py [--force]      (XSCHED_REFERENCE_DIR overrides the tree location)
 """
@@ -82,8 +82,8 @@ def main() -> None:
     if lane_srcs and (force or stale(lane, lane_srcs + [core])):
         run([CXX, *FLAGS, *ref_includes(), lane_inc, "-shared", "-o", str(lane), *map(str, lane_srcs), *link])
         print(f"built {lane}")
-    for name, extra in (("lane_driver", ["-lhalhost_ref"]), ("policy_probe", []), ("ref_server", [])):
-        src = HERE / f"{name}.cpp"
+    for name, srcname, extra in (("lane_driver", "lane_driver", ["-lhalhost_ref"]), ("sched_probe", "sched_probe_ref", [])):
+        src = HERE / f"{srcname}.cpp"
         out = OUT / f"{name}_ref"
         if src.exists() and (force or stale(out, [src, core, lane])):
             run([CXX, *FLAGS, *ref_includes(), lane_inc, "-o", str(out), str(src), *link, *extra])

@@ -41,8 +41,9 @@ static int64_t NowNs() {
     return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 static void SleepUs(int64_t us) { std::this_thread::sleep_for(std::chrono::microseconds(us)); }
-static uint64_t Executed(uint32_t lane = 0) { uint64_t e = 0, f = 0; HostLaneStats(lane, &e, &f); return e; }
-static uint64_t Flushed(uint32_t lane = 0) { uint64_t e = 0, f = 0; HostLaneStats(lane, &e, &f); return f; }
+static uint32_t LaneId();
+static uint64_t Executed() { uint64_t e = 0, f = 0; HostLaneStats(LaneId(), &e, &f); return e; }
+static uint64_t Flushed() { uint64_t e = 0, f = 0; HostLaneStats(LaneId(), &e, &f); return f; }
 static double Pct(std::vector<double> v, double p) {
     if (v.empty()) return 0;
     std::sort(v.begin(), v.end());
@@ -51,10 +52,13 @@ static double Pct(std::vector<double> v, double p) {
 }
 #define CHECK(x) do { XResult r_ = (x); if (r_ != kXSchedSuccess) { std::fprintf(stderr, "%s -> %d\n", #x, (int)r_); std::exit(2); } } while (0)
 
+// The lane (= XDevice id) is taken from LANE_ID so that several driver processes can stand for several devices.
+static uint32_t LaneId() { const char *v = std::getenv("LANE_ID"); return v ? (uint32_t)std::atoi(v) : 0u; }
+
 static XQueueHandle MakeQueue(int64_t level, int64_t threshold, int64_t batch, HwQueueHandle *hwq_out = nullptr) {
     HwQueueHandle hwq = 0;
     XQueueHandle xq = 0;
-    CHECK(HostLaneQueueCreate(&hwq, 0));
+    CHECK(HostLaneQueueCreate(&hwq, LaneId()));
     CHECK(XQueueCreate(&xq, hwq, level, kQueueCreateFlagNone));
     if (threshold > 0 || batch > 0) CHECK(XQueueSetLaunchConfig(xq, threshold, batch));
     if (hwq_out) *hwq_out = hwq;

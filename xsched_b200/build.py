@@ -150,6 +150,9 @@ def build_lane_driver(force: bool = False, verbose: bool = False) -> Path | None
     if force or _stale(out, deps):
         _run([CXX, "-std=c++20", "-O2", "-pthread", f"-I{INC}", "-o", out, src, f"-L{LIB}", f"-Wl,-rpath,{LIB}",
               "-lhalhost", "-lpreempt"], verbose)
+    probe_src, probe = ORACLE / "sched_probe_new.cpp", ORACLE / "sched_probe_new"
+    if probe_src.exists() and (force or _stale(probe, [probe_src, LIB / "libpreempt.so"])):
+        _run([CXX, "-std=c++20", "-O2", "-pthread", f"-I{INC}", "-o", probe, probe_src, f"-L{LIB}", f"-Wl,-rpath,{LIB}", "-lpreempt"], verbose)
     return out
 
 
