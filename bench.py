@@ -88,6 +88,13 @@ class ClockSampler(threading.Thread):
                 "samples": len(s)}
 
 
+_T0 = time.time()
+
+
+def mark(msg: str) -> None:
+    print(f"[bench +{time.time() - _T0:6.1f}s rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def worker_cmd(role: str, device: int, **kw) -> list[str]:
     cmd = [str(WORKER), "--role", role, "--device", str(device)]
     for k, v in kw.items():
@@ -96,7 +103,10 @@ def worker_cmd(role: str, device: int, **kw) -> list[str]:
 
 
 def run_json(cmd: list[str], env: dict, timeout: float) -> list[dict]:
-    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout)
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=timeout)
+    except subprocess.TimeoutExpired as e:
+        raise RuntimeError(f"{' '.join(cmd[:4])} timed out after {timeout:.0f} s; stderr: {(e.stderr or b'')[-1500:]!r}")
     if r.returncode != 0:
         raise RuntimeError(f"{' '.join(cmd[:4])} failed rc={r.returncode}: {r.stderr[-1500:]}")
     return [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
@@ -114,27 +124,44 @@ def base_env(ns: str, sched: str | None) -> dict:
 
 def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, period_us: int, lp_kw: dict) -> tuple[dict, dict]:
     """LP process + HP process under the (already running) xserver.  Returns (hp_json, lp_json)."""
+    import tempfile
     env = base_env(ns, "GLB")
+    lp_err = tempfile.TemporaryFile(mode="w+")
     lp = subprocess.Popen(worker_cmd("lp", device, level=level, prio=0, duration_s=3600, warmup_s=0.5, **lp_kw),
-                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env)
+                          stdout=subprocess.PIPE, stderr=lp_err, text=True, env=env)
+
+    def lp_stderr_tail() -> str:
+        lp_err.seek(0)
+        return lp_err.read()[-1500:]
+
     try:
-        t0 = time.time()
-        while True:
-            line = lp.stdout.readline()
-            if line.startswith("READY"):
-                break
-            if not line and lp.poll() is not None:
-                raise RuntimeError("LP worker died: " + lp.stderr.read()[-1500:])
-            if time.time() - t0 > 120:
-                raise RuntimeError("LP worker did not become ready")
+        ready = threading.Event()
+
+        def wait_ready():
+            for line in lp.stdout:
+                if line.startswith("READY"):
+                    ready.set()
+                    return
+        th = threading.Thread(target=wait_ready, daemon=True)
+        th.start()
+        if not ready.wait(timeout=90):
+            raise RuntimeError(f"LP worker not ready after 90 s (rc={lp.poll()}): {lp_stderr_tail()}")
+        mark(f"corun level {level}: LP ready, starting HP")
+        # budget: every request takes at most a few periods even when things go badly
+        hp_timeout = 60 + (steps + warmup) * period_us * 20 / 1e6
         hp = run_json(worker_cmd("hp", device, level=level, prio=1, count=steps + warmup, period_us=period_us, hp_n=HP_N,
-                                 e2e=int(e2e)), env, timeout=600)[-1]
+                                 e2e=int(e2e)), env, timeout=hp_timeout)[-1]
+        mark(f"corun level {level}: HP done")
     finally:
         lp.send_signal(signal.SIGTERM)
-        out, err = lp.communicate(timeout=120)
+        try:
+            out, _ = lp.communicate(timeout=60)
+        except subprocess.TimeoutExpired:
+            lp.kill()
+            out, _ = lp.communicate()
     lp_json = [json.loads(l) for l in out.splitlines() if l.startswith("{")]
     if not lp_json:
-        raise RuntimeError("LP worker printed no result: " + err[-1500:])
+        raise RuntimeError("LP worker printed no result: " + lp_stderr_tail())
     return hp, lp_json[-1]
 
 
@@ -264,17 +291,20 @@ def main() -> None:
     try:
         # ---- standalone phases (untimed with respect to the step clock) ----
         env_alone = base_env(ns, "APP")
-        hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(100, args.steps // 2), period_us=PERIOD_US, hp_n=HP_N), env_alone, 300)[-1]
-        lp_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **lp_kw), env_alone, 300)[-1]
+        mark("standalone phases")
+        hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(100, args.steps // 2), period_us=PERIOD_US, hp_n=HP_N), env_alone, 120)[-1]
+        lp_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **lp_kw), env_alone, 120)[-1]
         launches += hp_alone["xpk_launches"] + lp_alone["xpk_launches"]
-        lat = run_json(worker_cmd("preempt-latency", device, level=2, count=300, **lp_kw), env_alone, 300)[-1]
+        lat = run_json(worker_cmd("preempt-latency", device, level=2, count=300, **lp_kw), env_alone, 120)[-1]
         roof, roof_launches = gemm_roofline(device)
         print(f"[bench] standalone hp={hp_alone} lp={lp_alone} lat={lat} roof={roof}", file=sys.stderr, flush=True)
         launches += roof_launches
 
         # ---- timed region: K high-priority steps against the running low-priority loop ----
+        mark("barrier before the timed region")
         if pg:
             pg.barrier()
+        mark("timed region")
         sampler = ClockSampler(device)
         sampler.start()
         t0 = time.time()

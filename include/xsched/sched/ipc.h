@@ -18,7 +18,11 @@ public:
 
     bool Bind(uint64_t key);                       // become the receiver of `key`
     bool OpenSender();                             // unbound socket for SendTo
-    bool SendTo(uint64_t key, const void *data, size_t size);
+    bool SendTo(uint64_t key, const void *data, size_t size);        // may block while the receiver's queue is full
+    /// Never blocks: 1 = sent, 0 = the receiver's queue is full right now, -1 = no such receiver / error.
+    int TrySendTo(uint64_t key, const void *data, size_t size);
+    /// Wait until a record can be received or `timeout_ms` passed (-1 = forever).  False on timeout.
+    bool WaitReadable(int timeout_ms);
     /// Blocks.  Returns bytes received, 0 after Close(), -1 on error.
     long Receive(void *buf, size_t cap);
     /// Non-blocking: bytes received, -2 when nothing is queued, 0 after Close(), -1 on error.  A thread

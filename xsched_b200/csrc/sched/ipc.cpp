@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <poll.h>
 #include <sys/socket.h>
 #include <sys/un.h>
 #include <unistd.h>
@@ -46,6 +47,21 @@ bool IpcEndpoint::SendTo(uint64_t key, const void *data, size_t size) {
     sockaddr_un addr;
     const socklen_t len = MakeAddr(key, addr);
     return ::sendto(fd_, data, size, 0, (sockaddr *)&addr, len) == (ssize_t)size;
+}
+
+int IpcEndpoint::TrySendTo(uint64_t key, const void *data, size_t size) {
+    if (fd_ < 0 || closed_) return -1;
+    sockaddr_un addr;
+    const socklen_t len = MakeAddr(key, addr);
+    const ssize_t n = ::sendto(fd_, data, size, MSG_DONTWAIT, (sockaddr *)&addr, len);
+    if (n == (ssize_t)size) return 1;
+    return (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) ? 0 : -1;
+}
+
+bool IpcEndpoint::WaitReadable(int timeout_ms) {
+    if (fd_ < 0 || closed_) return true;
+    pollfd p{fd_, POLLIN, 0};
+    return ::poll(&p, 1, timeout_ms) > 0;
 }
 
 long IpcEndpoint::Receive(void *buf, size_t cap) {

@@ -13,6 +13,7 @@
 #include <atomic>
 #include <chrono>
 #include <csignal>
+#include <deque>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -88,11 +89,15 @@ public:
                     for (auto &e : injected_) batch.push_back(e);
                     injected_.clear();
                 }
+                FlushOutbox();
                 if (!batch.empty() || NowEpochUs() >= sched_.NextTimerUs()) sched_.StepInline(batch.data(), batch.size());
                 else for (int i = 0; i < 16; ++i) __builtin_ia32_pause();
             }
         } else {
             while (!g_stop.load()) {
+                // Operations are parked by the scheduler's thread; wake up regularly to retry them
+                // (every millisecond while some are parked, every 20 ms otherwise).
+                if (!recv_.WaitReadable(FlushOutbox() ? 1 : 20)) continue;
                 const long n = recv_.Receive(buf, sizeof(buf));
                 if (n <= 0) break;
                 Event e;
@@ -111,14 +116,46 @@ public:
     }
 
 private:
+    // The server must never block in a send: a client whose receive queue is full may itself be blocked
+    // sending to the server, and two blocked senders would wait for each other forever (datagram queues
+    // hold only a handful of records).  An operation that cannot be delivered now is parked per client and
+    // retried from the main loop; since a Sched operation carries the client's complete running/suspended
+    // sets, a newer one simply replaces a parked older one.
     void Send(const Operation &op) {
         const int32_t pid = op.Meta().pid;
-        if (!send_.SendTo((uint64_t)pid, op.bytes.data(), op.bytes.size())) {
-            // The client is gone or not listening yet: acknowledge on its behalf so nobody waits for it.
-            Event ack = Event::OperationComplete(op.Meta().id);
-            reinterpret_cast<EventMeta *>(ack.bytes)->pid = pid;
-            Deliver(ack);
+        std::lock_guard<std::mutex> lk(out_mu_);
+        auto it = outbox_.find(pid);
+        if (it != outbox_.end()) {
+            if (op.Meta().type == kOperationSched && it->second.back().Meta().type == kOperationSched) it->second.back() = op;
+            else it->second.push_back(op);
+            return;
         }
+        const int r = send_.TrySendTo((uint64_t)pid, op.bytes.data(), op.bytes.size());
+        if (r == 1) return;
+        if (r == 0) { outbox_[pid].push_back(op); return; }
+        AckOnBehalf(op);        // the client is gone or not listening yet: nobody should wait for it
+    }
+
+    void AckOnBehalf(const Operation &op) {
+        Event ack = Event::OperationComplete(op.Meta().id);
+        reinterpret_cast<EventMeta *>(ack.bytes)->pid = op.Meta().pid;
+        Deliver(ack);
+    }
+
+    /// Retry parked operations.  Returns true while something is still parked.
+    bool FlushOutbox() {
+        std::lock_guard<std::mutex> lk(out_mu_);
+        for (auto it = outbox_.begin(); it != outbox_.end();) {
+            auto &q = it->second;
+            while (!q.empty()) {
+                const int r = send_.TrySendTo((uint64_t)it->first, q.front().bytes.data(), q.front().bytes.size());
+                if (r == 0) break;
+                if (r < 0) AckOnBehalf(q.front());
+                q.pop_front();
+            }
+            it = q.empty() ? outbox_.erase(it) : std::next(it);
+        }
+        return !outbox_.empty();
     }
 
     // Events produced inside the server (client death, acknowledgements on behalf of a dead client).
@@ -191,6 +228,8 @@ private:
     std::map<int32_t, int> clients_;
     std::mutex inject_mu_;
     std::vector<Event> injected_;
+    std::mutex out_mu_;
+    std::map<int32_t, std::deque<Operation>> outbox_;
 };
 
 } // namespace
