@@ -27,6 +27,18 @@ static int64_t NowNs() {
     return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
+// Makes a queue's CUDA context current for the duration of a call.  HAL entry points are called from
+// several threads (the XQueue worker, the scheduler's executor thread, application threads); a thread
+// that never bound a context would otherwise run runtime-API launches on device 0's primary context,
+// whatever device the queue belongs to.
+class ContextScope {
+public:
+    explicit ContextScope(CUcontext ctx) { CUDA_ASSERT(Driver().cuCtxPushCurrent(ctx)); }
+    ~ContextScope() { CUcontext old; Driver().cuCtxPopCurrent(&old); }
+    ContextScope(const ContextScope &) = delete;
+    ContextScope &operator=(const ContextScope &) = delete;
+};
+
 class CudaQueue final : public HwQueue {
 public:
     explicit CudaQueue(CUstream stream) : stream_(stream) {
@@ -59,6 +71,7 @@ public:
         CUDA_ASSERT(d.cuStreamSynchronize(stream_));     // nothing may be running on the stream yet
     }
     ~CudaQueue() override {
+        ContextScope scope(ctx_);
         const DriverApi &d = Driver();
         d.cuStreamDestroy(ctrl_);
         d.cuMemFree(flag_);
@@ -66,6 +79,7 @@ public:
     }
 
     void Launch(std::shared_ptr<HwCommand> hw_cmd) override {
+        ContextScope scope(ctx_);
         auto c = std::dynamic_pointer_cast<CudaCommand>(hw_cmd);
         XASSERT(c != nullptr, "a command that is not a CudaCommand was submitted to a CUDA queue");
         CUDA_ASSERT(c->LaunchOn(stream_, counter_));
@@ -73,6 +87,7 @@ public:
     }
 
     void Synchronize() override {
+        ContextScope scope(ctx_);
         CUresult r = CUDA_SUCCESS;
         const uint64_t t = counter_->Issue(stream_, &r);
         CUDA_ASSERT(r);
@@ -82,12 +97,14 @@ public:
     }
 
     void Deactivate() override {
+        ContextScope scope(ctx_);
         deactivate_ns_.store(NowNs());
         CUDA_ASSERT(Driver().cuStreamWriteValue32(ctrl_, flag_, 1, CU_STREAM_WRITE_VALUE_DEFAULT));
         stats_.deactivations.fetch_add(1, std::memory_order_relaxed);
     }
 
     void Reactivate(const CommandLog &log) override {
+        ContextScope scope(ctx_);
         const DriverApi &d = Driver();
         CUDA_ASSERT(d.cuStreamSynchronize(stream_));      // flushed kernels have published their cursors
         CUDA_ASSERT(d.cuStreamWriteValue32(ctrl_, flag_, 0, CU_STREAM_WRITE_VALUE_DEFAULT));

@@ -78,7 +78,7 @@ const DriverApi &Driver() {
         };
 #define LOAD(name) api.name = (decltype(api.name))need(#name, nullptr);
 #define LOAD_V(name, sym) api.name = (decltype(api.name))need(sym, #name);
-        LOAD(cuInit) LOAD(cuGetErrorString) LOAD(cuCtxGetCurrent) LOAD(cuCtxSetCurrent) LOAD(cuCtxGetDevice)
+        LOAD(cuInit) LOAD(cuGetErrorString) LOAD(cuCtxGetCurrent) LOAD(cuCtxSetCurrent) LOAD_V(cuCtxPushCurrent, "cuCtxPushCurrent_v2") LOAD_V(cuCtxPopCurrent, "cuCtxPopCurrent_v2") LOAD(cuCtxGetDevice)
         LOAD(cuCtxGetStreamPriorityRange) LOAD(cuCtxSynchronize) LOAD(cuDeviceGetAttribute) LOAD(cuStreamGetCtx)
         LOAD(cuStreamGetFlags) LOAD(cuStreamSynchronize) LOAD(cuStreamQuery) LOAD(cuStreamCreateWithPriority)
         LOAD_V(cuStreamDestroy, "cuStreamDestroy_v2") LOAD(cuStreamWaitEvent)

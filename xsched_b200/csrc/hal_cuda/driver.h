@@ -16,6 +16,8 @@ struct DriverApi {
     XSCHED_DRV(cuGetErrorString)
     XSCHED_DRV(cuCtxGetCurrent)
     XSCHED_DRV(cuCtxSetCurrent)
+    XSCHED_DRV(cuCtxPushCurrent)
+    XSCHED_DRV(cuCtxPopCurrent)
     XSCHED_DRV(cuCtxGetDevice)
     XSCHED_DRV(cuCtxGetStreamPriorityRange)
     XSCHED_DRV(cuCtxSynchronize)
