@@ -71,6 +71,41 @@ def build_xpk(force: bool = False, verbose: bool = False) -> Path:
     return out
 
 
+# Driver entry points the shim implements itself (by the name the library exports); everything else that
+# cuda.h declares is forwarded by a generated trampoline.
+SHIM_HANDLED = {
+    "cuLaunchKernel", "cuMemcpyAsync", "cuMemcpyHtoDAsync_v2", "cuMemcpyDtoHAsync_v2", "cuMemcpyDtoDAsync_v2", "cuMemsetD8Async",
+    "cuMemsetD32Async", "cuLaunchHostFunc", "cuEventRecord", "cuEventSynchronize", "cuEventQuery", "cuEventDestroy_v2",
+    "cuStreamWaitEvent", "cuStreamSynchronize", "cuStreamQuery", "cuCtxSynchronize", "cuMemFree_v2", "cuStreamCreate",
+    "cuStreamCreateWithPriority", "cuStreamDestroy_v2", "cuStreamBeginCapture_v2", "cuStreamEndCapture", "cuGetProcAddress",
+    "cuGetProcAddress_v2", "cuLaunchKernelEx", "cuLaunchCooperativeKernel", "cuMemAllocAsync", "cuMemFreeAsync", "cuMemcpy2DAsync_v2",
+    "cuMemcpyPeerAsync", "cuMemsetD16Async", "cuGraphLaunch", "cuStreamAddCallback", "cuMemcpy", "cuMemcpyDtoH_v2", "cuMemcpyHtoD_v2",
+    "cuMemcpyDtoD_v2",
+}
+
+
+def gen_shim_exports() -> Path:
+    """Write csrc/shim/shim_exports.inc: one XSHIM_FWD(name) per driver entry point named in cuda.h —
+    declared names, the versioned names their #defines map to, and the _ptds/_ptsz variants."""
+    import re
+    hdr = (Path(CUDA_HOME) / "include" / "cuda.h").read_text(errors="replace")
+    names = set(re.findall(r"CUresult\s+CUDAAPI\s+(cu[A-Z]\w+)\s*\(", hdr))
+    for a, b in re.findall(r"#define\s+(cu[A-Z]\w+)\s+(cu[A-Z]\w+)\s*$", hdr, flags=re.M):
+        names.add(a)
+        names.add(b)
+    for kind, arg in re.findall(r"#define\s+cu[A-Z]\w+\s+__CUDA_API_(PTDS|PTSZ)\((cu[A-Z]\w+)\)", hdr):
+        names.add(arg)
+        names.add(arg + ("_ptds" if kind == "PTDS" else "_ptsz"))
+        base = re.sub(r"_v\d+$", "", arg)
+        names.add(base)
+    names -= SHIM_HANDLED
+    out = CSRC / "shim" / "shim_exports.inc"
+    text = "// generated from cuda.h by xsched_b200/build.py (gen_shim_exports); do not edit\n" + "".join(f"XSHIM_FWD({n})\n" for n in sorted(names))
+    if not out.exists() or out.read_text() != text:
+        out.write_text(text)
+    return out
+
+
 def build_host(force: bool = False, verbose: bool = False) -> list[Path]:
     """Host libraries: libpreempt.so, libhalcuda.so, libshimcuda.so, xserver and the host-only lane."""
     outs: list[Path] = []
@@ -93,6 +128,8 @@ def build_host(force: bool = False, verbose: bool = False) -> list[Path]:
     so("libpreempt.so", ["utils", "sched", "preempt"], ["-ldl", "-lrt"])
     so("libhalhost.so", ["hal_host"], ["-lpreempt"])
     so("libhalcuda.so", ["hal_cuda"], ["-lpreempt", "-lxpk", "-ldl"])
+    if (CSRC / "shim" / "shim.cpp").exists():
+        hdrs.append(gen_shim_exports())
     so("libshimcuda.so", ["shim"], ["-lhalcuda", "-lpreempt", "-ldl"],
        extra=["-Wl,-soname,libcuda.so.1"])
 
@@ -139,6 +176,18 @@ def build_bench_worker(force: bool = False, verbose: bool = False) -> Path | Non
     return out
 
 
+def build_test_apps(force: bool = False, verbose: bool = False) -> Path | None:
+    """tests/apps/plain_streams — an XSched-unaware CUDA program the interposer tests run (cudart linked
+    dynamically-loaded driver: it finds "libcuda.so.1" through the loader path like any application)."""
+    src = ROOT / "tests" / "apps" / "plain_streams.cu"
+    out = ROOT / "tests" / "apps" / "plain_streams"
+    if not src.exists():
+        return None
+    if force or _stale(out, [src]):
+        _run([NVCC, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, src], verbose)
+    return out
+
+
 def build_lane_driver(force: bool = False, verbose: bool = False) -> Path | None:
     """oracle/lane_driver_new — the scenario runner linked against this repository's libraries
     (its twin linked against the reference core is built by oracle/build_ref.py)."""
@@ -174,6 +223,7 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
     build_xpk(force, verbose)
     build_host(force, verbose)
     build_bench_worker(force, verbose)
+    build_test_apps(force, verbose)
     build_oracle(force, verbose)
     build_lane_driver(force, verbose)
     build_oracle_ref(force, verbose)

@@ -61,13 +61,24 @@ CUresult CudaCommand::LaunchOn(CUstream stream, const std::shared_ptr<Completion
 CudaKernelLaunchCommand::CudaKernelLaunchCommand(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by,
                                                  unsigned bz, unsigned shmem, void **params, void **extra)
     : CudaCommand(preempt::kCommandPropertyNone), f_(f), g_{gx, gy, gz}, b_{bx, by, bz}, shmem_(shmem) {
+    CopyArgs(params, extra);
+}
+
+CudaKernelLaunchCommand::CudaKernelLaunchCommand(const CUlaunchConfig *c, CUfunction f, void **params, void **extra)
+    : CudaCommand(preempt::kCommandPropertyNone), f_(f), g_{c->gridDimX, c->gridDimY, c->gridDimZ},
+      b_{c->blockDimX, c->blockDimY, c->blockDimZ}, shmem_(c->sharedMemBytes), use_ex_(true) {
+    if (c->attrs && c->numAttrs) attrs_.assign(c->attrs, c->attrs + c->numAttrs);
+    CopyArgs(params, extra);
+}
+
+void CudaKernelLaunchCommand::CopyArgs(void **params, void **extra) {
     if (params != nullptr) {
         // Argument layout comes from the driver: offset and size of parameter i until it says "no more".
         std::vector<std::pair<size_t, size_t>> layout;
         size_t total = 0;
         for (size_t i = 0;; ++i) {
             size_t off = 0, sz = 0;
-            if (Driver().cuFuncGetParamInfo(f, i, &off, &sz) != CUDA_SUCCESS) break;
+            if (Driver().cuFuncGetParamInfo(f_, i, &off, &sz) != CUDA_SUCCESS) break;
             layout.emplace_back(off, sz);
             total = std::max(total, off + sz);
         }
@@ -78,7 +89,7 @@ CudaKernelLaunchCommand::CudaKernelLaunchCommand(CUfunction f, unsigned gx, unsi
             arg_ptrs_[i] = arg_bytes_.data() + layout[i].first;
         }
     } else if (extra != nullptr) {
-        // CU_LAUNCH_PARAM_BUFFER_POINTER / _SIZE / _END triple list.
+        // CU_LAUNCH_PARAM_BUFFER_POINTER / _SIZE / _END list.
         void *buf = nullptr;
         size_t size = 0;
         for (int i = 0; extra[i] != CU_LAUNCH_PARAM_END && i < 16; i += 2) {
@@ -92,15 +103,27 @@ CudaKernelLaunchCommand::CudaKernelLaunchCommand(CUfunction f, unsigned gx, unsi
 }
 
 CUresult CudaKernelLaunchCommand::Enqueue(CUstream stream) {
+    void **params = arg_ptrs_.empty() ? nullptr : arg_ptrs_.data();
+    void **extra = nullptr;
+    size_t size = extra_bytes_.size();
     if (use_extra_) {
-        size_t size = extra_bytes_.size();
         extra_[0] = CU_LAUNCH_PARAM_BUFFER_POINTER; extra_[1] = extra_bytes_.data();
         extra_[2] = CU_LAUNCH_PARAM_BUFFER_SIZE;    extra_[3] = &size;
         extra_[4] = CU_LAUNCH_PARAM_END;
-        return Driver().cuLaunchKernel(f_, g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, stream, nullptr, extra_);
+        extra = extra_;
+        params = nullptr;
     }
-    return Driver().cuLaunchKernel(f_, g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, stream,
-                                   arg_ptrs_.empty() ? nullptr : arg_ptrs_.data(), nullptr);
+    if (use_ex_) {
+        CUlaunchConfig c{};
+        c.gridDimX = g_[0]; c.gridDimY = g_[1]; c.gridDimZ = g_[2];
+        c.blockDimX = b_[0]; c.blockDimY = b_[1]; c.blockDimZ = b_[2];
+        c.sharedMemBytes = shmem_;
+        c.hStream = stream;
+        c.attrs = attrs_.empty() ? nullptr : attrs_.data();
+        c.numAttrs = (unsigned)attrs_.size();
+        return Driver().cuLaunchKernelEx(&c, f_, params, extra);
+    }
+    return Driver().cuLaunchKernel(f_, g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, stream, params, extra);
 }
 
 // ------------------------------------------------------------------------------------ copies, sets

@@ -56,6 +56,8 @@ class CudaKernelLaunchCommand final : public CudaCommand {
 public:
     CudaKernelLaunchCommand(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                             unsigned shmem, void **params, void **extra);
+    /// cuLaunchKernelEx form: the launch attributes (cluster shape, priority, ...) are copied as well.
+    CudaKernelLaunchCommand(const CUlaunchConfig *config, CUfunction f, void **params, void **extra);
     bool ParamsCopied() const { return ok_; }
 protected:
     CUresult Enqueue(CUstream stream) override;
@@ -68,6 +70,9 @@ private:
     void *extra_[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     bool use_extra_ = false;
     bool ok_ = true;
+    bool use_ex_ = false;
+    std::vector<CUlaunchAttribute> attrs_;
+    void CopyArgs(void **params, void **extra);
 };
 
 enum class CopyKind { kHtoD, kDtoH, kDtoD, kGeneric };

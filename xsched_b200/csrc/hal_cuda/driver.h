@@ -44,6 +44,7 @@ struct DriverApi {
     XSCHED_DRV(cuMemcpyDtoHAsync)
     XSCHED_DRV(cuMemcpyDtoDAsync)
     XSCHED_DRV(cuLaunchKernel)
+    XSCHED_DRV(cuLaunchKernelEx)
     XSCHED_DRV(cuLaunchHostFunc)
     XSCHED_DRV(cuFuncGetParamInfo)
     XSCHED_DRV(cuEventCreate)

@@ -1,0 +1,460 @@
+// libshimcuda.so — transparent interposer for the CUDA driver library.  Installed under the names
+// libcuda.so.1 / libcuda.so in a directory that is put first on LD_LIBRARY_PATH, it is what the CUDA
+// runtime (and therefore any framework) loads as "the driver".  Calls that enqueue work on a stream that
+// has an XQueue — cuLaunchKernel, cuMemcpy*Async, cuMemset*Async, cuEventRecord, cuStreamWaitEvent,
+// cuLaunchHostFunc — become HwCommands submitted to that XQueue and return CUDA_SUCCESS at once;
+// cuStreamSynchronize / cuEventSynchronize / cuEventQuery / cuStreamQuery / cuCtxSynchronize / cuMemFree
+// wait on (or ask) the XQueue; cuStreamCreate* / cuStreamDestroy create and destroy XQueues when
+// XSCHED_AUTO_XQUEUE=ON.  Every other driver entry point is forwarded untouched by a one-instruction
+// trampoline generated from the function list of cuda.h (shim_exports.inc).
+//
+// Behaviour follows the reference's shim (platforms/cuda/shim/src/shim.cpp:25-567, shim.h:20-105,
+// cuGetProcAddress override intercept.cpp:1108-1166): legacy-stream calls first drain XQueues of blocking
+// streams and then go straight to the driver; while a stream capture is open everything goes straight to
+// the driver.  Unlike the reference, the generic cuMemcpyAsync is routed too.  x86-64 only (trampolines).
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <list>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+#include <cuda.h>
+
+#include "hal_cuda/cuda_command.h"
+#include "hal_cuda/driver.h"
+#include "xsched/cuda/hal.h"
+#include "xsched/preempt/hal/hw_queue.h"
+#include "xsched/preempt/xqueue/xqueue.h"
+#include "xsched/protocol/def.h"
+#include "xsched/utils/xassert.h"
+
+using namespace xsched::cuda;
+using namespace xsched::preempt;
+
+// Marker looked for by the HAL's driver loader: a library exporting it is not the real driver.
+extern "C" {
+__attribute__((visibility("default"))) int XSchedShimMarker = 1;
+}
+
+namespace {
+
+// ---- statistics (dumped as JSON to $XSCHED_SHIM_STATS_FILE at exit) ----
+struct Stats {
+    std::atomic<uint64_t> launches_queued{0}, launches_direct{0}, copies_queued{0}, copies_direct{0}, events_queued{0},
+        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0};
+} g_stats;
+
+void DumpStats() {
+    const std::string path = GetEnv("XSCHED_SHIM_STATS_FILE");
+    if (path.empty()) return;
+    if (FILE *f = std::fopen(path.c_str(), "w")) {
+        std::fprintf(f, "{\"launches_queued\": %llu, \"launches_direct\": %llu, \"copies_queued\": %llu, \"copies_direct\": %llu, "
+                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu}\n",
+                     (unsigned long long)g_stats.launches_queued, (unsigned long long)g_stats.launches_direct,
+                     (unsigned long long)g_stats.copies_queued, (unsigned long long)g_stats.copies_direct,
+                     (unsigned long long)g_stats.events_queued, (unsigned long long)g_stats.syncs_via_xqueue,
+                     (unsigned long long)g_stats.streams_with_xqueue, (unsigned long long)g_stats.getproc_hooked);
+        std::fclose(f);
+    }
+}
+
+// ---- real entry points used by the handlers ----
+template <class F> F Real(const char *name) {
+    void *p = Driver().Sym(name);
+    XASSERT(p != nullptr, "the CUDA driver lacks %s", name);
+    return reinterpret_cast<F>(p);
+}
+#define REAL(fn, sym) static const auto real = Real<decltype(&fn)>(sym)
+
+std::atomic<int64_t> g_capturing{0};
+
+bool IsLegacy(CUstream s) { return s == nullptr || s == CU_STREAM_LEGACY; }
+
+// Work on the legacy default stream is ordered after everything on blocking streams: drain their XQueues.
+void DrainBlockingStreams() {
+    std::list<std::shared_ptr<XQueueWaitAllCommand>> markers;
+    XQueueManager::ForEach([&](std::shared_ptr<XQueue> xq) -> XResult {
+        unsigned flags = 0;
+        CUstream s = (CUstream)(uintptr_t)xq->GetHwQueue()->GetHandle();
+        if (Driver().cuStreamGetFlags(s, &flags) == CUDA_SUCCESS && (flags & CU_STREAM_NON_BLOCKING)) return kXSchedSuccess;
+        if (auto m = xq->SubmitWaitAll()) markers.push_back(std::move(m));
+        return kXSchedSuccess;
+    });
+    for (auto &m : markers) m->Wait();
+}
+
+// The XQueue to submit to, or nullptr when the call must go straight to the driver.
+std::shared_ptr<XQueue> Route(CUstream s) {
+    if (g_capturing.load(std::memory_order_relaxed) > 0) return nullptr;
+    if (IsLegacy(s)) { DrainBlockingStreams(); return nullptr; }
+    if (s == CU_STREAM_PER_THREAD) return nullptr;
+    return HwQueueManager::GetXQueue((HwQueueHandle)(uintptr_t)s);
+}
+
+std::mutex g_ev_mu;
+std::unordered_map<CUevent, std::shared_ptr<CudaEventRecordCommand>> g_events;   // event -> its newest record command
+
+std::shared_ptr<CudaEventRecordCommand> FindRecord(CUevent ev) {
+    std::lock_guard<std::mutex> lk(g_ev_mu);
+    auto it = g_events.find(ev);
+    return it == g_events.end() ? nullptr : it->second;
+}
+
+void AutoCreate(CUstream s) {
+    const XResult r = XQueueManager::AutoCreate([&](HwQueueHandle *hwq) { return CudaQueueCreate(hwq, s); });
+    if (r == kXSchedSuccess && HwQueueManager::GetXQueue((HwQueueHandle)(uintptr_t)s)) g_stats.streams_with_xqueue++;
+}
+
+CUresult Unsupported() { return CUDA_ERROR_NOT_SUPPORTED; }
+
+} // namespace
+
+// ======================================================================================= handlers
+extern "C" {
+#define SHIM_API __attribute__((visibility("default")))
+
+SHIM_API CUresult CUDAAPI cuLaunchKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
+                                         unsigned shmem, CUstream s, void **params, void **extra) {
+    REAL(cuLaunchKernel, "cuLaunchKernel");
+    auto xq = Route(s);
+    if (xq) {
+        auto cmd = std::make_shared<CudaKernelLaunchCommand>(f, gx, gy, gz, bx, by, bz, shmem, params, extra);
+        if (cmd->ParamsCopied()) {
+            xq->Submit(cmd);
+            g_stats.launches_queued++;
+            return CUDA_SUCCESS;
+        }
+        xq->WaitAll();       // argument block could not be copied: keep the order and launch directly
+    }
+    g_stats.launches_direct++;
+    return real(f, gx, gy, gz, bx, by, bz, shmem, s, params, extra);
+}
+
+SHIM_API CUresult CUDAAPI cuLaunchKernelEx(const CUlaunchConfig *config, CUfunction f, void **params, void **extra) {
+    if (config == nullptr) return CUDA_ERROR_INVALID_VALUE;
+    auto xq = Route(config->hStream);
+    if (xq) {
+        auto cmd = std::make_shared<CudaKernelLaunchCommand>(config, f, params, extra);
+        if (cmd->ParamsCopied()) {
+            xq->Submit(cmd);
+            g_stats.launches_queued++;
+            return CUDA_SUCCESS;
+        }
+        xq->WaitAll();
+    }
+    g_stats.launches_direct++;
+    return Driver().cuLaunchKernelEx(config, f, params, extra);
+}
+
+// Stream-ordered entry points that are not turned into commands: keep their order relative to queued
+// commands by draining the stream's XQueue first, then call the driver (synchronous, but correct).
+#define DRAIN_THEN_CALL(stream, sym, ...)                                   \
+    do {                                                                    \
+        if (auto xq_ = Route(stream)) { xq_->WaitAll(); g_stats.syncs_via_xqueue++; } \
+        REAL_BY_NAME(sym);                                                  \
+        return real(__VA_ARGS__);                                           \
+    } while (0)
+
+SHIM_API CUresult CUDAAPI cuLaunchCooperativeKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
+                                                    unsigned shmem, CUstream s, void **params) {
+#define REAL_BY_NAME(sym) REAL(cuLaunchCooperativeKernel, sym)
+    DRAIN_THEN_CALL(s, "cuLaunchCooperativeKernel", f, gx, gy, gz, bx, by, bz, shmem, s, params);
+#undef REAL_BY_NAME
+}
+SHIM_API CUresult CUDAAPI cuMemAllocAsync(CUdeviceptr *p, size_t n, CUstream s) {
+#define REAL_BY_NAME(sym) REAL(cuMemAllocAsync, sym)
+    DRAIN_THEN_CALL(s, "cuMemAllocAsync", p, n, s);
+#undef REAL_BY_NAME
+}
+SHIM_API CUresult CUDAAPI cuMemFreeAsync(CUdeviceptr p, CUstream s) {
+#define REAL_BY_NAME(sym) REAL(cuMemFreeAsync, sym)
+    DRAIN_THEN_CALL(s, "cuMemFreeAsync", p, s);
+#undef REAL_BY_NAME
+}
+SHIM_API CUresult CUDAAPI cuMemcpy2DAsync(const CUDA_MEMCPY2D *c, CUstream s) {
+#define REAL_BY_NAME(sym) REAL(cuMemcpy2DAsync, sym)
+    DRAIN_THEN_CALL(s, "cuMemcpy2DAsync_v2", c, s);
+#undef REAL_BY_NAME
+}
+SHIM_API CUresult CUDAAPI cuMemcpyPeerAsync(CUdeviceptr d, CUcontext dc, CUdeviceptr sp, CUcontext sc, size_t n, CUstream s) {
+#define REAL_BY_NAME(sym) REAL(cuMemcpyPeerAsync, sym)
+    DRAIN_THEN_CALL(s, "cuMemcpyPeerAsync", d, dc, sp, sc, n, s);
+#undef REAL_BY_NAME
+}
+SHIM_API CUresult CUDAAPI cuMemsetD16Async(CUdeviceptr d, unsigned short v, size_t n, CUstream s) {
+#define REAL_BY_NAME(sym) REAL(cuMemsetD16Async, sym)
+    DRAIN_THEN_CALL(s, "cuMemsetD16Async", d, v, n, s);
+#undef REAL_BY_NAME
+}
+SHIM_API CUresult CUDAAPI cuGraphLaunch(CUgraphExec g, CUstream s) {
+#define REAL_BY_NAME(sym) REAL(cuGraphLaunch, sym)
+    DRAIN_THEN_CALL(s, "cuGraphLaunch", g, s);
+#undef REAL_BY_NAME
+}
+SHIM_API CUresult CUDAAPI cuStreamAddCallback(CUstream s, CUstreamCallback cb, void *data, unsigned flags) {
+#define REAL_BY_NAME(sym) REAL(cuStreamAddCallback, sym)
+    DRAIN_THEN_CALL(s, "cuStreamAddCallback", s, cb, data, flags);
+#undef REAL_BY_NAME
+}
+// Synchronous copies imply the legacy stream: everything queued on blocking streams goes first.
+SHIM_API CUresult CUDAAPI cuMemcpy(CUdeviceptr d, CUdeviceptr sp, size_t n) {
+    REAL(cuMemcpy, "cuMemcpy");
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();
+    return real(d, sp, n);
+}
+SHIM_API CUresult CUDAAPI cuMemcpyDtoH(void *d, CUdeviceptr sp, size_t n) {
+    REAL(cuMemcpyDtoH, "cuMemcpyDtoH_v2");
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();
+    return real(d, sp, n);
+}
+SHIM_API CUresult CUDAAPI cuMemcpyHtoD(CUdeviceptr d, const void *sp, size_t n) {
+    REAL(cuMemcpyHtoD, "cuMemcpyHtoD_v2");
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();
+    return real(d, sp, n);
+}
+SHIM_API CUresult CUDAAPI cuMemcpyDtoD(CUdeviceptr d, CUdeviceptr sp, size_t n) {
+    REAL(cuMemcpyDtoD, "cuMemcpyDtoD_v2");
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();
+    return real(d, sp, n);
+}
+
+static CUresult CopyCommon(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t n, CUstream s) {
+    auto xq = Route(s);
+    if (xq) {
+        xq->Submit(std::make_shared<CudaMemcpyCommand>(kind, dst, src, n));
+        g_stats.copies_queued++;
+        return CUDA_SUCCESS;
+    }
+    g_stats.copies_direct++;
+    const DriverApi &d = Driver();
+    switch (kind) {
+    case CopyKind::kHtoD: return d.cuMemcpyHtoDAsync(dst, (const void *)src, n, s);
+    case CopyKind::kDtoH: return d.cuMemcpyDtoHAsync((void *)dst, src, n, s);
+    case CopyKind::kDtoD: return d.cuMemcpyDtoDAsync(dst, src, n, s);
+    default: return d.cuMemcpyAsync(dst, src, n, s);
+    }
+}
+SHIM_API CUresult CUDAAPI cuMemcpyAsync(CUdeviceptr dst, CUdeviceptr src, size_t n, CUstream s) { return CopyCommon(CopyKind::kGeneric, dst, src, n, s); }
+SHIM_API CUresult CUDAAPI cuMemcpyHtoDAsync(CUdeviceptr dst, const void *src, size_t n, CUstream s) { return CopyCommon(CopyKind::kHtoD, dst, (CUdeviceptr)(uintptr_t)src, n, s); }
+SHIM_API CUresult CUDAAPI cuMemcpyDtoHAsync(void *dst, CUdeviceptr src, size_t n, CUstream s) { return CopyCommon(CopyKind::kDtoH, (CUdeviceptr)(uintptr_t)dst, src, n, s); }
+SHIM_API CUresult CUDAAPI cuMemcpyDtoDAsync(CUdeviceptr dst, CUdeviceptr src, size_t n, CUstream s) { return CopyCommon(CopyKind::kDtoD, dst, src, n, s); }
+
+SHIM_API CUresult CUDAAPI cuMemsetD8Async(CUdeviceptr dst, unsigned char v, size_t n, CUstream s) {
+    if (auto xq = Route(s)) { xq->Submit(std::make_shared<CudaMemsetCommand>(dst, v, n, 1)); return CUDA_SUCCESS; }
+    return Driver().cuMemsetD8Async(dst, v, n, s);
+}
+SHIM_API CUresult CUDAAPI cuMemsetD32Async(CUdeviceptr dst, unsigned v, size_t n, CUstream s) {
+    if (auto xq = Route(s)) { xq->Submit(std::make_shared<CudaMemsetCommand>(dst, v, n, 4)); return CUDA_SUCCESS; }
+    return Driver().cuMemsetD32Async(dst, v, n, s);
+}
+
+SHIM_API CUresult CUDAAPI cuLaunchHostFunc(CUstream s, CUhostFn fn, void *data) {
+    if (auto xq = Route(s)) { xq->Submit(std::make_shared<CudaHostFuncCommand>(fn, data)); return CUDA_SUCCESS; }
+    return Driver().cuLaunchHostFunc(s, fn, data);
+}
+
+SHIM_API CUresult CUDAAPI cuEventRecord(CUevent ev, CUstream s) {
+    auto xq = Route(s);
+    if (!xq) {
+        { std::lock_guard<std::mutex> lk(g_ev_mu); g_events.erase(ev); }
+        return Driver().cuEventRecord(ev, s);
+    }
+    auto cmd = std::make_shared<CudaEventRecordCommand>(ev);
+    { std::lock_guard<std::mutex> lk(g_ev_mu); g_events[ev] = cmd; }
+    xq->Submit(cmd);
+    g_stats.events_queued++;
+    return CUDA_SUCCESS;
+}
+
+SHIM_API CUresult CUDAAPI cuEventSynchronize(CUevent ev) {
+    if (auto rec = FindRecord(ev)) { rec->Wait(); return CUDA_SUCCESS; }
+    return Driver().cuEventSynchronize(ev);
+}
+
+SHIM_API CUresult CUDAAPI cuEventQuery(CUevent ev) {
+    if (auto rec = FindRecord(ev)) {
+        if (rec->GetState() >= kCommandStateCompleted) return CUDA_SUCCESS;
+        if (rec->GetState() < kCommandStateInFlight) return CUDA_ERROR_NOT_READY;
+    }
+    return Driver().cuEventQuery(ev);
+}
+
+SHIM_API CUresult CUDAAPI cuEventDestroy(CUevent ev) {
+    REAL(cuEventDestroy, "cuEventDestroy_v2");
+    std::shared_ptr<CudaEventRecordCommand> rec;
+    { std::lock_guard<std::mutex> lk(g_ev_mu); auto it = g_events.find(ev); if (it != g_events.end()) { rec = it->second; g_events.erase(it); } }
+    if (rec) rec->WaitUntil(kCommandStateInFlight);     // the record must have reached the driver before the event goes away
+    return real(ev);
+}
+
+SHIM_API CUresult CUDAAPI cuStreamWaitEvent(CUstream s, CUevent ev, unsigned flags) {
+    auto rec = FindRecord(ev);
+    auto xq = Route(s);
+    if (xq) {
+        xq->Submit(std::make_shared<CudaEventWaitCommand>(ev, flags, rec));
+        return CUDA_SUCCESS;
+    }
+    if (rec) rec->WaitUntil(kCommandStateInFlight);     // the record is still pending in another XQueue
+    return Driver().cuStreamWaitEvent(s, ev, flags);
+}
+
+SHIM_API CUresult CUDAAPI cuStreamSynchronize(CUstream s) {
+    if (auto xq = Route(s)) {
+        xq->WaitAll();
+        g_stats.syncs_via_xqueue++;
+        return CUDA_SUCCESS;
+    }
+    return Driver().cuStreamSynchronize(s);
+}
+
+SHIM_API CUresult CUDAAPI cuStreamQuery(CUstream s) {
+    if (auto xq = Route(s)) return xq->Query() == kQueueStateIdle ? CUDA_SUCCESS : CUDA_ERROR_NOT_READY;
+    return Driver().cuStreamQuery(s);
+}
+
+SHIM_API CUresult CUDAAPI cuCtxSynchronize(void) {
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();
+    return Driver().cuCtxSynchronize();
+}
+
+SHIM_API CUresult CUDAAPI cuMemFree(CUdeviceptr p) {
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();     // queued commands may still use the memory
+    return Driver().cuMemFree(p);
+}
+
+SHIM_API CUresult CUDAAPI cuStreamCreate(CUstream *s, unsigned flags) {
+    REAL(cuStreamCreate, "cuStreamCreate");
+    const CUresult r = real(s, flags);
+    if (r == CUDA_SUCCESS) AutoCreate(*s);
+    return r;
+}
+
+SHIM_API CUresult CUDAAPI cuStreamCreateWithPriority(CUstream *s, unsigned flags, int prio) {
+    const CUresult r = Driver().cuStreamCreateWithPriority(s, flags, prio);
+    if (r == CUDA_SUCCESS) AutoCreate(*s);
+    return r;
+}
+
+SHIM_API CUresult CUDAAPI cuStreamDestroy(CUstream s) {
+    if (HwQueueManager::GetXQueue((HwQueueHandle)(uintptr_t)s)) XQueueManager::AutoDestroy((HwQueueHandle)(uintptr_t)s);
+    return Driver().cuStreamDestroy(s);
+}
+
+SHIM_API CUresult CUDAAPI cuStreamBeginCapture(CUstream s, CUstreamCaptureMode mode) {
+    REAL(cuStreamBeginCapture, "cuStreamBeginCapture_v2");
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();     // nothing queued may leak into the graph
+    g_capturing.fetch_add(1);
+    const CUresult r = real(s, mode);
+    if (r != CUDA_SUCCESS) g_capturing.fetch_sub(1);
+    return r;
+}
+
+SHIM_API CUresult CUDAAPI cuStreamEndCapture(CUstream s, CUgraph *g) {
+    REAL(cuStreamEndCapture, "cuStreamEndCapture");
+    const CUresult r = real(s, g);
+    if (g_capturing.load() > 0) g_capturing.fetch_sub(1);
+    return r;
+}
+
+// ---- cuGetProcAddress: the CUDA runtime resolves everything through it ----
+struct Hook { const char *name; void *fn; int min_version; };
+static const Hook kHooks[] = {
+    {"cuLaunchKernel", (void *)&cuLaunchKernel, 4000},
+    {"cuLaunchKernelEx", (void *)&cuLaunchKernelEx, 11060},
+    {"cuLaunchCooperativeKernel", (void *)&cuLaunchCooperativeKernel, 9000},
+    {"cuMemAllocAsync", (void *)&cuMemAllocAsync, 11020},
+    {"cuMemFreeAsync", (void *)&cuMemFreeAsync, 11020},
+    {"cuMemcpy2DAsync", (void *)&cuMemcpy2DAsync, 3020},
+    {"cuMemcpyPeerAsync", (void *)&cuMemcpyPeerAsync, 4000},
+    {"cuMemsetD16Async", (void *)&cuMemsetD16Async, 3020},
+    {"cuGraphLaunch", (void *)&cuGraphLaunch, 10000},
+    {"cuStreamAddCallback", (void *)&cuStreamAddCallback, 5000},
+    {"cuMemcpy", (void *)&cuMemcpy, 4000},
+    {"cuMemcpyDtoH", (void *)&cuMemcpyDtoH, 3020},
+    {"cuMemcpyHtoD", (void *)&cuMemcpyHtoD, 3020},
+    {"cuMemcpyDtoD", (void *)&cuMemcpyDtoD, 3020},
+    {"cuMemcpyAsync", (void *)&cuMemcpyAsync, 4000},
+    {"cuMemcpyHtoDAsync", (void *)&cuMemcpyHtoDAsync, 3020},
+    {"cuMemcpyDtoHAsync", (void *)&cuMemcpyDtoHAsync, 3020},
+    {"cuMemcpyDtoDAsync", (void *)&cuMemcpyDtoDAsync, 3020},
+    {"cuMemsetD8Async", (void *)&cuMemsetD8Async, 3020},
+    {"cuMemsetD32Async", (void *)&cuMemsetD32Async, 3020},
+    {"cuLaunchHostFunc", (void *)&cuLaunchHostFunc, 10000},
+    {"cuEventRecord", (void *)&cuEventRecord, 2000},
+    {"cuEventSynchronize", (void *)&cuEventSynchronize, 2000},
+    {"cuEventQuery", (void *)&cuEventQuery, 2000},
+    {"cuEventDestroy", (void *)&cuEventDestroy, 4000},
+    {"cuStreamWaitEvent", (void *)&cuStreamWaitEvent, 3020},
+    {"cuStreamSynchronize", (void *)&cuStreamSynchronize, 2000},
+    {"cuStreamQuery", (void *)&cuStreamQuery, 2000},
+    {"cuCtxSynchronize", (void *)&cuCtxSynchronize, 2000},
+    {"cuMemFree", (void *)&cuMemFree, 3020},
+    {"cuStreamCreate", (void *)&cuStreamCreate, 2000},
+    {"cuStreamCreateWithPriority", (void *)&cuStreamCreateWithPriority, 5050},
+    {"cuStreamDestroy", (void *)&cuStreamDestroy, 4000},
+    {"cuStreamBeginCapture", (void *)&cuStreamBeginCapture, 10010},
+    {"cuStreamEndCapture", (void *)&cuStreamEndCapture, 10000},
+};
+
+static void *FindHook(const char *symbol, int version, cuuint64_t flags);
+
+SHIM_API CUresult CUDAAPI cuGetProcAddress(const char *symbol, void **pfn, int version, cuuint64_t flags, CUdriverProcAddressQueryResult *status) {
+    REAL(cuGetProcAddress, "cuGetProcAddress_v2");
+    const CUresult r = real(symbol, pfn, version, flags, status);
+    if (r != CUDA_SUCCESS || pfn == nullptr || *pfn == nullptr || symbol == nullptr) return r;
+    if (void *h = FindHook(symbol, version, flags)) { *pfn = h; g_stats.getproc_hooked++; }
+    return r;
+}
+
+#undef cuGetProcAddress
+SHIM_API CUresult CUDAAPI cuGetProcAddress(const char *symbol, void **pfn, int version, cuuint64_t flags) {
+    typedef CUresult(CUDAAPI * Fn)(const char *, void **, int, cuuint64_t);
+    static const Fn real = Real<Fn>("cuGetProcAddress");
+    const CUresult r = real(symbol, pfn, version, flags);
+    if (r != CUDA_SUCCESS || pfn == nullptr || *pfn == nullptr || symbol == nullptr) return r;
+    if (void *h = FindHook(symbol, version, flags)) { *pfn = h; g_stats.getproc_hooked++; }
+    return r;
+}
+
+static void *FindHook(const char *symbol, int version, cuuint64_t flags) {
+    // Per-thread-default-stream entry points are left to the driver (their NULL stream is not the legacy one).
+    if (flags & CU_GET_PROC_ADDRESS_PER_THREAD_DEFAULT_STREAM) return nullptr;
+    if (std::strcmp(symbol, "cuGetProcAddress") == 0) {
+        extern CUresult CUDAAPI cuGetProcAddress_v2(const char *, void **, int, cuuint64_t, CUdriverProcAddressQueryResult *);
+        return version >= 12000 ? (void *)&cuGetProcAddress_v2 : (void *)&cuGetProcAddress;
+    }
+    for (const Hook &h : kHooks)
+        if (std::strcmp(symbol, h.name) == 0) return version >= h.min_version ? h.fn : nullptr;
+    return nullptr;
+}
+
+} // extern "C"
+
+// ======================================================================================= forwarders
+// One pointer + one `jmp *pointer(%rip)` per driver entry point that is not handled above.
+#define XSHIM_FWD(name)                                                                  \
+    extern "C" { __attribute__((visibility("hidden"))) void *xshim_ptr_##name = nullptr; } \
+    asm(".text\n.globl " #name "\n.type " #name ", @function\n" #name ":\n\tjmp *xshim_ptr_" #name "(%rip)\n.size " #name ", .-" #name "\n");
+#include "shim_exports.inc"
+#undef XSHIM_FWD
+
+namespace {
+struct FwdEntry { const char *name; void **slot; };
+#define XSHIM_FWD(name) {#name, &xshim_ptr_##name},
+const FwdEntry kForwarders[] = {
+#include "shim_exports.inc"
+};
+#undef XSHIM_FWD
+
+struct Init {
+    Init() {
+        const DriverApi &d = Driver();
+        for (const FwdEntry &e : kForwarders) {
+            void *p = d.Sym(e.name);
+            *e.slot = p ? p : (void *)&Unsupported;
+        }
+        std::atexit(DumpStats);
+    }
+} g_init __attribute__((init_priority(200)));
+} // namespace
