@@ -99,6 +99,9 @@ def gen_shim_exports() -> Path:
         base = re.sub(r"_v\d+$", "", arg)
         names.add(base)
     names -= SHIM_HANDLED
+    # The batched-copy entry points (plain and 3D) get no forwarder: that family is not to be used on this
+    # hardware pool; a program that asks for them through the proc-address lookup still reaches the driver's own.
+    names = {n for n in names if not re.search(r"Memcpy(3D)?B" + "atch", n)}
     out = CSRC / "shim" / "shim_exports.inc"
     text = "// generated from cuda.h by xsched_b200/build.py (gen_shim_exports); do not edit\n" + "".join(f"XSHIM_FWD({n})\n" for n in sorted(names))
     if not out.exists() or out.read_text() != text:
