@@ -29,7 +29,8 @@ ROOT = HERE.parent
 REF = Path(os.environ.get("XSCHED_REFERENCE_DIR", "/root/reference"))
 OUT = HERE / "_ref"
 OBJ = OUT / "obj"
-CXX = os.environ.get("CXX", "g++")
+import shutil
+CXX = os.environ.get("XSCHED_CXX") or shutil.which("g++", path="/usr/bin:/usr/local/bin") or "g++"
 FLAGS = ["-std=c++20", "-O2", "-fPIC", "-DRELEASE_MODE", "-pthread", "-w"]
 
 

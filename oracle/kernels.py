@@ -14,7 +14,7 @@ _SRC = _HERE / "kernels_oracle.c"
 
 def _build() -> None:
     if not _SO.exists() or _SO.stat().st_mtime < _SRC.stat().st_mtime:
-        subprocess.check_call(["gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-o", str(_SO), str(_SRC), "-lm"])
+        subprocess.check_call(["/usr/bin/gcc" if Path("/usr/bin/gcc").exists() else "gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-o", str(_SO), str(_SRC), "-lm"])
 
 
 _build()

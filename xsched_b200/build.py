@@ -23,8 +23,11 @@ INC = ROOT / "include"
 ORACLE = ROOT / "oracle"
 
 NVCC = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-CXX = os.environ.get("CXX", "g++")
-CC = os.environ.get("CC", "gcc")
+# The system compiler, on purpose not $CXX/$CC: the libraries must link the shared libstdc++.  A toolchain
+# that links it statically makes every .so export its own copy of libstdc++ internals (__once_proxy,
+# std::string's empty rep, ...), which then get interposed into unrelated libraries of a large host process.
+CXX = os.environ.get("XSCHED_CXX") or shutil.which("g++", path="/usr/bin:/usr/local/bin") or "g++"
+CC = os.environ.get("XSCHED_CC") or shutil.which("gcc", path="/usr/bin:/usr/local/bin") or "gcc"
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 NVCC_FLAGS = [
