@@ -1,18 +1,24 @@
 // Preemptible persistent bf16 GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T, fp32 accumulate.
 //
-// Tensor-pipe bound: 2*M*N*K flop.  One CTA per SM owns a 128x256 output tile at a time:
+// Tensor-pipe bound: 2*M*N*K flop.  One CTA per SM owns a 256x256 output tile at a time:
 //
 //   warp 0 (one lane)   claims tiles (xpk::claim_tile: flag poll + ticket), publishes the tile
-//                       id on a 4-slot ring, and streams 128x64 A / 256x64 B k-blocks into a
-//                       4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte
+//                       id on a 4-slot ring, and streams 256x64 A / 256x64 B k-blocks (64 KB) into
+//                       a 3-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte
 //                       swizzle, no multicast: every CTA fetches its own operands);
 //   warp 1 (one lane)   issues tcgen05.mma.cta_group::1.kind::f16 (M128 N256 K16) from
-//                       shared-memory descriptors into one of two 256-column fp32 accumulators
-//                       in tensor memory; tcgen05.commit releases the smem stage / publishes
-//                       the accumulator through mbarriers;
-//   warps 2-5           read the finished accumulator with tcgen05.ld (32 lanes x 32 columns
-//                       per instruction), round to bf16 and store rows to global memory while
-//                       warp 1 already accumulates the next tile in the other buffer.
+//                       shared-memory descriptors: per K=16 step one MMA for rows 0-127 and one
+//                       for rows 128-255, both reading the same B tile, into two 256-column fp32
+//                       accumulators that together fill tensor memory (512 columns);
+//                       tcgen05.commit releases the smem stage / publishes the accumulators;
+//   warps 2-9           two groups of four warps, one per accumulator, read it with tcgen05.ld
+//                       (32 lanes x 32 columns per instruction), round to bf16 and store rows.
+//
+// A 256x256 tile moves 64 KB of operands per 64-deep k-block for 2*256*256*64 flop — one third less
+// L2->SM traffic per flop than a 128x256 tile, which measured as the limiter of that shape (tensor pipe
+// 74 % busy at 15 TB/s of operand traffic over the chip).  The price: both accumulators belong to the
+// same tile, so the epilogue no longer overlaps the next tile's MMAs (it overlaps its TMA prefetch);
+// eight epilogue warps keep that window to a few microseconds per ~120 us tile.
 //
 // Preemption.  Between tiles the producer stops claiming once the flag is up; tiles already
 // claimed are finished.  With kAbort it also polls the flag every 8 k-blocks inside a tile
@@ -32,17 +38,19 @@
 
 namespace xpk {
 
-constexpr int kBM = 128, kBN = 256, kBK = 64;
-constexpr int kStages = 4;
-constexpr int kAccBufs = 2;
+constexpr int kBM = 256, kBN = 256, kBK = 64;   // CTA tile
+constexpr int kMmaM = 128;                      // rows per MMA / per accumulator
+constexpr int kStages = 3;
+constexpr int kAccBufs = 2;                     // the two row-halves of one tile
 constexpr int kSchedSlots = 4;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kRasterGroup = 16;
-constexpr uint32_t kABytes = kBM * kBK * 2;          // 16 KiB
+constexpr uint32_t kABytes = kBM * kBK * 2;          // 32 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;          // 32 KiB
 constexpr uint32_t kTmemCols = 512;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-constexpr int kAbortPollEvery = 8;
+constexpr int kAbortPollEvery = 4;
 
 constexpr uint32_t kErrGemmProducer = 0x60000001u;
 constexpr uint32_t kErrGemmMma      = 0x60000002u;
@@ -52,8 +60,8 @@ constexpr uint32_t kErrGemmDrain    = 0x60000004u;
 struct GemmShared {
     unsigned long long full[kStages];
     unsigned long long empty[kStages];
-    unsigned long long tmem_full[kAccBufs];
-    unsigned long long tmem_empty[kAccBufs];
+    unsigned long long tmem_full;                 // both accumulators of the tile are complete
+    unsigned long long tmem_empty[kAccBufs];      // one per accumulator: its epilogue group has drained it
     unsigned long long sched_full[kSchedSlots];
     unsigned long long sched_empty[kSchedSlots];
     unsigned long long drain;
@@ -125,7 +133,7 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     return d;
 }
 // Instruction descriptor for kind::f16: D fp32, A/B bf16, both K-major, N=256, M=128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kMmaM >> 4) << 24);
 
 __device__ __forceinline__ unsigned long long gemm_time_ns() {
     unsigned long long t;
@@ -175,7 +183,7 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
     GemmShared *sh = reinterpret_cast<GemmShared *>(smem + kStages * (kABytes + kBBytes));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t m_tiles = M / kBM, n_tiles = N / kBN;
+    const uint32_t m_tiles = (M + kBM - 1) / kBM, n_tiles = N / kBN;   // M is a multiple of 128: the last row-block may be half full
     const uint32_t k_blocks = K / kBK;
     const unsigned long long total_tiles = (unsigned long long)m_tiles * n_tiles;
     volatile uint32_t *v_abort = &sh->abort;
@@ -194,8 +202,9 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
     }
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
-        for (int i = 0; i < kAccBufs; ++i) { mbar_init(&sh->tmem_full[i], 1); mbar_init(&sh->tmem_empty[i], 4); }
-        for (int i = 0; i < kSchedSlots; ++i) { mbar_init(&sh->sched_full[i], 1); mbar_init(&sh->sched_empty[i], 5); }
+        mbar_init(&sh->tmem_full, 1);
+        for (int i = 0; i < kAccBufs; ++i) mbar_init(&sh->tmem_empty[i], 4);
+        for (int i = 0; i < kSchedSlots; ++i) { mbar_init(&sh->sched_full[i], 1); mbar_init(&sh->sched_empty[i], 1 + kEpiWarps); }
         mbar_init(&sh->drain, 1);
         sh->abort = 0;
         sh->abort_kseq = ~0ull;
@@ -279,12 +288,12 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
                 const unsigned long long tile = sh->sched_tile[slot];
                 mbar_arrive(&sh->sched_empty[slot]);
                 if (tile == kNoTile) break;
-                const int acc = (int)(tseq % kAccBufs);
-                const uint32_t aph = (uint32_t)((tseq / kAccBufs) & 1);
-                if (!bounded_wait(&sh->tmem_empty[acc], aph ^ 1u, sh, ctl, kErrGemmMma,
-                                  [&] { return *v_abort == 2u; })) break;
+                // Both accumulators must have been drained by the previous tile's epilogue.
+                const uint32_t aph = (uint32_t)(tseq & 1);
+                if (!bounded_wait(&sh->tmem_empty[0], aph ^ 1u, sh, ctl, kErrGemmMma, [&] { return *v_abort == 2u; })) break;
+                if (!bounded_wait(&sh->tmem_empty[1], aph ^ 1u, sh, ctl, kErrGemmMma, [&] { return *v_abort == 2u; })) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)acc * kBN;
+                const uint32_t d_tmem0 = tmem_base, d_tmem1 = tmem_base + (uint32_t)kBN;
                 bool abandoned = false;
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                     const int stage = (int)(kseq % kStages);
@@ -297,19 +306,22 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + stage * kABytes);
                     const uint32_t b_addr = smem_u32(smem_b + stage * kBBytes);
-                    const uint64_t adesc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t adesc0 = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t adesc1 = make_kmajor_sw128_desc(a_addr + kMmaM * kBK * 2);   // rows 128..255
                     const uint64_t bdesc = make_kmajor_sw128_desc(b_addr);
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k) {
                         // +32 bytes per K=16 step inside the 128-byte swizzle atom (address field is >>4).
-                        tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), kIdesc, (kb | (uint32_t)k) != 0u);
+                        const uint32_t acc_flag = (kb | (uint32_t)k) != 0u;
+                        tc_mma_bf16(d_tmem0, adesc0 + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), kIdesc, acc_flag);
+                        tc_mma_bf16(d_tmem1, adesc1 + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), kIdesc, acc_flag);
                     }
                     issued_any = true;
                     tc_commit(&sh->empty[stage]);
                     ++kseq;
                 }
                 if (abandoned) break;
-                tc_commit(&sh->tmem_full[acc]);
+                tc_commit(&sh->tmem_full);
                 ++tseq;
             }
             // All issued MMAs must have retired before tensor memory is freed.
@@ -320,7 +332,8 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
         }
         __syncwarp();
     } else {
-        // ======================= epilogue (warps 2..5) =======================
+        // ======================= epilogue (warps 2..9: two groups of four) =======================
+        const uint32_t half = (uint32_t)(warp - 2) / 4u;         // which accumulator / row-half of the tile
         const uint32_t quarter = (uint32_t)(warp & 3);           // TMEM lanes [32q, 32q+32)
         unsigned long long tseq = 0;
         while (true) {
@@ -334,41 +347,42 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->sched_empty[slot]);
             if (tile == kNoTile) break;
-            const int acc = (int)(tseq % kAccBufs);
-            const uint32_t aph = (uint32_t)((tseq / kAccBufs) & 1);
-            ok = bounded_wait(&sh->tmem_full[acc], aph, sh, ctl, kErrGemmEpilogue,
+            const uint32_t aph = (uint32_t)(tseq & 1);
+            ok = bounded_wait(&sh->tmem_full, aph, sh, ctl, kErrGemmEpilogue,
                               [&] { return *v_abort == 2u || (*v_abort == 1u && tseq >= *(volatile unsigned long long *)&sh->abort_tile_seq); });
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             uint32_t m_blk, n_blk;
             tile_coords(tile, m_tiles, n_tiles, m_blk, n_blk);
-            const uint32_t row = m_blk * kBM + quarter * 32u + (uint32_t)lane;
-            __nv_bfloat16 *crow = C + (size_t)row * N + (size_t)n_blk * kBN;
-            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + (uint32_t)acc * kBN;
+            const uint32_t row = m_blk * kBM + half * kMmaM + quarter * 32u + (uint32_t)lane;
+            if (m_blk * kBM + half * kMmaM < M) {                    // the last row-block may have only its first half
+                __nv_bfloat16 *crow = C + (size_t)row * N + (size_t)n_blk * kBN;
+                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + half * (uint32_t)kBN;
 #pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
-                uint32_t r[32];
-                tc_ld32(taddr + (uint32_t)c, r);
-                tc_wait_ld();
-                uint4 *dst = reinterpret_cast<uint4 *>(crow + c);
+                for (int c = 0; c < kBN; c += 32) {
+                    uint32_t r[32];
+                    tc_ld32(taddr + (uint32_t)c, r);
+                    tc_wait_ld();
+                    uint4 *dst = reinterpret_cast<uint4 *>(crow + c);
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    uint4 o;
-                    __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                    __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                    __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                    __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                    o.x = *reinterpret_cast<uint32_t *>(&p0);
-                    o.y = *reinterpret_cast<uint32_t *>(&p1);
-                    o.z = *reinterpret_cast<uint32_t *>(&p2);
-                    o.w = *reinterpret_cast<uint32_t *>(&p3);
-                    dst[v] = o;
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                        __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                        o.x = *reinterpret_cast<uint32_t *>(&p0);
+                        o.y = *reinterpret_cast<uint32_t *>(&p1);
+                        o.z = *reinterpret_cast<uint32_t *>(&p2);
+                        o.w = *reinterpret_cast<uint32_t *>(&p3);
+                        dst[v] = o;
+                    }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
+            if (lane == 0) mbar_arrive(&sh->tmem_empty[half]);
             if (warp == 2 && lane == 0) ++tiles_done;
             ++tseq;
         }
@@ -406,7 +420,7 @@ int gemm_make_map(void *map_out, const void *base, uint64_t rows, uint64_t cols,
     if (!fn) return 1;
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};     // rows past the end of the tensor read as zero
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn((CUtensorMap *)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -423,7 +437,7 @@ cudaError_t gemm_prepare() {
     return cudaFuncSetAttribute(gemm_bf16_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
 }
 
-unsigned long long gemm_tiles(uint32_t M, uint32_t N) { return (unsigned long long)(M / kBM) * (N / kBN); }
+unsigned long long gemm_tiles(uint32_t M, uint32_t N) { return (unsigned long long)((M + kBM - 1) / kBM) * (N / kBN); }
 
 cudaError_t launch_gemm(bool preemptible, bool abort_inflight, Ctl *ctl, const void *map_a, const void *map_b,
                         void *C, uint32_t M, uint32_t N, uint32_t K, unsigned long long launch_no, int grid,

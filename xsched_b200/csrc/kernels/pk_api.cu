@@ -274,7 +274,7 @@ xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void 
             d->gemm_ready = true;
         }
     }
-    if (xpk::gemm_make_map(t->map_a, A, M, K, 128) != 0 || xpk::gemm_make_map(t->map_b, B, N, K, 256) != 0) {
+    if (xpk::gemm_make_map(t->map_a, A, M, K, 256) != 0 || xpk::gemm_make_map(t->map_b, B, N, K, 256) != 0) {
         task_free(t);
         return XPK_ERR_CUDA;
     }
