@@ -126,6 +126,7 @@ def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, 
     """LP process + HP process under the (already running) xserver.  Returns (hp_json, lp_json)."""
     import tempfile
     env = base_env(ns, "GLB")
+    hp_env = dict(env, XSCHED_IPC_SPIN="OFF")      # operations for the HP process are never urgent: do not burn a core on them
     lp_err = tempfile.TemporaryFile(mode="w+")
     lp = subprocess.Popen(worker_cmd("lp", device, level=level, prio=0, duration_s=3600, warmup_s=0.5, **lp_kw),
                           stdout=subprocess.PIPE, stderr=lp_err, text=True, env=env)
@@ -150,7 +151,7 @@ def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, 
         # budget: every request takes at most a few periods even when things go badly
         hp_timeout = 60 + (steps + warmup) * period_us * 20 / 1e6
         hp = run_json(worker_cmd("hp", device, level=level, prio=1, count=steps + warmup, period_us=period_us, hp_n=HP_N,
-                                 e2e=int(e2e)), env, timeout=hp_timeout)[-1]
+                                 e2e=int(e2e)), hp_env, timeout=hp_timeout)[-1]
         mark(f"corun level {level}: HP done")
     finally:
         lp.send_signal(signal.SIGTERM)
@@ -194,7 +195,9 @@ def gemm_roofline(device: int) -> tuple[dict, int]:
     return ({"bound": "tensor", "kernel": "gemm_bf16_kernel<preemptible, abort>", "achieved": round(achieved, 1),
              "peak": pk_["bf16_tflops"], "peak_source": pk_["source"] + " bf16_tflops (burst: kernel timed alone)", "unit": "TFLOP/s",
              "frac": round(achieved / pk_["bf16_tflops"], 4), "avg_launch_ms": round(avg, 4), "median_launch_ms": round(ms[len(ms) // 2], 4),
-             "traffic": None}, reps + 5)
+             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
+             # capture summarised in profiles/gemm_bf16_8192_ncu.md (algorithmic minimum: 402.7 MB)
+             "traffic": 940.8e6, "traffic_source": "ncu, profiles/gemm_bf16_8192_ncu.md"}, reps + 5)
 
 
 def reference_config0(level: int, lp_count: int, threshold: int = 16, batch: int = 8, lp_us: int = 1000, hp_us: int = 2000,
@@ -292,7 +295,7 @@ def main() -> None:
         # ---- standalone phases (untimed with respect to the step clock) ----
         env_alone = base_env(ns, "APP")
         mark("standalone phases")
-        hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(100, args.steps // 2), period_us=PERIOD_US, hp_n=HP_N), env_alone, 120)[-1]
+        hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(500, args.steps), period_us=PERIOD_US, hp_n=HP_N), env_alone, 180)[-1]
         lp_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **lp_kw), env_alone, 120)[-1]
         launches += hp_alone["xpk_launches"] + lp_alone["xpk_launches"]
         lat = run_json(worker_cmd("preempt-latency", device, level=2, count=300, **lp_kw), env_alone, 120)[-1]
@@ -384,6 +387,7 @@ def main() -> None:
                    "lp": "persistent preemptible bf16 GEMM 8192^3 in a loop", "hp": "fp32 vector add, 64 Mi elements",
                    "l2": "LP operands+output 384 MiB and HP arrays 768 MiB both exceed the 126 MB L2 (no flush needed)", "xserver": 1},
         "hp_p99_us": round(worst["hp_p99"], 2), "hp_standalone_p99_us": round(worst["alone_p99"], 2),
+        "hp_p50_us": hp_co["p50_us"], "hp_standalone_p50_us": hp_alone["p50_us"], "hp_p50_ratio": round(hp_co["p50_us"] / hp_alone["p50_us"], 4),
         "preempt_latency_us": round(max(r["preempt_p99"] for r in allr), 2),
         "preempt_latency": {"p50_us": lat["preempt_p50_us"], "p95_us": lat["preempt_p95_us"], "p99_us": lat["preempt_p99_us"],
                             "definition": "wall time of XQueueSuspend(xq, kQueueSuspendFlagSyncHwQueue), 300 samples at random moments"},
