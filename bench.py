@@ -268,6 +268,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--level1", action="store_true", help="also run the co-run phase at preemption level 1")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-config3", action="store_true", help="skip the triad-vs-sort leg (BASELINE config 3)")
     ap.add_argument("--no-variants", action="store_true", help="skip the one-process and native-priority comparison runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -334,6 +335,37 @@ def main() -> None:
                                                "bg_kept_pct": round(100 * lp_b["rate"] / lp_alone["rate"], 2), "bit_exact": lp_b["bit_exact"]}
             extra["native_stream_priority"] = {"hp_p99_us": nat["p99_us"], "hp_p50_us": nat["p50_us"], "hp_standalone_p99_us": nat["standalone_p99_us"],
                                                "ratio": nat["ratio_p99"]}
+        if not args.no_config3:
+            # BASELINE config 3 (memory-bound pair): LP = preemptible fp32 triad over 3 x 2^31 elements (24 GiB),
+            # HP = int32 radix sort of 16 Mi keys every 5 ms.  Same two-process set-up under the same server.
+            try:
+                tri_kw = dict(kernel="triad", n=1 << 31, depth=2, threshold=2, batch=1)
+                sort_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=300, period_us=5000, hp_kernel="sort", hp_n=1 << 24), env_alone, 180)[-1]
+                tri_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **tri_kw), env_alone, 180)[-1]
+                mark("config 3 co-run")
+                env3 = base_env(ns, "GLB")
+                lp3 = subprocess.Popen(worker_cmd("lp", device, level=2, prio=0, duration_s=3600, warmup_s=0.5, **tri_kw), stdout=subprocess.PIPE,
+                                       stderr=subprocess.DEVNULL, text=True, env=env3)
+                try:
+                    t_wait = time.time()
+                    while not lp3.stdout.readline().startswith("READY"):
+                        if lp3.poll() is not None or time.time() - t_wait > 90:
+                            raise RuntimeError("config 3 LP worker not ready")
+                    sort_co = run_json(worker_cmd("hp", device, level=2, prio=1, count=300, period_us=5000, hp_kernel="sort", hp_n=1 << 24),
+                                       dict(env3, XSCHED_IPC_SPIN="OFF"), 180)[-1]
+                finally:
+                    lp3.send_signal(signal.SIGTERM)
+                    out3, _ = lp3.communicate(timeout=120)
+                tri_co = [json.loads(l) for l in out3.splitlines() if l.startswith("{")][-1]
+                launches += sort_alone["xpk_launches"] + tri_alone["xpk_launches"] + sort_co["xpk_launches"] + tri_co["xpk_launches"]
+                extra["config3_triad_vs_sort"] = {
+                    "hp_sort_p99_us": sort_co["p99_us"], "hp_sort_standalone_p99_us": sort_alone["p99_us"],
+                    "hp_p99_ratio": round(sort_co["p99_us"] / sort_alone["p99_us"], 3), "hp_p50_ratio": round(sort_co["p50_us"] / sort_alone["p50_us"], 3),
+                    "sort_sorted": sort_co["verified"], "triad_gbs_standalone": tri_alone["rate"], "triad_gbs_corun": tri_co["rate"],
+                    "triad_kept_pct": round(100 * tri_co["rate"] / tri_alone["rate"], 2), "triad_bit_exact": tri_co["bit_exact"] and tri_alone["bit_exact"],
+                    "triad_frac_of_measured_hbm": round(tri_alone["rate"] / peaks()["hbm_gbs"], 4), "deactivations": tri_co["deactivations"]}
+            except Exception as e:       # an extra leg must not take the headline down with it
+                extra["config3_triad_vs_sort"] = {"error": str(e)[:300]}
         if args.level1:
             hp_l1, lp_l1 = corun(device, ns, 1, args.steps, args.warmup, False, PERIOD_US, lp_kw)
             extra["level1"] = {"hp_p99_us": hp_l1["p99_us"], "ratio": round(hp_l1["p99_us"] / hp_alone["p99_us"], 3),
@@ -376,6 +408,14 @@ def main() -> None:
                         "sample": "config 0 on the host-only lane: 3000 x 1 ms LP commands + 2 ms HP commands Poisson 20/s (seed 42), "
                                   "reference core compiled from its sources, LCL scheduler + HPF, level 1, threshold/batch 16/8",
                         "hp_p99_us": r1["corun"]["p99_us"], "hp_standalone_p99_us": r1["standalone"]["p99_us"], "lp_kept_pct": r1["lp_kept_pct"]}
+        own = ROOT / "oracle" / "lane_driver_new"
+        if own.exists():       # the same scenario on this repository's host runtime (same lane HAL source), levels 1 and 2
+            for lvl in (1, 2):
+                ro = subprocess.run([str(own), "config0", str(lvl), "3000", "1000", "2000", "20", "42", "16", "8", "LCL"], capture_output=True, text=True,
+                                    env=dict(os.environ, XLOG_LEVEL="ERRO"), timeout=300)
+                if ro.returncode == 0:
+                    j = json.loads(ro.stdout.strip().splitlines()[-1])
+                    cpu_baseline[f"this_runtime_level{lvl}"] = {"value": round(j["p99_ratio"], 3), "hp_p99_us": j["corun"]["p99_us"], "lp_kept_pct": j["lp_kept_pct"]}
 
     worst = max(allr, key=lambda r: r["ratio"])
     line = {
