@@ -183,6 +183,62 @@ def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, 
     return hp, lp_json[-1]
 
 
+def find_real_driver() -> str | None:
+    for d in ("/usr/lib/x86_64-linux-gnu", "/usr/lib64", "/usr/lib", "/usr/local/nvidia/lib64", "/usr/local/nvidia/lib", "/usr/lib/wsl/lib",
+              "/usr/local/cuda/compat"):
+        p = Path(d) / "libcuda.so.1"
+        if p.exists():
+            return str(p.resolve())
+    return None
+
+
+def transparent_corun(device: int, shim_lib: Path, steps: int, threshold: int, batch: int) -> dict:
+    """The XSched-unaware plain_worker processes (LP GEMM loop, HP vector add) under a libcuda interposer at
+    preemption level 1, scheduled by an xserver (HPF) — the reference's transparent mode.  `shim_lib` is this
+    repository's libshimcuda.so or the reference's own shim from oracle/_ref."""
+    import tempfile
+    real = find_real_driver()
+    if real is None:
+        return {"unavailable": "real libcuda.so.1 not found"}
+    d = Path(tempfile.mkdtemp(prefix="xsched_shim_"))
+    for name in ("libcuda.so.1", "libcuda.so"):
+        os.symlink(shim_lib, d / name)
+    base = dict(os.environ, XLOG_LEVEL="WARN", XSCHED_CUDA_LIB=real, XSCHED_SCHEDULER="GLB", XSCHED_AUTO_XQUEUE="ON",
+                XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_THRESHOLD=str(threshold), XSCHED_AUTO_XQUEUE_BATCH_SIZE=str(batch))
+    base["LD_LIBRARY_PATH"] = f"{d}:{shim_lib.parent}:{LIB}:" + base.get("LD_LIBRARY_PATH", "")
+    for k in ("XSCHED_IPC_NAMESPACE", "XSCHED_POLICY", "XSCHED_IPC_SPIN"):      # the reference's clients know no namespace
+        base.pop(k, None)
+    srv_env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+    srv = subprocess.Popen([str(XSERVER), "HPF", "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+                           env=dict(srv_env, XLOG_LEVEL="WARN", XSCHED_IPC_SPIN="ON"))
+    srv.stdout.readline()
+    pw = str(LIB / "plain_worker")
+    lp = subprocess.Popen([pw, "--role", "lp", "--device", str(device), "--in-flight", "3", "--M", str(GEMM["M"]), "--N", str(GEMM["N"]), "--K", str(GEMM["K"])],
+                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="0"))
+    try:
+        t0 = time.time()
+        while not lp.stdout.readline().startswith("READY"):
+            if lp.poll() is not None or time.time() - t0 > 90:
+                raise RuntimeError("transparent LP worker not ready")
+        hp = run_json([pw, "--role", "hp", "--device", str(device), "--count", str(steps), "--period-us", str(PERIOD_US), "--hp-n", str(HP_N)],
+                      dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="1"), timeout=60 + steps * PERIOD_US * 30 / 1e6)[-1]
+    finally:
+        lp.send_signal(signal.SIGTERM)
+        try:
+            out, _ = lp.communicate(timeout=60)
+        except subprocess.TimeoutExpired:
+            lp.kill()
+            out, _ = lp.communicate()
+        srv.send_signal(signal.SIGTERM)
+        try:
+            srv.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            srv.kill()
+    lpj = [json.loads(l) for l in out.splitlines() if l.startswith("{")]
+    return {"hp_p50_us": hp["p50_us"], "hp_p99_us": hp["p99_us"], "hp_verified": hp["verified"], "lp_tflops": lpj[-1]["rate"] if lpj else None,
+            "window": f"threshold {threshold} / batch {batch}"}
+
+
 def gemm_roofline(device: int) -> tuple[dict, int]:
     """Average launch duration of the preemptible GEMM, CUDA events on the launching stream."""
     import torch
@@ -356,6 +412,32 @@ def main() -> None:
                                                "bg_kept_pct": round(100 * lp_b["rate"] / lp_alone["rate"], 2), "bit_exact": lp_b["bit_exact"]}
             extra["native_stream_priority"] = {"hp_p99_us": nat["p99_us"], "hp_p50_us": nat["p50_us"], "hp_standalone_p99_us": nat["standalone_p99_us"],
                                                "ratio": nat["ratio_p99"]}
+            if world == 1 and (LIB / "plain_worker").exists():
+                # Transparent mode, level 1: XSched-unaware processes under a libcuda interposer.  Once with this
+                # repository's shim and once with the REFERENCE's own level-1 CUDA HAL + shim (compiled from its sources
+                # under oracle/_ref) — "the reference's own Level-1 CUDA build on the same B200".
+                try:
+                    plain_env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+                    pw = str(LIB / "plain_worker")
+                    plain_hp = run_json([pw, "--role", "hp", "--device", str(device), "--count", "300", "--period-us", str(PERIOD_US), "--hp-n", str(HP_N)],
+                                        plain_env, 120)[-1]
+                    plain_lp = run_json([pw, "--role", "lp", "--device", str(device), "--in-flight", "3", "--duration-s", "3"], plain_env, 120)[-1]
+                    tr = {"plain_hp_p99_us": plain_hp["p99_us"], "plain_hp_p50_us": plain_hp["p50_us"], "plain_lp_tflops": plain_lp["rate"]}
+                    shims = {"this_shim": LIB / "libshimcuda.so", "reference_shim": ROOT / "oracle" / "_ref" / "libshimcuda_ref.so"}
+                    for name, lib_path in shims.items():
+                        if not lib_path.exists():
+                            tr[name] = {"unavailable": f"{lib_path.name} not built"}
+                            continue
+                        for th, bs in ((16, 8), (2, 1)):
+                            mark(f"transparent level 1: {name} window {th}/{bs}")
+                            r = transparent_corun(device, lib_path, min(args.steps, 200), th, bs)
+                            if "hp_p99_us" in r:
+                                r["ratio_p99"] = round(r["hp_p99_us"] / plain_hp["p99_us"], 3)
+                                r["lp_kept_pct"] = round(100 * r["lp_tflops"] / plain_lp["rate"], 2) if r.get("lp_tflops") else None
+                            tr.setdefault(name, {})[f"window_{th}_{bs}"] = r
+                    extra["transparent_level1"] = tr
+                except Exception as e:
+                    extra["transparent_level1"] = {"error": str(e)[:400]}
         if not args.no_config3:
             # BASELINE config 3 (memory-bound pair): LP = preemptible fp32 triad over 3 x 2^31 elements (24 GiB),
             # HP = int32 radix sort of 16 Mi keys every 5 ms.  Same two-process set-up under the same server.

@@ -13,6 +13,9 @@ the trace driver that tests and bench.py use to run the reference as the checker
     oracle/_ref/libhalhost_ref.so   from xsched_b200/csrc/hal_host/*.cpp
     oracle/_ref/lane_driver_ref     from oracle/lane_driver.cpp
     oracle/_ref/sched_probe_ref     from oracle/sched_probe_ref.cpp (drives the reference LocalScheduler + policies)
+    oracle/_ref/libhalcuda_ref.so   the reference's CUDA HAL, level 1 only: platforms/cuda/hal/src/{common,level1}/*.cpp
+                                    + oracle/stubs/cuda/arch_level1.cpp + oracle/stubs/cuxtra/cuxtra.h (stand-ins)
+    oracle/_ref/libshimcuda_ref.so  the reference's libcuda interposer: platforms/cuda/shim/src/{shim,intercept}.cpp
 
 Usage: python oracle/build_ref.py [--force]      (XSCHED_REFERENCE_DIR overrides the tree location)
 """
@@ -83,6 +86,29 @@ def main() -> None:
     if lane_srcs and (force or stale(lane, lane_srcs + [core])):
         run([CXX, *FLAGS, *ref_includes(), lane_inc, "-shared", "-o", str(lane), *map(str, lane_srcs), *link])
         print(f"built {lane}")
+    # ---- the reference's level-1 CUDA HAL and its libcuda shim (baseline "reference level 1 on this GPU") ----
+    cuda = REF / "platforms" / "cuda"
+    cuda_inc = [f"-I{cuda / 'hal' / 'include'}", f"-I{cuda / 'shim' / 'include'}"]
+    hal_srcs = sorted((cuda / "hal" / "src" / "common").glob("*.cpp")) + sorted((cuda / "hal" / "src" / "level1").glob("*.cpp")) + \
+        [HERE / "stubs" / "cuda" / "arch_level1.cpp"]
+    hal = OUT / "libhalcuda_ref.so"
+    if force or stale(hal, hal_srcs + [core, HERE / "stubs" / "cuxtra" / "cuxtra.h"]):
+        run([CXX, *FLAGS, *ref_includes(), *cuda_inc, "-shared", "-o", str(hal), *map(str, hal_srcs), *link])
+        print(f"built {hal} (reference sources: hal/src/common, hal/src/level1; stand-ins: cuxtra.h, arch_level1.cpp)")
+    shim_srcs = [cuda / "shim" / "src" / "shim.cpp", cuda / "shim" / "src" / "intercept.cpp"]
+    shim = OUT / "libshimcuda_ref.so"
+    if force or stale(shim, shim_srcs + [hal]):
+        run([CXX, *FLAGS, *ref_includes(), *cuda_inc, "-shared", "-Wl,-soname,libcuda.so.1", "-o", str(shim), *map(str, shim_srcs), *link,
+             "-lhalcuda_ref"])
+        print(f"built {shim}")
+    shim_dir = OUT / "shim"
+    shim_dir.mkdir(exist_ok=True)
+    for alias in ("libcuda.so.1", "libcuda.so"):
+        l = shim_dir / alias
+        if l.is_symlink() or l.exists():
+            l.unlink()
+        l.symlink_to(Path("..") / "libshimcuda_ref.so")
+
     for name, srcname, extra in (("lane_driver", "lane_driver", ["-lhalhost_ref"]), ("sched_probe", "sched_probe_ref", [])):
         src = HERE / f"{srcname}.cpp"
         out = OUT / f"{name}_ref"

@@ -179,6 +179,13 @@ def build_bench_worker(force: bool = False, verbose: bool = False) -> Path | Non
     if force or _stale(out, deps):
         _run([NVCC, "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", f"-I{INC}", "-o", out, src,
               f"-L{LIB}", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lhalcuda", "-lpreempt", "-lxpk"], verbose)
+    # The XSched-unaware twin of the worker: CUDA runtime + kernel library only (no XQueue API linked), for the
+    # transparent-interposer comparisons (its CUDA runtime loads "libcuda.so.1" by name, so the interposer that
+    # is first on LD_LIBRARY_PATH is what it gets as the driver).
+    psrc, pout = CSRC / "bench" / "plain_worker.cu", LIB / "plain_worker"
+    if psrc.exists() and (force or _stale(pout, [psrc, LIB / "libxpk.so"])):
+        _run([NVCC, "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", f"-I{INC}", "-o", pout, psrc,
+              f"-L{LIB}", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lxpk"], verbose)
     return out
 
 
