@@ -341,6 +341,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--level1", action="store_true", help="also run the co-run phase at preemption level 1")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-config2", action="store_true", help="skip the Llama-decode-vs-GEMM leg (BASELINE config 2)")
     ap.add_argument("--no-config3", action="store_true", help="skip the triad-vs-sort leg (BASELINE config 3)")
     ap.add_argument("--no-variants", action="store_true", help="skip the one-process and native-priority comparison runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -469,6 +470,50 @@ def main() -> None:
                     "triad_frac_of_measured_hbm": round(tri_alone["rate"] / peaks()["hbm_gbs"], 4), "deactivations": tri_co["deactivations"]}
             except Exception as e:       # an extra leg must not take the headline down with it
                 extra["config3_triad_vs_sort"] = {"error": str(e)[:300]}
+        if not args.no_config2 and world == 1:
+            # BASELINE config 2 (inference-shaped): HP = batch-1 decode of a random-init Llama-3-8B-shaped model in
+            # PyTorch, run UNCHANGED under the libcuda interposer (its stream becomes a priority-1 XQueue); LP = the
+            # preemptible GEMM stream (16384x4096)*(4096x14336) at level 2.  10 req/s x 128 tokens at batch 1 is ~3x
+            # more than one GPU can serve sequentially, so requests arrive at 1/s here; the primary number is the
+            # per-token step latency against the same script running alone.
+            try:
+                import tempfile
+                real = find_real_driver()
+                d = Path(tempfile.mkdtemp(prefix="xsched_shim_"))
+                for name in ("libcuda.so.1", "libcuda.so"):
+                    os.symlink(LIB / "libshimcuda.so", d / name)
+                env2 = base_env(ns, "GLB")
+                env2.update(XSCHED_CUDA_LIB=real or "", XSCHED_AUTO_XQUEUE="ON", XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_PRIORITY="1",
+                            XSCHED_IPC_SPIN="OFF", LD_LIBRARY_PATH=f"{d}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""))
+                dec = [sys.executable, "-m", "xsched_b200.llama_decode", "--device", str(device), "--requests", "10", "--tokens", "128", "--rate", "1.0"]
+                mark("config 2: decode alone")
+                dec_alone = run_json(dec, env2, 400)[-1]
+                big = dict(kernel="gemm", abort=1, depth=3, threshold=2, batch=1, M=16384, N=14336, K=4096)
+                big_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **big), env_alone, 180)[-1]
+                mark("config 2: co-run")
+                lp2 = subprocess.Popen(worker_cmd("lp", device, level=2, prio=0, duration_s=3600, warmup_s=0.5, **big), stdout=subprocess.PIPE,
+                                       stderr=subprocess.DEVNULL, text=True, env=base_env(ns, "GLB"))
+                try:
+                    t_wait = time.time()
+                    while not lp2.stdout.readline().startswith("READY"):
+                        if lp2.poll() is not None or time.time() - t_wait > 90:
+                            raise RuntimeError("config 2 LP worker not ready")
+                    dec_co = run_json(dec, env2, 600)[-1]
+                finally:
+                    lp2.send_signal(signal.SIGTERM)
+                    out2, _ = lp2.communicate(timeout=120)
+                big_co = [json.loads(l) for l in out2.splitlines() if l.startswith("{")][-1]
+                extra["config2_llama_decode_vs_gemm"] = {
+                    "token_p99_ms": dec_co["token_p99_ms"], "token_standalone_p99_ms": dec_alone["token_p99_ms"],
+                    "token_p99_ratio": round(dec_co["token_p99_ms"] / dec_alone["token_p99_ms"], 3),
+                    "token_p50_ratio": round(dec_co["token_p50_ms"] / dec_alone["token_p50_ms"], 3),
+                    "request_p99_ms": dec_co["request_p99_ms"], "request_standalone_p99_ms": dec_alone["request_p99_ms"],
+                    "hbm_frac_of_decode_step": round(((dec_alone["weights_gb"] + dec_alone["kv_gb"]) / (dec_alone["token_p50_ms"] * 1e-3)) / peaks()["hbm_gbs"], 3),
+                    "lp_tflops_standalone": big_alone["rate"], "lp_tflops_corun": big_co["rate"], "lp_kept_pct": round(100 * big_co["rate"] / big_alone["rate"], 2),
+                    "lp_bit_exact": big_co["bit_exact"], "deactivations": big_co["deactivations"], "arrival_rate_per_s": 1.0,
+                    "note": "HP runs unmodified PyTorch under libshimcuda.so; vocabulary 128256 assumed"}
+            except Exception as e:
+                extra["config2_llama_decode_vs_gemm"] = {"error": str(e)[:400]}
         if args.level1:
             hp_l1, lp_l1 = corun(device, ns, 1, args.steps, args.warmup, False, PERIOD_US, lp_kw)
             extra["level1"] = {"hp_p99_us": hp_l1["p99_us"], "ratio": round(hp_l1["p99_us"] / hp_alone["p99_us"], 3),
