@@ -213,13 +213,15 @@ def transparent_corun(device: int, shim_lib: Path, steps: int, threshold: int, b
                            env=dict(srv_env, XLOG_LEVEL="WARN", XSCHED_IPC_SPIN="ON"))
     srv.stdout.readline()
     pw = str(LIB / "plain_worker")
+    lp_err = open(d / "lp.stderr", "w+")
     lp = subprocess.Popen([pw, "--role", "lp", "--device", str(device), "--in-flight", "3", "--M", str(GEMM["M"]), "--N", str(GEMM["N"]), "--K", str(GEMM["K"])],
-                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="0"))
+                          stdout=subprocess.PIPE, stderr=lp_err, text=True, env=dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="0"))
     try:
         t0 = time.time()
         while not lp.stdout.readline().startswith("READY"):
             if lp.poll() is not None or time.time() - t0 > 90:
-                raise RuntimeError("transparent LP worker not ready")
+                lp_err.seek(0)
+                raise RuntimeError(f"transparent LP worker not ready (rc {lp.poll()}): " + lp_err.read()[-600:])
         hp = run_json([pw, "--role", "hp", "--device", str(device), "--count", str(steps), "--period-us", str(PERIOD_US), "--hp-n", str(HP_N)],
                       dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="1"), timeout=60 + steps * PERIOD_US * 30 / 1e6)[-1]
     finally:

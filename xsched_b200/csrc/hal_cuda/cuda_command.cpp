@@ -1,6 +1,7 @@
 #include "hal_cuda/cuda_command.h"
 
 #include <chrono>
+#include <cstdio>
 #include <cstring>
 #include <thread>
 #include <immintrin.h>
@@ -78,7 +79,12 @@ void CudaKernelLaunchCommand::CopyArgs(void **params, void **extra) {
         size_t total = 0;
         for (size_t i = 0;; ++i) {
             size_t off = 0, sz = 0;
-            if (Driver().cuFuncGetParamInfo(f_, i, &off, &sz) != CUDA_SUCCESS) break;
+            const CUresult r = Driver().cuFuncGetParamInfo(f_, i, &off, &sz);
+            if (r != CUDA_SUCCESS) {
+                // "Invalid value" ends the list; anything else means the layout cannot be asked for.
+                if (r != CUDA_ERROR_INVALID_VALUE) { ok_ = false; return; }
+                break;
+            }
             layout.emplace_back(off, sz);
             total = std::max(total, off + sz);
         }
@@ -126,7 +132,41 @@ CUresult CudaKernelLaunchCommand::Enqueue(CUstream stream) {
     return Driver().cuLaunchKernel(f_, g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, stream, params, extra);
 }
 
+std::string CudaKernelLaunchCommand::Describe() const {
+    const char *name = nullptr;
+    using GetNameFn = CUresult (*)(const char **, CUfunction);
+    static const GetNameFn get_name = (GetNameFn)Driver().Sym("cuFuncGetName");
+    if (get_name) get_name(&name, f_);
+    char buf[512];
+    snprintf(buf, sizeof(buf), "kernel %s grid (%u,%u,%u) block (%u,%u,%u) shmem %u, %zu params / %zu bytes%s%s, %zu attrs",
+             name ? name : "?", g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, arg_ptrs_.size(), arg_bytes_.size(),
+             use_extra_ ? ", extra buffer" : "", use_ex_ ? ", cuLaunchKernelEx" : "", attrs_.size());
+    return buf;
+}
+
 // ------------------------------------------------------------------------------------ copies, sets
+bool IsPageableHost(const void *p) {
+    unsigned type = 0;
+    const CUresult r = Driver().cuPointerGetAttribute(&type, CU_POINTER_ATTRIBUTE_MEMORY_TYPE, (CUdeviceptr)(uintptr_t)p);
+    return r != CUDA_SUCCESS || type == 0;
+}
+
+CudaMemcpyCommand::CudaMemcpyCommand(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t bytes, bool stage_source)
+    : CudaCommand(preempt::kCommandPropertyNone), kind_(kind), dst_(dst), src_(src), bytes_(bytes) {
+    if (stage_source && bytes) {
+        const unsigned char *p = (const unsigned char *)(uintptr_t)src;
+        staged_.assign(p, p + bytes);
+        src_ = (CUdeviceptr)(uintptr_t)staged_.data();
+    }
+}
+
+std::string CudaMemcpyCommand::Describe() const {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "copy kind %d dst %#llx src %#llx bytes %zu%s", (int)kind_, (unsigned long long)dst_,
+             (unsigned long long)src_, bytes_, staged_.empty() ? "" : " (staged source)");
+    return buf;
+}
+
 CUresult CudaMemcpyCommand::Enqueue(CUstream stream) {
     const DriverApi &d = Driver();
     switch (kind_) {

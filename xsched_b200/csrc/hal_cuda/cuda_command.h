@@ -8,6 +8,7 @@
 #include <cstdint>
 #include <memory>
 #include <mutex>
+#include <string>
 #include <vector>
 #include <cuda.h>
 #include "xsched/preempt/hal/hw_command.h"
@@ -39,6 +40,8 @@ public:
 
     /// Enqueue the work on `stream`, then (if waitable) the counter write that marks its completion.
     CUresult LaunchOn(CUstream stream, const std::shared_ptr<CompletionCounter> &counter);
+    /// One line for the log when the driver refuses the command.
+    virtual std::string Describe() const { return "command"; }
 
 protected:
     virtual CUresult Enqueue(CUstream stream) = 0;
@@ -59,6 +62,7 @@ public:
     /// cuLaunchKernelEx form: the launch attributes (cluster shape, priority, ...) are copied as well.
     CudaKernelLaunchCommand(const CUlaunchConfig *config, CUfunction f, void **params, void **extra);
     bool ParamsCopied() const { return ok_; }
+    std::string Describe() const override;
 protected:
     CUresult Enqueue(CUstream stream) override;
 private:
@@ -76,16 +80,24 @@ private:
 };
 
 enum class CopyKind { kHtoD, kDtoH, kDtoD, kGeneric };
+/// True when the driver does not know `p`: ordinary (pageable) host memory.
+bool IsPageableHost(const void *p);
+
+/// An asynchronous copy.  With `stage_source` the source bytes are captured at construction: a copy
+/// from pageable host memory returns to its caller only after the source was read, so the caller may
+/// reuse the buffer at once, long before a queued command reaches the driver (the reference stages
+/// such sources into pinned memory, platforms/cuda/hal/include/xsched/cuda/hal/common/cuda_command.h:175-199).
 class CudaMemcpyCommand final : public CudaCommand {
 public:
-    CudaMemcpyCommand(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t bytes)
-        : CudaCommand(preempt::kCommandPropertyNone), kind_(kind), dst_(dst), src_(src), bytes_(bytes) {}
+    CudaMemcpyCommand(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t bytes, bool stage_source = false);
+    std::string Describe() const override;
 protected:
     CUresult Enqueue(CUstream stream) override;
 private:
     CopyKind kind_;
     CUdeviceptr dst_, src_;
     size_t bytes_;
+    std::vector<unsigned char> staged_;
 };
 
 class CudaMemsetCommand final : public CudaCommand {

@@ -82,7 +82,8 @@ public:
         ContextScope scope(ctx_);
         auto c = std::dynamic_pointer_cast<CudaCommand>(hw_cmd);
         XASSERT(c != nullptr, "a command that is not a CudaCommand was submitted to a CUDA queue");
-        CUDA_ASSERT(c->LaunchOn(stream_, counter_));
+        const CUresult r = c->LaunchOn(stream_, counter_);
+        if (UNLIKELY(r != CUDA_SUCCESS)) XERRO("the CUDA driver refused a queued command: %d (%s): %s", (int)r, ErrorString(r), c->Describe().c_str());
         stats_.launched.fetch_add(1, std::memory_order_relaxed);
     }
 
@@ -120,7 +121,8 @@ public:
             } else if (x && x->TaskCompleted()) {
                 continue;
             }
-            CUDA_ASSERT(c->LaunchOn(stream_, counter_));
+            const CUresult r = c->LaunchOn(stream_, counter_);
+        if (UNLIKELY(r != CUDA_SUCCESS)) XERRO("the CUDA driver refused a queued command: %d (%s): %s", (int)r, ErrorString(r), c->Describe().c_str());
             stats_.relaunches.fetch_add(1, std::memory_order_relaxed);
         }
     }

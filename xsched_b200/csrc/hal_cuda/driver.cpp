@@ -88,7 +88,7 @@ const DriverApi &Driver() {
         LOAD_V(cuMemsetD32, "cuMemsetD32_v2") LOAD(cuMemsetD8Async) LOAD(cuMemsetD32Async) LOAD(cuMemcpyAsync)
         LOAD_V(cuMemcpyHtoDAsync, "cuMemcpyHtoDAsync_v2") LOAD_V(cuMemcpyDtoHAsync, "cuMemcpyDtoHAsync_v2")
         LOAD_V(cuMemcpyDtoDAsync, "cuMemcpyDtoDAsync_v2") LOAD(cuLaunchKernel) LOAD(cuLaunchKernelEx) LOAD(cuLaunchHostFunc)
-        LOAD(cuFuncGetParamInfo) LOAD(cuEventCreate) LOAD_V(cuEventDestroy, "cuEventDestroy_v2") LOAD(cuEventRecord)
+        LOAD(cuFuncGetParamInfo) LOAD(cuPointerGetAttribute) LOAD(cuEventCreate) LOAD_V(cuEventDestroy, "cuEventDestroy_v2") LOAD(cuEventRecord)
         LOAD(cuEventQuery) LOAD(cuEventSynchronize) LOAD_V(cuGetProcAddress, "cuGetProcAddress_v2")
 #undef LOAD
 #undef LOAD_V

@@ -47,6 +47,7 @@ struct DriverApi {
     XSCHED_DRV(cuLaunchKernelEx)
     XSCHED_DRV(cuLaunchHostFunc)
     XSCHED_DRV(cuFuncGetParamInfo)
+    XSCHED_DRV(cuPointerGetAttribute)
     XSCHED_DRV(cuEventCreate)
     XSCHED_DRV(cuEventDestroy)
     XSCHED_DRV(cuEventRecord)

@@ -240,8 +240,9 @@ void WindowedXQueue::SyncAllLocked(std::unique_lock<std::mutex> &lk) {
 }
 
 // Wait for one waitable command, then retire it and everything launched before it.  Callable from
-// the worker and from application threads (XQueueWait).
-void WindowedXQueue::SyncCmdLocked(std::unique_lock<std::mutex> &lk, const std::shared_ptr<HwCommand> &cmd) {
+// the worker and from application threads (XQueueWait).  The command is taken by value: callers pass
+// elements of sync_points_, which another thread may pop while this one waits unlocked.
+void WindowedXQueue::SyncCmdLocked(std::unique_lock<std::mutex> &lk, std::shared_ptr<HwCommand> cmd) {
     XASSERT(cmd->Synchronizable(), "SyncCmd needs a synchronizable command");
     while (true) {
         // Another thread may retire the command while this one sleeps on the pause.

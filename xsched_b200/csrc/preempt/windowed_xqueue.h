@@ -53,7 +53,7 @@ private:
     void WorkerMain();
     void LaunchOne(std::shared_ptr<HwCommand> cmd);
     void SyncAllLocked(std::unique_lock<std::mutex> &lk);
-    void SyncCmdLocked(std::unique_lock<std::mutex> &lk, const std::shared_ptr<HwCommand> &cmd);
+    void SyncCmdLocked(std::unique_lock<std::mutex> &lk, std::shared_ptr<HwCommand> cmd);
     void RetireThrough(int64_t idx);
     void RetireAll();
     void WaitWhilePaused(std::unique_lock<std::mutex> &lk);

@@ -46,7 +46,7 @@ namespace {
 // ---- statistics (dumped as JSON to $XSCHED_SHIM_STATS_FILE at exit) ----
 struct Stats {
     std::atomic<uint64_t> launches_queued{0}, launches_direct{0}, copies_queued{0}, copies_direct{0}, events_queued{0},
-        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0};
+        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0}, copies_waited{0};
 } g_stats;
 
 void DumpStats() {
@@ -54,11 +54,12 @@ void DumpStats() {
     if (path.empty()) return;
     if (FILE *f = std::fopen(path.c_str(), "w")) {
         std::fprintf(f, "{\"launches_queued\": %llu, \"launches_direct\": %llu, \"copies_queued\": %llu, \"copies_direct\": %llu, "
-                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu}\n",
+                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu, \"copies_waited\": %llu}\n",
                      (unsigned long long)g_stats.launches_queued, (unsigned long long)g_stats.launches_direct,
                      (unsigned long long)g_stats.copies_queued, (unsigned long long)g_stats.copies_direct,
                      (unsigned long long)g_stats.events_queued, (unsigned long long)g_stats.syncs_via_xqueue,
-                     (unsigned long long)g_stats.streams_with_xqueue, (unsigned long long)g_stats.getproc_hooked);
+                     (unsigned long long)g_stats.streams_with_xqueue, (unsigned long long)g_stats.getproc_hooked,
+                     (unsigned long long)g_stats.copies_waited);
         std::fclose(f);
     }
 }
@@ -226,7 +227,20 @@ SHIM_API CUresult CUDAAPI cuMemcpyDtoD(CUdeviceptr d, CUdeviceptr sp, size_t n) 
 static CUresult CopyCommon(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t n, CUstream s) {
     auto xq = Route(s);
     if (xq) {
-        xq->Submit(std::make_shared<CudaMemcpyCommand>(kind, dst, src, n));
+        // Pageable host memory makes the copy synchronous for its caller (the source may be reused, the
+        // destination read, as soon as the call returns).  Sources are captured now unless they are
+        // large; a pageable destination, or a large pageable source, waits for the copy.
+        constexpr size_t kStageLimit = 32u << 20;
+        const bool src_host = kind == CopyKind::kHtoD || kind == CopyKind::kGeneric;
+        const bool dst_host = kind == CopyKind::kDtoH || kind == CopyKind::kGeneric;
+        const bool src_pageable = src_host && IsPageableHost((const void *)(uintptr_t)src);
+        const bool dst_pageable = dst_host && IsPageableHost((const void *)(uintptr_t)dst);
+        const bool stage = src_pageable && n <= kStageLimit;
+        auto cmd = std::make_shared<CudaMemcpyCommand>(kind, dst, src, n, stage);
+        const bool wait = dst_pageable || (src_pageable && !stage);
+        if (wait) cmd->EnableSynchronization();
+        xq->Submit(cmd);
+        if (wait) { xq->Wait(cmd); g_stats.copies_waited++; }
         g_stats.copies_queued++;
         return CUDA_SUCCESS;
     }
