@@ -335,6 +335,145 @@ def impl_reference(args) -> None:
     print(json.dumps(line))
 
 
+def shim_dir(shim_lib: Path) -> Path:
+    """A directory in which libcuda.so.1 / libcuda.so resolve to the interposer."""
+    import tempfile
+    d = Path(tempfile.mkdtemp(prefix="xsched_shim_"))
+    for name in ("libcuda.so.1", "libcuda.so"):
+        os.symlink(shim_lib, d / name)
+    return d
+
+
+def start_lp(cmd: list[str], env: dict, what: str, ready_timeout: float = 120):
+    """Start a long-running LP worker and wait for its READY line.  Returns (process, stderr file)."""
+    import tempfile
+    err = tempfile.TemporaryFile(mode="w+")
+    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=err, text=True, env=env)
+    t0 = time.time()
+    while True:
+        line = p.stdout.readline()
+        if line.startswith("READY"):
+            return p, err
+        if (not line and p.poll() is not None) or time.time() - t0 > ready_timeout:
+            err.seek(0)
+            tail = err.read()[-600:]
+            p.kill()
+            raise RuntimeError(f"{what} not ready (rc {p.poll()}): {tail}")
+
+
+def stop_lp(p, timeout: float = 120) -> dict:
+    p.send_signal(signal.SIGTERM)
+    try:
+        out, _ = p.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        p.kill()
+        out, _ = p.communicate()
+    js = [json.loads(l) for l in out.splitlines() if l.startswith("{")]
+    return js[-1] if js else {}
+
+
+def config4(args) -> None:
+    """BASELINE config 4: one xserver under the laxity policy (LLF) with per-device state; every GPU hosts four
+    processes — a high-priority Llama-3-8B-shaped decode (unmodified PyTorch under the interposer, 20 ms deadline
+    per decode step: laxity = 20 ms - standalone step time, relaxed priority 0, critical priority 1) and three
+    low-priority level-2 loops (8192^3 bf16 GEMM, 2^31-element fp32 triad, 16 Mi-key int32 sort).  Weak scaling:
+    the same four processes per GPU at every N; no data-path collective.  Prints one JSON line."""
+    import tempfile
+    rank, world, local, pg = dist_ctx()
+    device = local
+    ns = f"cfg4{os.environ.get('MASTER_PORT', os.getpid())}."
+    policy = args.config4_policy
+    deadline_ms = 20.0
+    server = None
+    if rank == 0:
+        server = subprocess.Popen([str(XSERVER), policy, "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+                                  env=dict(base_env(ns, None), XSCHED_POLICY_SCOPE="DEVICE"))
+        server.stdout.readline()
+    if pg:
+        pg.barrier()
+    res: dict = {}
+    try:
+        real = find_real_driver()
+        d = shim_dir(LIB / "libshimcuda.so")
+        quiet = dict(base_env(ns, "GLB"), XSCHED_IPC_SPIN="OFF")       # 4 processes per GPU: nobody burns a core polling
+        alone = dict(base_env(ns, "APP"), XSCHED_IPC_SPIN="OFF")
+        hp_env = dict(quiet, XSCHED_CUDA_LIB=real or "", XSCHED_AUTO_XQUEUE="ON", XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_PRIORITY="1",
+                      LD_LIBRARY_PATH=f"{d}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""))
+        lps = {
+            "gemm": dict(kernel="gemm", abort=1, depth=3, threshold=2, batch=1, **GEMM),
+            "triad": dict(kernel="triad", n=1 << 31, depth=2, threshold=2, batch=1),
+            "sort": dict(kernel="sort", n=1 << 24, depth=1, threshold=2, batch=1),
+        }
+        mark("config 4: standalone legs")
+        lp_alone = {k: run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=2, warmup_s=0.5, **kw), alone, 240)[-1] for k, kw in lps.items()}
+        dec = [sys.executable, "-m", "xsched_b200.llama_decode", "--device", str(device), "--tokens", "128", "--deadline-ms", str(deadline_ms)]
+        dec_alone = run_json(dec + ["--requests", "3", "--rate", "2.0"], dict(hp_env, XSCHED_SCHEDULER="APP"), 400)[-1]
+        # laxity = deadline - standalone step time (its P99) - 0.5 ms for the preemption and the context switch
+        laxity_us = max(0, int(deadline_ms * 1e3 - dec_alone["token_p99_ms"] * 1e3 - 500))
+        if pg:
+            pg.barrier()
+        mark(f"config 4: co-run under {policy}, laxity {laxity_us} us")
+        procs = {}
+        samples = tempfile.mktemp(prefix="xsched_cfg4_", suffix=".txt")
+        t0 = time.time()
+        try:
+            for k, kw in lps.items():
+                procs[k] = start_lp(worker_cmd("lp", device, level=2, prio=0, duration_s=3600, warmup_s=0.5, **kw), quiet, f"config 4 LP {k}")
+            env_co = dict(hp_env)
+            if policy == "LAX":
+                env_co["XSCHED_AUTO_XQUEUE_LAXITY"] = str(laxity_us)
+            dec_co = run_json(dec + ["--requests", str(args.config4_requests), "--rate", "2.0", "--samples", samples], env_co, 900)[-1]
+        finally:
+            lp_co = {k: stop_lp(p) for k, (p, _) in procs.items()}
+        res = {"elapsed": time.time() - t0, "dec_alone": dec_alone, "dec_co": dec_co, "tok_ms": read_samples(samples), "lp_alone": lp_alone, "lp_co": lp_co,
+               "laxity_us": laxity_us}
+    except Exception as e:
+        res = {"error": str(e)[:600]}
+    finally:
+        if pg:
+            pg.barrier()
+        if server:
+            server.send_signal(signal.SIGTERM)
+            try:
+                server.wait(timeout=10)
+            except subprocess.TimeoutExpired:
+                server.kill()
+    allr = [res]
+    if pg:
+        allr = [None] * world
+        pg.all_gather_object(allr, res)
+    if rank != 0:
+        return
+    bad = [r["error"] for r in allr if "error" in r]
+    if bad:
+        print(json.dumps({"metric": "config4_deadline_miss_rate", "n_gpus": world, "error": bad[0], "ranks_failed": len(bad)}))
+        return
+    toks = [x for r in allr for x in r["tok_ms"]]
+    missed = sum(1 for x in toks if x > deadline_ms)
+    def agg(kind: str, key: str) -> float:
+        return sum(r[key][kind].get("rate", 0.0) for r in allr)
+    line = {
+        "metric": "config4_deadline_miss_rate", "value": round(missed / max(1, len(toks)), 5), "unit": "fraction of decode steps later than 20 ms",
+        "n_gpus": world, "higher_is_better": False, "scaling": "weak", "data": "synthetic", "impl": "ours",
+        "config": {"workload": "per GPU: llama3-8b-shaped decode (HP, transparent, level 1) + gemm8192 + triad 2^31 + sort 16Mi (LP, level 2)",
+                   "policy": policy, "policy_scope": "DEVICE", "deadline_ms": deadline_ms, "laxity_us": [r["laxity_us"] for r in allr],
+                   "processes_per_gpu": 4, "xserver": 1, "requests_per_gpu": args.config4_requests, "tokens_per_request": 128},
+        "decode_steps": len(toks), "token_p50_ms": round(pct(toks, 0.5), 3), "token_p99_ms": round(pct(toks, 0.99), 3), "token_max_ms": round(max(toks), 3) if toks else None,
+        "token_standalone_p50_ms": round(sum(r["dec_alone"]["token_p50_ms"] for r in allr) / world, 3),
+        "token_standalone_p99_ms": round(max(r["dec_alone"]["token_p99_ms"] for r in allr), 3),
+        "lp_aggregate": {"gemm_tflops": round(agg("gemm", "lp_co"), 1), "triad_gbs": round(agg("triad", "lp_co"), 1),
+                         "sort_mkeys_s": round(agg("sort", "lp_co") * 1e3 / 36.0, 1)},
+        "lp_standalone_aggregate": {"gemm_tflops": round(agg("gemm", "lp_alone"), 1), "triad_gbs": round(agg("triad", "lp_alone"), 1),
+                                    "sort_mkeys_s": round(agg("sort", "lp_alone") * 1e3 / 36.0, 1)},
+        "lp_bit_exact": all(r["lp_co"][k].get("bit_exact", False) for r in allr for k in ("gemm", "triad", "sort")),
+        "deactivations": sum(r["lp_co"][k].get("deactivations", 0) for r in allr for k in ("gemm", "triad", "sort")),
+        "per_gpu_miss_rate": [r["dec_co"]["deadline_miss_rate"] for r in allr],
+        "seconds": round(max(r["elapsed"] for r in allr), 2),
+        "gpu_launches": int(sum(r[key][k].get("xpk_launches", 0) for r in allr for key in ("lp_alone", "lp_co") for k in ("gemm", "triad", "sort"))),
+    }
+    print(json.dumps(line))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -347,9 +486,15 @@ def main() -> None:
     ap.add_argument("--no-config3", action="store_true", help="skip the triad-vs-sort leg (BASELINE config 3)")
     ap.add_argument("--no-variants", action="store_true", help="skip the one-process and native-priority comparison runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config", type=int, default=1, help="1 = the headline workload (default); 4 = the LLF decode + three LP loops per GPU run")
+    ap.add_argument("--config4-policy", default="LAX", choices=["LAX", "HPF"])
+    ap.add_argument("--config4-requests", type=int, default=4)
     args = ap.parse_args()
     if args.impl == "reference":
         impl_reference(args)
+        return
+    if args.config == 4:
+        config4(args)
         return
     if not WORKER.exists() or not (LIB / "libxpk.so").exists():
         raise SystemExit("native libraries missing: run `python -c 'import __graft_entry__ as g; g.build()'` (there is no fallback path)")

@@ -259,11 +259,17 @@ static int Drop(int64_t level, int count, int64_t spin_us) {
 struct HpResult { std::vector<double> lat_us; double lp_total_ms = 0; };
 
 static HpResult RunTwoQueues(int64_t level, int lp_count, int64_t lp_us, const std::vector<int64_t> &hp_arrivals_us, int64_t hp_us,
-                             int64_t threshold, int64_t batch, bool with_lp) {
+                             int64_t threshold, int64_t batch, bool with_lp, int64_t lax_us = -1) {
     XQueueHandle lp = MakeQueue(level, threshold, batch);
     XQueueHandle hp = MakeQueue(level, threshold, batch);
-    CHECK(XHintPriority(lp, 0));
-    CHECK(XHintPriority(hp, 1));
+    if (lax_us < 0) {
+        CHECK(XHintPriority(lp, 0));
+        CHECK(XHintPriority(hp, 1));
+    } else {
+        // laxity policy: the low-priority queue stays un-hinted (priority 0); the other one is relaxed
+        // (priority 0) for lax_us after it becomes ready and critical (priority 1) from then on
+        CHECK(XHintLaxity(hp, lax_us, 0, 1));
+    }
     HpResult res;
     std::atomic<bool> lp_done{false};
     const int64_t t_begin = NowNs();
@@ -304,12 +310,12 @@ static void PrintHp(const char *name, const HpResult &r) {
 }
 
 static int Hpf(int64_t level, int lp_count, int64_t lp_us, int hp_count, int64_t hp_us, int64_t hp_gap_us, int64_t th, int64_t bs,
-               const std::string &sched) {
+               const std::string &sched, int64_t lax_us = -1) {
     if (sched == "GLB") CHECK(XHintSetScheduler(kSchedulerGlobal, kPolicyUnknown));      // needs a running xserver
-    else CHECK(XHintSetScheduler(kSchedulerLocal, kPolicyHighestPriorityFirst));
+    else CHECK(XHintSetScheduler(kSchedulerLocal, lax_us < 0 ? kPolicyHighestPriorityFirst : kPolicyLaxity));
     std::vector<int64_t> arrivals;
     for (int i = 0; i < hp_count; ++i) arrivals.push_back((i + 1) * hp_gap_us);
-    HpResult r = RunTwoQueues(level, lp_count, lp_us, arrivals, hp_us, th, bs, true);
+    HpResult r = RunTwoQueues(level, lp_count, lp_us, arrivals, hp_us, th, bs, true, lax_us);
     std::printf("{\"level\": %" PRId64 ", ", level);
     PrintHp("hp", r);
     std::printf(", \"flushed\": %" PRIu64 "}\n", Flushed());
@@ -354,6 +360,7 @@ int main(int argc, char **argv) {
     if (s == "suspend") return Suspend(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "drop") return Drop(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "hpf") return Hpf(I(2, 1), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL");
+    if (s == "lax") return Hpf(I(2, 2), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL", I(11, 5000));
     if (s == "config0") return Config0(I(2, 1), (int)I(3, 3000), I(4, 1000), I(5, 2000), (double)I(6, 20), (uint64_t)I(7, 42), I(8, 16), I(9, 8),
                                        argc > 10 ? argv[10] : "LCL");
     std::fprintf(stderr, "unknown scenario %s\n", s.c_str());

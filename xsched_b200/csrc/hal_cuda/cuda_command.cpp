@@ -72,17 +72,38 @@ CudaKernelLaunchCommand::CudaKernelLaunchCommand(const CUlaunchConfig *c, CUfunc
     CopyArgs(params, extra);
 }
 
+// Offset and size of parameter i of a kernel, from whichever query understands the handle: the CUDA
+// runtime and the math libraries launch library kernels (CUkernel handles passed where a CUfunction
+// is expected), which the function-level query refuses.
+static CUresult ParamInfo(CUfunction f, size_t i, size_t *off, size_t *sz, bool *as_kernel) {
+    using KernelInfoFn = CUresult (*)(CUkernel, size_t, size_t *, size_t *);
+    static const KernelInfoFn kernel_info = (KernelInfoFn)Driver().Sym("cuKernelGetParamInfo");
+    if (!*as_kernel) {
+        const CUresult r = Driver().cuFuncGetParamInfo(f, i, off, sz);
+        if (r == CUDA_SUCCESS || r == CUDA_ERROR_INVALID_VALUE || i != 0 || !kernel_info) return r;
+        *as_kernel = true;                  // first query refused the handle itself: try it as a CUkernel
+    }
+    return kernel_info((CUkernel)f, i, off, sz);
+}
+
 void CudaKernelLaunchCommand::CopyArgs(void **params, void **extra) {
+    auto borrow = [&] {
+        borrowed_ = true;
+        caller_params_ = params;
+        caller_extra_ = extra;
+        SetProps(preempt::kCommandPropertyBlockingSubmit);
+    };
     if (params != nullptr) {
         // Argument layout comes from the driver: offset and size of parameter i until it says "no more".
         std::vector<std::pair<size_t, size_t>> layout;
         size_t total = 0;
+        bool as_kernel = false;
         for (size_t i = 0;; ++i) {
             size_t off = 0, sz = 0;
-            const CUresult r = Driver().cuFuncGetParamInfo(f_, i, &off, &sz);
+            const CUresult r = ParamInfo(f_, i, &off, &sz, &as_kernel);
             if (r != CUDA_SUCCESS) {
                 // "Invalid value" ends the list; anything else means the layout cannot be asked for.
-                if (r != CUDA_ERROR_INVALID_VALUE) { ok_ = false; return; }
+                if (r != CUDA_ERROR_INVALID_VALUE) { borrow(); return; }
                 break;
             }
             layout.emplace_back(off, sz);
@@ -102,7 +123,7 @@ void CudaKernelLaunchCommand::CopyArgs(void **params, void **extra) {
             if (extra[i] == CU_LAUNCH_PARAM_BUFFER_POINTER) buf = extra[i + 1];
             else if (extra[i] == CU_LAUNCH_PARAM_BUFFER_SIZE) size = *(size_t *)extra[i + 1];
         }
-        if (buf == nullptr) { ok_ = false; return; }
+        if (buf == nullptr) { borrow(); return; }
         extra_bytes_.assign((unsigned char *)buf, (unsigned char *)buf + size);
         use_extra_ = true;
     }
@@ -112,7 +133,10 @@ CUresult CudaKernelLaunchCommand::Enqueue(CUstream stream) {
     void **params = arg_ptrs_.empty() ? nullptr : arg_ptrs_.data();
     void **extra = nullptr;
     size_t size = extra_bytes_.size();
-    if (use_extra_) {
+    if (borrowed_) {
+        params = caller_params_;
+        extra = caller_extra_;
+    } else if (use_extra_) {
         extra_[0] = CU_LAUNCH_PARAM_BUFFER_POINTER; extra_[1] = extra_bytes_.data();
         extra_[2] = CU_LAUNCH_PARAM_BUFFER_SIZE;    extra_[3] = &size;
         extra_[4] = CU_LAUNCH_PARAM_END;
@@ -140,7 +164,7 @@ std::string CudaKernelLaunchCommand::Describe() const {
     char buf[512];
     snprintf(buf, sizeof(buf), "kernel %s grid (%u,%u,%u) block (%u,%u,%u) shmem %u, %zu params / %zu bytes%s%s, %zu attrs",
              name ? name : "?", g_[0], g_[1], g_[2], b_[0], b_[1], b_[2], shmem_, arg_ptrs_.size(), arg_bytes_.size(),
-             use_extra_ ? ", extra buffer" : "", use_ex_ ? ", cuLaunchKernelEx" : "", attrs_.size());
+             use_extra_ ? ", extra buffer" : (borrowed_ ? ", borrowed arguments" : ""), use_ex_ ? ", cuLaunchKernelEx" : "", attrs_.size());
     return buf;
 }
 

@@ -42,6 +42,8 @@ public:
     CUresult LaunchOn(CUstream stream, const std::shared_ptr<CompletionCounter> &counter);
     /// One line for the log when the driver refuses the command.
     virtual std::string Describe() const { return "command"; }
+    /// Ticket of the completion write behind the latest launch of this command (0 = none).
+    uint64_t Ticket() const { return ticket_.load(std::memory_order_acquire); }
 
 protected:
     virtual CUresult Enqueue(CUstream stream) = 0;
@@ -55,13 +57,18 @@ private:
 /// cuLaunchKernel with a private copy of the argument block (the caller's argument array is only
 /// valid during the call that was intercepted).  Not deactivatable: an arbitrary kernel cannot be
 /// stopped cooperatively.
+/// When the driver cannot describe the kernel's parameters the command borrows the caller's argument
+/// array instead and is marked "blocking submit": XQueue::Submit returns only after the launch, so the
+/// array is still valid when it is read, the stream's XQueue does not have to drain, and the scheduler
+/// keeps seeing the work.
 class CudaKernelLaunchCommand final : public CudaCommand {
 public:
     CudaKernelLaunchCommand(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                             unsigned shmem, void **params, void **extra);
     /// cuLaunchKernelEx form: the launch attributes (cluster shape, priority, ...) are copied as well.
     CudaKernelLaunchCommand(const CUlaunchConfig *config, CUfunction f, void **params, void **extra);
-    bool ParamsCopied() const { return ok_; }
+    /// False when the arguments are borrowed from the caller (blocking submit).
+    bool ParamsCopied() const { return !borrowed_; }
     std::string Describe() const override;
 protected:
     CUresult Enqueue(CUstream stream) override;
@@ -73,7 +80,8 @@ private:
     std::vector<unsigned char> extra_bytes_;
     void *extra_[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     bool use_extra_ = false;
-    bool ok_ = true;
+    bool borrowed_ = false;
+    void **caller_params_ = nullptr, **caller_extra_ = nullptr;
     bool use_ex_ = false;
     std::vector<CUlaunchAttribute> attrs_;
     void CopyArgs(void **params, void **extra);

@@ -82,16 +82,32 @@ public:
         ContextScope scope(ctx_);
         auto c = std::dynamic_pointer_cast<CudaCommand>(hw_cmd);
         XASSERT(c != nullptr, "a command that is not a CudaCommand was submitted to a CUDA queue");
-        const CUresult r = c->LaunchOn(stream_, counter_);
-        if (UNLIKELY(r != CUDA_SUCCESS)) XERRO("the CUDA driver refused a queued command: %d (%s): %s", (int)r, ErrorString(r), c->Describe().c_str());
+        LaunchAndNote(c);
         stats_.launched.fetch_add(1, std::memory_order_relaxed);
     }
 
+    void OnHwCommandSubmit(std::shared_ptr<HwCommand> hw_cmd) override {
+        // A callback command enqueues on the stream by itself: from then on the newest completion write
+        // is not known to be the last thing on the stream.
+        if (std::dynamic_pointer_cast<CudaCommand>(hw_cmd) == nullptr) foreign_.store(true, std::memory_order_relaxed);
+    }
+
     void Synchronize() override {
-        ContextScope scope(ctx_);
-        CUresult r = CUDA_SUCCESS;
-        const uint64_t t = counter_->Issue(stream_, &r);
-        CUDA_ASSERT(r);
+        // When the newest thing on the stream is already a completion write, wait for that one: no driver
+        // call, and the write retires the moment the work before it ends.  This is the common case while
+        // preempting (every command of a small window carries a write).
+        uint64_t t = 0;
+        {
+            std::lock_guard<std::mutex> lk(tail_mu_);
+            if (!foreign_.load(std::memory_order_relaxed)) t = tail_ticket_;
+            if (t == 0) {
+                ContextScope scope(ctx_);
+                CUresult r = CUDA_SUCCESS;
+                t = counter_->Issue(stream_, &r);
+                CUDA_ASSERT(r);
+                tail_ticket_ = t;
+            }
+        }
         counter_->Wait(t);
         const int64_t t0 = deactivate_ns_.exchange(0);
         if (t0) stats_.last_preempt_ns.store((uint64_t)(NowNs() - t0));
@@ -121,8 +137,7 @@ public:
             } else if (x && x->TaskCompleted()) {
                 continue;
             }
-            const CUresult r = c->LaunchOn(stream_, counter_);
-        if (UNLIKELY(r != CUDA_SUCCESS)) XERRO("the CUDA driver refused a queued command: %d (%s): %s", (int)r, ErrorString(r), c->Describe().c_str());
+            LaunchAndNote(c);
             stats_.relaunches.fetch_add(1, std::memory_order_relaxed);
         }
     }
@@ -142,8 +157,18 @@ public:
     }
 
 private:
+    void LaunchAndNote(const std::shared_ptr<CudaCommand> &c) {
+        std::lock_guard<std::mutex> lk(tail_mu_);      // the stream's tail changes only under this lock
+        const CUresult r = c->LaunchOn(stream_, counter_);
+        if (UNLIKELY(r != CUDA_SUCCESS)) XERRO("the CUDA driver refused a queued command: %d (%s): %s", (int)r, ErrorString(r), c->Describe().c_str());
+        tail_ticket_ = c->Synchronizable() ? c->Ticket() : 0;
+    }
+
     CUstream stream_;
     CUcontext ctx_ = nullptr;
+    std::mutex tail_mu_;
+    uint64_t tail_ticket_ = 0;             // ticket of the completion write that ends the stream, 0 = unknown
+    std::atomic<bool> foreign_{false};
     XDevice xdevice_ = 0;
     std::shared_ptr<CompletionCounter> counter_;
     CUdeviceptr flag_ = 0;

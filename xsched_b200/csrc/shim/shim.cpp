@@ -46,7 +46,7 @@ namespace {
 // ---- statistics (dumped as JSON to $XSCHED_SHIM_STATS_FILE at exit) ----
 struct Stats {
     std::atomic<uint64_t> launches_queued{0}, launches_direct{0}, copies_queued{0}, copies_direct{0}, events_queued{0},
-        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0}, copies_waited{0};
+        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0}, copies_waited{0}, launches_blocking{0};
 } g_stats;
 
 void DumpStats() {
@@ -54,12 +54,12 @@ void DumpStats() {
     if (path.empty()) return;
     if (FILE *f = std::fopen(path.c_str(), "w")) {
         std::fprintf(f, "{\"launches_queued\": %llu, \"launches_direct\": %llu, \"copies_queued\": %llu, \"copies_direct\": %llu, "
-                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu, \"copies_waited\": %llu}\n",
+                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu, \"copies_waited\": %llu, \"launches_blocking\": %llu}\n",
                      (unsigned long long)g_stats.launches_queued, (unsigned long long)g_stats.launches_direct,
                      (unsigned long long)g_stats.copies_queued, (unsigned long long)g_stats.copies_direct,
                      (unsigned long long)g_stats.events_queued, (unsigned long long)g_stats.syncs_via_xqueue,
                      (unsigned long long)g_stats.streams_with_xqueue, (unsigned long long)g_stats.getproc_hooked,
-                     (unsigned long long)g_stats.copies_waited);
+                     (unsigned long long)g_stats.copies_waited, (unsigned long long)g_stats.launches_blocking);
         std::fclose(f);
     }
 }
@@ -125,12 +125,9 @@ SHIM_API CUresult CUDAAPI cuLaunchKernel(CUfunction f, unsigned gx, unsigned gy,
     auto xq = Route(s);
     if (xq) {
         auto cmd = std::make_shared<CudaKernelLaunchCommand>(f, gx, gy, gz, bx, by, bz, shmem, params, extra);
-        if (cmd->ParamsCopied()) {
-            xq->Submit(cmd);
-            g_stats.launches_queued++;
-            return CUDA_SUCCESS;
-        }
-        xq->WaitAll();       // argument block could not be copied: keep the order and launch directly
+        xq->Submit(cmd);     // returns after the launch when the arguments had to be borrowed
+        if (cmd->ParamsCopied()) g_stats.launches_queued++; else g_stats.launches_blocking++;
+        return CUDA_SUCCESS;
     }
     g_stats.launches_direct++;
     return real(f, gx, gy, gz, bx, by, bz, shmem, s, params, extra);
@@ -141,12 +138,9 @@ SHIM_API CUresult CUDAAPI cuLaunchKernelEx(const CUlaunchConfig *config, CUfunct
     auto xq = Route(config->hStream);
     if (xq) {
         auto cmd = std::make_shared<CudaKernelLaunchCommand>(config, f, params, extra);
-        if (cmd->ParamsCopied()) {
-            xq->Submit(cmd);
-            g_stats.launches_queued++;
-            return CUDA_SUCCESS;
-        }
-        xq->WaitAll();
+        xq->Submit(cmd);
+        if (cmd->ParamsCopied()) g_stats.launches_queued++; else g_stats.launches_blocking++;
+        return CUDA_SUCCESS;
     }
     g_stats.launches_direct++;
     return Driver().cuLaunchKernelEx(config, f, params, extra);

@@ -65,6 +65,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--seed", type=int, default=7)
     ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--deadline-ms", type=float, default=0.0, help="count decode steps that took longer than this (0 = off)")
+    ap.add_argument("--samples", default="", help="write every per-token latency (ms, one per line) to this file")
     a = ap.parse_args()
     torch.cuda.set_device(a.device)
     dev = torch.device("cuda", a.device)
@@ -100,11 +102,16 @@ def main() -> None:
                 x, _ = step(x, (r * a.tokens + t) % a.kv)
                 tok_ms.append((time.perf_counter() - t0) * 1e3)
             req_ms.append((time.perf_counter() - t_arr) * 1e3)
+    if a.samples:
+        with open(a.samples, "w") as f:
+            f.write("\n".join(f"{v:.4f}" for v in tok_ms))
+    missed = sum(1 for v in tok_ms if a.deadline_ms > 0 and v > a.deadline_ms)
     weights_gb = sum(p.numel() for l in layers for p in (l.wqkv, l.wo, l.w_gate_up, l.w_down)) * 2 / 1e9 + lm_head.numel() * 2 / 1e9
     print(json.dumps({"role": "llama-decode", "requests": len(req_ms), "tokens": len(tok_ms), "token_p50_ms": round(pct(tok_ms, 0.5), 3),
                       "token_p99_ms": round(pct(tok_ms, 0.99), 3), "token_mean_ms": round(sum(tok_ms) / max(1, len(tok_ms)), 3),
                       "request_p50_ms": round(pct(req_ms, 0.5), 2), "request_p99_ms": round(pct(req_ms, 0.99), 2),
-                      "weights_gb": round(weights_gb, 2), "kv_gb": round(a.layers * 2 * NKV * a.kv * HD * 2 / 1e9, 3), "rate": a.rate}))
+                      "weights_gb": round(weights_gb, 2), "kv_gb": round(a.layers * 2 * NKV * a.kv * HD * 2 / 1e9, 3), "rate": a.rate,
+                      "deadline_ms": a.deadline_ms, "deadline_missed": missed, "deadline_miss_rate": round(missed / max(1, len(tok_ms)), 5)}))
 
 
 if __name__ == "__main__":
