@@ -82,3 +82,49 @@ def test_hpf_same_behaviour_as_reference_core():
         a, b = _hpf(NEW, level), _hpf(REF, level)
         assert abs(a["hp"]["p50_us"] - b["hp"]["p50_us"]) <= 0.35 * b["hp"]["p50_us"] + 1500
         assert abs(a["hp"]["lp_total_ms"] - b["hp"]["lp_total_ms"]) <= 0.1 * b["hp"]["lp_total_ms"] + 10
+
+
+def _lax(driver, level, lax_us=5000):
+    return run(driver, ["lax", level, 300, 1000, 6, 2000, 40000, 16, 8, "LCL", lax_us])
+
+
+def test_lax_high_priority_waits_its_laxity_then_preempts():
+    # Laxity policy on the host lane at level 2: the hinted queue is relaxed (priority 0, served in FIFO
+    # order behind up to 16 x 1 ms commands) for 5 ms after it becomes ready, then critical: the other
+    # queue is deactivated, at most the running 1 ms command is in the way, then its own 2 ms run.
+    r = _lax(NEW, 2)
+    assert 5000 + 2000 <= r["hp"]["p50_us"] <= 5000 + 1000 + 2000 + 2500, r
+    assert r["flushed"] > 0
+    # a laxity longer than the window's natural drain never turns critical: same as level 1, no flush
+    slack = _lax(NEW, 2, 60000)
+    assert slack["flushed"] == 0 and slack["hp"]["p50_us"] > 8000, slack
+
+
+@pytest.mark.skipif(not REF.exists(), reason="compiled reference core not present")
+def test_lax_same_behaviour_as_reference_core():
+    a, b = _lax(NEW, 2), _lax(REF, 2)
+    assert abs(a["hp"]["p50_us"] - b["hp"]["p50_us"]) <= 1500, (a, b)
+    assert (a["flushed"] > 0) == (b["flushed"] > 0)
+
+
+def test_lax_through_the_server_per_device():
+    # The same scenario with the policy in an xserver (laxity policy, per-device scope).
+    import os
+    import signal
+    import subprocess
+    ns = f"lax{os.getpid()}."
+    env = dict(os.environ, XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns, XSCHED_POLICY_SCOPE="DEVICE")
+    env.pop("XSCHED_SCHEDULER", None)
+    srv = subprocess.Popen([str(NEW.parent.parent / "xsched_b200" / "lib" / "xserver"), "LAX", "50000"], stdout=subprocess.PIPE, text=True, env=env)
+    try:
+        assert "ready" in srv.stdout.readline()
+        out = subprocess.run([str(NEW), "lax", "2", "300", "1000", "6", "2000", "40000", "16", "8", "GLB", "5000"], capture_output=True, text=True,
+                             env=dict(env, XLOG_LEVEL="ERRO"), timeout=120)
+        assert out.returncode == 0, out.stderr[-800:]
+        import json
+        r = json.loads(out.stdout.strip().splitlines()[-1])
+        assert 5000 + 2000 <= r["hp"]["p50_us"] <= 5000 + 1000 + 2000 + 3000, r
+        assert r["flushed"] > 0
+    finally:
+        srv.send_signal(signal.SIGTERM)
+        srv.wait(timeout=10)

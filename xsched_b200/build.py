@@ -83,7 +83,8 @@ SHIM_HANDLED = {
     "cuStreamCreateWithPriority", "cuStreamDestroy_v2", "cuStreamBeginCapture_v2", "cuStreamEndCapture", "cuGetProcAddress",
     "cuGetProcAddress_v2", "cuLaunchKernelEx", "cuLaunchCooperativeKernel", "cuMemAllocAsync", "cuMemFreeAsync", "cuMemcpy2DAsync_v2",
     "cuMemcpyPeerAsync", "cuMemsetD16Async", "cuGraphLaunch", "cuStreamAddCallback", "cuMemcpy", "cuMemcpyDtoH_v2", "cuMemcpyHtoD_v2",
-    "cuMemcpyDtoD_v2",
+    "cuMemcpyDtoD_v2", "cuMemcpy3DAsync_v2", "cuMemsetD2D8Async", "cuMemsetD2D16Async", "cuMemsetD2D32Async", "cuGraphUpload",
+    "cuEventRecordWithFlags",
 }
 
 
@@ -190,14 +191,16 @@ def build_bench_worker(force: bool = False, verbose: bool = False) -> Path | Non
 
 
 def build_test_apps(force: bool = False, verbose: bool = False) -> Path | None:
-    """tests/apps/plain_streams — an XSched-unaware CUDA program the interposer tests run (cudart linked
-    dynamically-loaded driver: it finds "libcuda.so.1" through the loader path like any application)."""
-    src = ROOT / "tests" / "apps" / "plain_streams.cu"
-    out = ROOT / "tests" / "apps" / "plain_streams"
-    if not src.exists():
-        return None
-    if force or _stale(out, [src]):
-        _run([NVCC, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, src], verbose)
+    """tests/apps/plain_streams, plain_graph — XSched-unaware CUDA programs the interposer tests run (cudart
+    linked, dynamically-loaded driver: they find "libcuda.so.1" through the loader path like any application)."""
+    out = None
+    for name in ("plain_streams", "plain_graph"):
+        src = ROOT / "tests" / "apps" / f"{name}.cu"
+        out = ROOT / "tests" / "apps" / name
+        if not src.exists():
+            continue
+        if force or _stale(out, [src]):
+            _run([NVCC, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, src], verbose)
     return out
 
 

@@ -206,7 +206,12 @@ CUresult CudaMemsetCommand::Enqueue(CUstream stream) {
     return Driver().cuMemsetD32Async(dst_, value_, count_, stream);
 }
 
-CUresult CudaEventRecordCommand::Enqueue(CUstream stream) { return Driver().cuEventRecord(ev_, stream); }
+CUresult CudaEventRecordCommand::Enqueue(CUstream stream) {
+    if (!with_flags_) return Driver().cuEventRecord(ev_, stream);
+    using Fn = CUresult (*)(CUevent, CUstream, unsigned);
+    static const Fn record_with_flags = (Fn)Driver().Sym("cuEventRecordWithFlags");
+    return record_with_flags ? record_with_flags(ev_, stream, flags_) : CUDA_ERROR_NOT_SUPPORTED;
+}
 
 void CudaEventWaitCommand::BeforeLaunch() {
     if (record_) record_->WaitUntil(preempt::kCommandStateInFlight);

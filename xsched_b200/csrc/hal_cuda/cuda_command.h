@@ -6,6 +6,7 @@
 #pragma once
 #include <atomic>
 #include <cstdint>
+#include <functional>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -121,14 +122,34 @@ private:
     int width_;
 };
 
-/// cuEventRecord: re-executable, always individually waitable.
+/// Any other stream-ordered driver call (graph launch and upload, 2D/3D/peer copies, the remaining
+/// memsets, stream-ordered allocation, cooperative launches, stream callbacks), kept as a closure over
+/// its copied arguments.  Calls whose arguments are only valid during the intercepted call, or whose
+/// result the caller reads on return, are created with the blocking-submit property.  (The reference has
+/// one generated command class per entry point, platforms/cuda/hal/include/xsched/cuda/hal/common/cuda_command.h:121-233.)
+class CudaCallCommand final : public CudaCommand {
+public:
+    CudaCallCommand(const char *what, std::function<CUresult(CUstream)> call, preempt::XCommandProperties props = preempt::kCommandPropertyNone)
+        : CudaCommand(props), what_(what), call_(std::move(call)) {}
+    std::string Describe() const override { return what_; }
+protected:
+    CUresult Enqueue(CUstream stream) override { return call_(stream); }
+private:
+    const char *what_;
+    std::function<CUresult(CUstream)> call_;
+};
+
+/// cuEventRecord[WithFlags]: re-executable, always individually waitable.
 class CudaEventRecordCommand final : public CudaCommand {
 public:
-    explicit CudaEventRecordCommand(CUevent ev) : CudaCommand(preempt::kCommandPropertyIdempotent), ev_(ev) { EnableSynchronization(); }
+    explicit CudaEventRecordCommand(CUevent ev, unsigned flags = 0, bool with_flags = false)
+        : CudaCommand(preempt::kCommandPropertyIdempotent), ev_(ev), flags_(flags), with_flags_(with_flags) { EnableSynchronization(); }
 protected:
     CUresult Enqueue(CUstream stream) override;
 private:
     CUevent ev_;
+    unsigned flags_;
+    bool with_flags_;
 };
 
 /// cuStreamWaitEvent: before it is launched, the command that records the event must have been

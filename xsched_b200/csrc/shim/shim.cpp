@@ -46,7 +46,7 @@ namespace {
 // ---- statistics (dumped as JSON to $XSCHED_SHIM_STATS_FILE at exit) ----
 struct Stats {
     std::atomic<uint64_t> launches_queued{0}, launches_direct{0}, copies_queued{0}, copies_direct{0}, events_queued{0},
-        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0}, copies_waited{0}, launches_blocking{0};
+        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0}, copies_waited{0}, launches_blocking{0}, calls_queued{0}, graphs_queued{0};
 } g_stats;
 
 void DumpStats() {
@@ -54,12 +54,13 @@ void DumpStats() {
     if (path.empty()) return;
     if (FILE *f = std::fopen(path.c_str(), "w")) {
         std::fprintf(f, "{\"launches_queued\": %llu, \"launches_direct\": %llu, \"copies_queued\": %llu, \"copies_direct\": %llu, "
-                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu, \"copies_waited\": %llu, \"launches_blocking\": %llu}\n",
+                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu, \"copies_waited\": %llu, \"launches_blocking\": %llu, \"calls_queued\": %llu, \"graphs_queued\": %llu}\n",
                      (unsigned long long)g_stats.launches_queued, (unsigned long long)g_stats.launches_direct,
                      (unsigned long long)g_stats.copies_queued, (unsigned long long)g_stats.copies_direct,
                      (unsigned long long)g_stats.events_queued, (unsigned long long)g_stats.syncs_via_xqueue,
                      (unsigned long long)g_stats.streams_with_xqueue, (unsigned long long)g_stats.getproc_hooked,
-                     (unsigned long long)g_stats.copies_waited, (unsigned long long)g_stats.launches_blocking);
+                     (unsigned long long)g_stats.copies_waited, (unsigned long long)g_stats.launches_blocking,
+                     (unsigned long long)g_stats.calls_queued, (unsigned long long)g_stats.graphs_queued);
         std::fclose(f);
     }
 }
@@ -146,55 +147,111 @@ SHIM_API CUresult CUDAAPI cuLaunchKernelEx(const CUlaunchConfig *config, CUfunct
     return Driver().cuLaunchKernelEx(config, f, params, extra);
 }
 
-// Stream-ordered entry points that are not turned into commands: keep their order relative to queued
-// commands by draining the stream's XQueue first, then call the driver (synchronous, but correct).
-#define DRAIN_THEN_CALL(stream, sym, ...)                                   \
-    do {                                                                    \
-        if (auto xq_ = Route(stream)) { xq_->WaitAll(); g_stats.syncs_via_xqueue++; } \
-        REAL_BY_NAME(sym);                                                  \
-        return real(__VA_ARGS__);                                           \
-    } while (0)
+// The remaining stream-ordered entry points become closure commands.  `blocking` = the call returns only
+// after the worker handed it to the driver (arguments borrowed from the caller, or a result the caller reads).
+extern "C++" {
+template <class F>
+static bool SubmitCall(CUstream s, const char *what, F &&call, bool blocking = false) {
+    auto xq = Route(s);
+    if (!xq) return false;
+    xq->Submit(std::make_shared<CudaCallCommand>(what, std::function<CUresult(CUstream)>(std::forward<F>(call)),
+                                                 blocking ? kCommandPropertyBlockingSubmit : kCommandPropertyNone));
+    g_stats.calls_queued++;
+    return true;
+}
+} // extern "C++"
 
 SHIM_API CUresult CUDAAPI cuLaunchCooperativeKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                                                     unsigned shmem, CUstream s, void **params) {
-#define REAL_BY_NAME(sym) REAL(cuLaunchCooperativeKernel, sym)
-    DRAIN_THEN_CALL(s, "cuLaunchCooperativeKernel", f, gx, gy, gz, bx, by, bz, shmem, s, params);
-#undef REAL_BY_NAME
+    REAL(cuLaunchCooperativeKernel, "cuLaunchCooperativeKernel");
+    if (SubmitCall(s, "cooperative launch", [=](CUstream st) { return real(f, gx, gy, gz, bx, by, bz, shmem, st, params); }, /*blocking=*/true))
+        return CUDA_SUCCESS;
+    return real(f, gx, gy, gz, bx, by, bz, shmem, s, params);
 }
 SHIM_API CUresult CUDAAPI cuMemAllocAsync(CUdeviceptr *p, size_t n, CUstream s) {
-#define REAL_BY_NAME(sym) REAL(cuMemAllocAsync, sym)
-    DRAIN_THEN_CALL(s, "cuMemAllocAsync", p, n, s);
-#undef REAL_BY_NAME
+    REAL(cuMemAllocAsync, "cuMemAllocAsync");
+    // Blocking: the address is read by the caller as soon as the call returns.
+    auto res = std::make_shared<CUresult>(CUDA_SUCCESS);
+    if (SubmitCall(s, "cuMemAllocAsync", [=](CUstream st) { *res = real(p, n, st); return CUDA_SUCCESS; }, /*blocking=*/true)) return *res;
+    return real(p, n, s);
 }
 SHIM_API CUresult CUDAAPI cuMemFreeAsync(CUdeviceptr p, CUstream s) {
-#define REAL_BY_NAME(sym) REAL(cuMemFreeAsync, sym)
-    DRAIN_THEN_CALL(s, "cuMemFreeAsync", p, s);
-#undef REAL_BY_NAME
+    REAL(cuMemFreeAsync, "cuMemFreeAsync");
+    if (SubmitCall(s, "cuMemFreeAsync", [=](CUstream st) { return real(p, st); })) return CUDA_SUCCESS;
+    return real(p, s);
+}
+static bool PageableSide(CUmemorytype type, const void *host) {
+    return type == CU_MEMORYTYPE_HOST && host != nullptr && IsPageableHost(host);
 }
 SHIM_API CUresult CUDAAPI cuMemcpy2DAsync(const CUDA_MEMCPY2D *c, CUstream s) {
-#define REAL_BY_NAME(sym) REAL(cuMemcpy2DAsync, sym)
-    DRAIN_THEN_CALL(s, "cuMemcpy2DAsync_v2", c, s);
-#undef REAL_BY_NAME
+    REAL(cuMemcpy2DAsync, "cuMemcpy2DAsync_v2");
+    if (c == nullptr) return CUDA_ERROR_INVALID_VALUE;
+    auto xq = Route(s);
+    if (!xq) return real(c, s);
+    if (PageableSide(c->srcMemoryType, c->srcHost) || PageableSide(c->dstMemoryType, c->dstHost)) {
+        xq->WaitAll();                       // pageable host memory: the call is synchronous for its caller anyway
+        const CUresult r = real(c, s);
+        return r != CUDA_SUCCESS ? r : Driver().cuStreamSynchronize(s);
+    }
+    const CUDA_MEMCPY2D copy = *c;
+    SubmitCall(s, "cuMemcpy2DAsync", [=](CUstream st) { return real(&copy, st); });
+    return CUDA_SUCCESS;
+}
+SHIM_API CUresult CUDAAPI cuMemcpy3DAsync(const CUDA_MEMCPY3D *c, CUstream s) {
+    REAL(cuMemcpy3DAsync, "cuMemcpy3DAsync_v2");
+    if (c == nullptr) return CUDA_ERROR_INVALID_VALUE;
+    auto xq = Route(s);
+    if (!xq) return real(c, s);
+    if (PageableSide(c->srcMemoryType, c->srcHost) || PageableSide(c->dstMemoryType, c->dstHost)) {
+        xq->WaitAll();
+        const CUresult r = real(c, s);
+        return r != CUDA_SUCCESS ? r : Driver().cuStreamSynchronize(s);
+    }
+    const CUDA_MEMCPY3D copy = *c;
+    SubmitCall(s, "cuMemcpy3DAsync", [=](CUstream st) { return real(&copy, st); });
+    return CUDA_SUCCESS;
 }
 SHIM_API CUresult CUDAAPI cuMemcpyPeerAsync(CUdeviceptr d, CUcontext dc, CUdeviceptr sp, CUcontext sc, size_t n, CUstream s) {
-#define REAL_BY_NAME(sym) REAL(cuMemcpyPeerAsync, sym)
-    DRAIN_THEN_CALL(s, "cuMemcpyPeerAsync", d, dc, sp, sc, n, s);
-#undef REAL_BY_NAME
+    REAL(cuMemcpyPeerAsync, "cuMemcpyPeerAsync");
+    if (SubmitCall(s, "cuMemcpyPeerAsync", [=](CUstream st) { return real(d, dc, sp, sc, n, st); })) return CUDA_SUCCESS;
+    return real(d, dc, sp, sc, n, s);
 }
 SHIM_API CUresult CUDAAPI cuMemsetD16Async(CUdeviceptr d, unsigned short v, size_t n, CUstream s) {
-#define REAL_BY_NAME(sym) REAL(cuMemsetD16Async, sym)
-    DRAIN_THEN_CALL(s, "cuMemsetD16Async", d, v, n, s);
-#undef REAL_BY_NAME
+    REAL(cuMemsetD16Async, "cuMemsetD16Async");
+    if (SubmitCall(s, "cuMemsetD16Async", [=](CUstream st) { return real(d, v, n, st); })) return CUDA_SUCCESS;
+    return real(d, v, n, s);
 }
+SHIM_API CUresult CUDAAPI cuMemsetD2D8Async(CUdeviceptr d, size_t pitch, unsigned char v, size_t w, size_t h, CUstream s) {
+    REAL(cuMemsetD2D8Async, "cuMemsetD2D8Async");
+    if (SubmitCall(s, "cuMemsetD2D8Async", [=](CUstream st) { return real(d, pitch, v, w, h, st); })) return CUDA_SUCCESS;
+    return real(d, pitch, v, w, h, s);
+}
+SHIM_API CUresult CUDAAPI cuMemsetD2D16Async(CUdeviceptr d, size_t pitch, unsigned short v, size_t w, size_t h, CUstream s) {
+    REAL(cuMemsetD2D16Async, "cuMemsetD2D16Async");
+    if (SubmitCall(s, "cuMemsetD2D16Async", [=](CUstream st) { return real(d, pitch, v, w, h, st); })) return CUDA_SUCCESS;
+    return real(d, pitch, v, w, h, s);
+}
+SHIM_API CUresult CUDAAPI cuMemsetD2D32Async(CUdeviceptr d, size_t pitch, unsigned v, size_t w, size_t h, CUstream s) {
+    REAL(cuMemsetD2D32Async, "cuMemsetD2D32Async");
+    if (SubmitCall(s, "cuMemsetD2D32Async", [=](CUstream st) { return real(d, pitch, v, w, h, st); })) return CUDA_SUCCESS;
+    return real(d, pitch, v, w, h, s);
+}
+// A graph launch is one command of the stream's XQueue: it takes part in the window, and the scheduler
+// sees the queue as busy while the graph runs.
 SHIM_API CUresult CUDAAPI cuGraphLaunch(CUgraphExec g, CUstream s) {
-#define REAL_BY_NAME(sym) REAL(cuGraphLaunch, sym)
-    DRAIN_THEN_CALL(s, "cuGraphLaunch", g, s);
-#undef REAL_BY_NAME
+    REAL(cuGraphLaunch, "cuGraphLaunch");
+    if (SubmitCall(s, "cuGraphLaunch", [=](CUstream st) { return real(g, st); })) { g_stats.graphs_queued++; return CUDA_SUCCESS; }
+    return real(g, s);
+}
+SHIM_API CUresult CUDAAPI cuGraphUpload(CUgraphExec g, CUstream s) {
+    REAL(cuGraphUpload, "cuGraphUpload");
+    if (SubmitCall(s, "cuGraphUpload", [=](CUstream st) { return real(g, st); })) return CUDA_SUCCESS;
+    return real(g, s);
 }
 SHIM_API CUresult CUDAAPI cuStreamAddCallback(CUstream s, CUstreamCallback cb, void *data, unsigned flags) {
-#define REAL_BY_NAME(sym) REAL(cuStreamAddCallback, sym)
-    DRAIN_THEN_CALL(s, "cuStreamAddCallback", s, cb, data, flags);
-#undef REAL_BY_NAME
+    REAL(cuStreamAddCallback, "cuStreamAddCallback");
+    if (SubmitCall(s, "cuStreamAddCallback", [=](CUstream st) { return real(st, cb, data, flags); })) return CUDA_SUCCESS;
+    return real(s, cb, data, flags);
 }
 // Synchronous copies imply the legacy stream: everything queued on blocking streams goes first.
 SHIM_API CUresult CUDAAPI cuMemcpy(CUdeviceptr d, CUdeviceptr sp, size_t n) {
@@ -273,6 +330,20 @@ SHIM_API CUresult CUDAAPI cuEventRecord(CUevent ev, CUstream s) {
         return Driver().cuEventRecord(ev, s);
     }
     auto cmd = std::make_shared<CudaEventRecordCommand>(ev);
+    { std::lock_guard<std::mutex> lk(g_ev_mu); g_events[ev] = cmd; }
+    xq->Submit(cmd);
+    g_stats.events_queued++;
+    return CUDA_SUCCESS;
+}
+
+SHIM_API CUresult CUDAAPI cuEventRecordWithFlags(CUevent ev, CUstream s, unsigned flags) {
+    REAL(cuEventRecordWithFlags, "cuEventRecordWithFlags");
+    auto xq = Route(s);
+    if (!xq) {
+        { std::lock_guard<std::mutex> lk(g_ev_mu); g_events.erase(ev); }
+        return real(ev, s, flags);
+    }
+    auto cmd = std::make_shared<CudaEventRecordCommand>(ev, flags, true);
     { std::lock_guard<std::mutex> lk(g_ev_mu); g_events[ev] = cmd; }
     xq->Submit(cmd);
     g_stats.events_queued++;
@@ -378,6 +449,12 @@ static const Hook kHooks[] = {
     {"cuMemAllocAsync", (void *)&cuMemAllocAsync, 11020},
     {"cuMemFreeAsync", (void *)&cuMemFreeAsync, 11020},
     {"cuMemcpy2DAsync", (void *)&cuMemcpy2DAsync, 3020},
+    {"cuMemcpy3DAsync", (void *)&cuMemcpy3DAsync, 3020},
+    {"cuMemsetD2D8Async", (void *)&cuMemsetD2D8Async, 3020},
+    {"cuMemsetD2D16Async", (void *)&cuMemsetD2D16Async, 3020},
+    {"cuMemsetD2D32Async", (void *)&cuMemsetD2D32Async, 3020},
+    {"cuGraphUpload", (void *)&cuGraphUpload, 11010},
+    {"cuEventRecordWithFlags", (void *)&cuEventRecordWithFlags, 11010},
     {"cuMemcpyPeerAsync", (void *)&cuMemcpyPeerAsync, 4000},
     {"cuMemsetD16Async", (void *)&cuMemsetD16Async, 3020},
     {"cuGraphLaunch", (void *)&cuGraphLaunch, 10000},
