@@ -71,8 +71,12 @@ public:
     void StepInline(const Event *events, size_t n);
     /// Earliest pending policy timer (epoch us), or INT64_MAX.
     int64_t NextTimerUs() const;
+    /// Replace the wall clock the inline mode reads (tests step a virtual clock through StepInline).
+    void SetClock(std::function<int64_t()> clock) { clock_ = std::move(clock); }
 
 private:
+    int64_t Now() const { return clock_ ? clock_() : NowEpochUs(); }
+    std::function<int64_t()> clock_;
     void Worker();
     void Apply(const Event &e);
     void Decide();

@@ -40,10 +40,12 @@ struct HintTimeslice   { int32_t type; int32_t pad0; int64_t ts_us; };
 struct HintDeadline    { int32_t type; int32_t pad0; uint64_t handle; int64_t ddl_us; };
 struct HintKDeadline   { int32_t type; int32_t pad0; uint64_t k; };
 struct HintLaxity      { int32_t type; int32_t pad0; uint64_t handle; int64_t lax_us; int32_t lax_prio; int32_t crit_prio; };
+struct HintWindowActive { int32_t type; int32_t pid; uint64_t display; };
 static_assert(sizeof(HintPriority) == 24 && offsetof(HintPriority, prio) == 16, "wire");
 static_assert(sizeof(HintUtilization) == 24 && offsetof(HintUtilization, util) == 16, "wire");
 static_assert(sizeof(HintTimeslice) == 16 && sizeof(HintDeadline) == 24 && sizeof(HintKDeadline) == 16, "wire");
 static_assert(sizeof(HintLaxity) == 32 && offsetof(HintLaxity, lax_prio) == 24, "wire");
+static_assert(sizeof(HintWindowActive) == 16 && offsetof(HintWindowActive, display) == 8, "wire");
 
 // ---- events ----
 struct EvHint          { EventMeta meta; uint64_t size; char hint[64]; };   // `size` bytes are sent

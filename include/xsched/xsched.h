@@ -78,8 +78,8 @@ typedef enum {
     kSchedulerUnknown = 0, kSchedulerAppManaged = 1, kSchedulerLocal = 2, kSchedulerGlobal = 3, kSchedulerMax,
 } XSchedulerType;
 
-/* reference: include/xsched/types.h:101-118.  Only HPF (1) and Laxity (8) are implemented here;
- * the other values are kept so that numeric values on the wire stay compatible. */
+/* reference: include/xsched/types.h:101-118.  Every policy the reference can create is provided;
+ * kPolicyStrictProcessUtilizationPartition is declared there but has no implementation, nor here. */
 typedef enum {
     kPolicyUnknown = 0, kPolicyHighestPriorityFirst = 1, kPolicyHeterogeneousHighestPriorityFirst = 2,
     kPolicyCPUHighestPriorityFirst = 3, kPolicyUtilizationPartition = 4, kPolicyProcessUtilizationPartition = 5,

@@ -1,6 +1,9 @@
 // sched_probe (this repository's build) — TEST INFRASTRUCTURE.  Same script and output format as
 // sched_probe_ref.cpp, driving this repository's LocalScheduler (csrc/sched/local_scheduler.cpp).
-//   usage: sched_probe_new <HPF|LAX> < script
+//   usage: sched_probe_new <policy> [--virtual <t0_us>] < script
+// With --virtual the scheduler runs on the calling thread against a virtual clock that starts at t0_us:
+// a round after every event, `sleep_ms` serves the policy's timers at their exact times, `flush` lets
+// 30 ms pass first (as the real-time mode does).  Outcomes are then exactly reproducible.
 #include <chrono>
 #include <cstdio>
 #include <iostream>
@@ -25,6 +28,16 @@ static std::vector<unsigned char> Unhex(const std::string &s) {
 int main(int argc, char **argv) {
     const XPolicyType policy = xsched::protocol::GetPolicyType(argc > 1 ? argv[1] : "HPF");
     LocalScheduler sched(policy);
+    const bool virt = argc > 3 && std::string(argv[2]) == "--virtual";
+    int64_t vnow = virt ? std::atoll(argv[3]) : 0;
+    if (virt) sched.SetClock([&vnow] { return vnow; });
+    auto advance = [&](int64_t until) {
+        while (sched.NextTimerUs() <= until) {
+            vnow = std::max(vnow, sched.NextTimerUs());
+            sched.StepInline(nullptr, 0);
+        }
+        vnow = until;
+    };
     std::mutex mu;
     std::map<int32_t, std::pair<std::vector<uint64_t>, std::vector<uint64_t>>> last;
     sched.SetExecutor([&](const Operation &op) {
@@ -37,11 +50,12 @@ int main(int argc, char **argv) {
             e.first.assign(handles, handles + h.running_cnt);
             e.second.assign(handles + h.running_cnt, handles + h.running_cnt + h.suspended_cnt);
         }
+        if (virt) return;
         Event ack = Event::OperationComplete(h.meta.id);
         reinterpret_cast<EventMeta *>(ack.bytes)->pid = h.meta.pid;
         sched.RecvEvent(ack);
     });
-    sched.Run();
+    if (!virt) sched.Run();
     std::string line;
     while (std::getline(std::cin, line)) {
         std::istringstream is(line);
@@ -53,13 +67,13 @@ int main(int argc, char **argv) {
             auto bytes = Unhex(hex);
             Event e;
             if (!e.Assign(bytes.data(), bytes.size())) { std::printf("malformed\n"); continue; }
-            sched.RecvEvent(e);
+            if (virt) sched.StepInline(&e, 1); else sched.RecvEvent(e);
         } else if (cmd == "sleep_ms") {
             int ms = 0;
             is >> ms;
-            std::this_thread::sleep_for(std::chrono::milliseconds(ms));
+            if (virt) advance(vnow + (int64_t)ms * 1000); else std::this_thread::sleep_for(std::chrono::milliseconds(ms));
         } else if (cmd == "flush") {
-            std::this_thread::sleep_for(std::chrono::milliseconds(30));
+            if (virt) advance(vnow + 30000); else std::this_thread::sleep_for(std::chrono::milliseconds(30));
             std::lock_guard<std::mutex> lk(mu);
             std::printf("flush");
             for (auto &[pid, rs] : last) {
@@ -71,6 +85,6 @@ int main(int argc, char **argv) {
             std::printf("\n");
         }
     }
-    sched.Stop();
+    if (!virt) sched.Stop();
     return 0;
 }

@@ -1,5 +1,6 @@
 #include "hal_cuda/cuda_command.h"
 
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <cstring>
@@ -11,23 +12,43 @@
 
 namespace xsched::cuda {
 
-void CompletionCounter::Wait(uint64_t ticket) const {
-    // Phase 1: spin with pause for ~100 us (a completion is usually that close); phase 2: yield the core
-    // between looks for up to ~2 ms; phase 3: sleep in 20 us slices so a long kernel does not burn a core.
+void CompletionCounter::Wait(uint64_t ticket, bool urgent) {
+    if (*host >= ticket) return;
     const auto t0 = std::chrono::steady_clock::now();
     auto elapsed_us = [&] { return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count(); };
+    auto done = [&] {
+        // moving average (1/4 new) of how long waits on this queue take
+        const uint32_t prev = typical_wait_us.load(std::memory_order_relaxed);
+        const uint32_t now = (uint32_t)std::min<int64_t>(elapsed_us(), 1000000);
+        typical_wait_us.store(prev - prev / 4 + now / 4, std::memory_order_relaxed);
+    };
+    // Phase 0: waits here have been long lately: sleep through the first half of the expected time.
+    const uint32_t typical = typical_wait_us.load(std::memory_order_relaxed);
+    if (!urgent && typical > 400) {
+        int64_t budget = std::min<int64_t>(typical / 2, 5000);
+        while (budget > 0 && *host < ticket) {
+            const int64_t slice = std::min<int64_t>(budget, 500);
+            std::this_thread::sleep_for(std::chrono::microseconds(slice));
+            budget -= slice;
+        }
+        if (*host >= ticket) { done(); return; }
+    }
+    // Phase 1: spin with pause for ~100 us (a completion is usually that close); phase 2: yield the core
+    // between looks for up to ~1 ms; phase 3: sleep in 20 us slices so a long kernel does not burn a core.
+    const int64_t spin_from = elapsed_us();
     while (true) {
         for (int i = 0; i < 64; ++i) {
-            if (*host >= ticket) return;
+            if (*host >= ticket) { done(); return; }
             _mm_pause();
         }
-        if (elapsed_us() > 100) break;
+        if (elapsed_us() - spin_from > 100) break;
     }
-    while (elapsed_us() < 2000) {
-        if (*host >= ticket) return;
+    while (elapsed_us() - spin_from < 1000) {
+        if (*host >= ticket) { done(); return; }
         std::this_thread::yield();
     }
     while (*host < ticket) std::this_thread::sleep_for(std::chrono::microseconds(20));
+    done();
 }
 
 uint64_t CompletionCounter::Issue(CUstream stream, CUresult *res) {

@@ -26,8 +26,11 @@ struct CompletionCounter {
     std::mutex issue_mu;                   // ticket order must equal stream order of the writes
     /// Take the next ticket and enqueue its write on `stream`; returns the ticket (0 on failure).
     uint64_t Issue(CUstream stream, CUresult *res);
-    /// Spin briefly, then back off, until *host >= ticket.
-    void Wait(uint64_t ticket) const;
+    /// Wait until *host >= ticket.  Spin briefly, then back off; when recent waits on this queue were long
+    /// (a low-priority queue of millisecond kernels) most of the expected time is slept away first, so
+    /// that such a queue does not keep a core busy.  `urgent` skips that sleep (preemption path).
+    void Wait(uint64_t ticket, bool urgent = false);
+    std::atomic<uint32_t> typical_wait_us{0};   // moving average of recent wait times
 };
 
 class CudaCommand : public preempt::HwCommand {

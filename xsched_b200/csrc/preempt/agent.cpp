@@ -35,7 +35,7 @@ std::string Cmdline() {
     return out;
 }
 
-bool PolicyAvailable(XPolicyType p) { return p == kPolicyHighestPriorityFirst || p == kPolicyLaxity; }
+bool PolicyAvailable(XPolicyType p) { return p > kPolicyUnknown && p < kPolicyMax && p != kPolicyStrictProcessUtilizationPartition; }
 
 void Start(XSchedulerType scheduler, XPolicyType policy) {
     if (policy > kPolicyUnknown && policy < kPolicyMax && !PolicyAvailable(policy)) {

@@ -137,7 +137,7 @@ void LocalScheduler::Worker() {
 
 void LocalScheduler::StepInline(const Event *events, size_t n) {
     std::lock_guard<std::mutex> sl(status_mtx_);
-    const int64_t now = NowEpochUs();
+    const int64_t now = Now();
     timers_.erase(timers_.begin(), std::upper_bound(timers_.begin(), timers_.end(), now));
     for (size_t i = 0; i < n; ++i) {
         const Event &e = events[i];
@@ -169,7 +169,7 @@ XQueueStatus &LocalScheduler::Ensure(XQueueHandle h, PID pid) {
     XQueueStatus q;
     q.handle = h;
     q.pid = pid;
-    q.ready_time_us = NowEpochUs();
+    q.ready_time_us = Now();
     ProcessStatus &p = status_.processes[pid];
     p.pid = pid;
     p.running.insert(h);
@@ -236,7 +236,7 @@ void LocalScheduler::Apply(const Event &e) {
 
 void LocalScheduler::Decide() {
     decision_.Clear();
-    policy_->Sched(status_, NowEpochUs(), decision_);
+    policy_->Sched(status_, Now(), decision_);
 
     auto move = [this](XQueueHandle h, bool to_suspended) {
         auto qit = status_.xqueues.find(h);
@@ -250,6 +250,7 @@ void LocalScheduler::Decide() {
     };
     for (XQueueHandle h : decision_.suspend) move(h, true);
     for (XQueueHandle h : decision_.resume) move(h, false);
+    for (const auto &[h, suspend] : decision_.ordered) move(h, suspend);
 
     for (PID pid : dirty_) {
         auto pit = status_.processes.find(pid);

@@ -93,7 +93,15 @@ std::unique_ptr<Policy> CreatePolicy(XPolicyType type) {
     switch (type) {
     case kPolicyHighestPriorityFirst: return std::make_unique<HighestPriorityFirstPolicy>();
     case kPolicyLaxity: return std::make_unique<LaxityPolicy>(PolicyScopeFromEnv());
-    default: return nullptr;
+    case kPolicyHeterogeneousHighestPriorityFirst: return std::make_unique<HeterogeneousHpfPolicy>();
+    case kPolicyCPUHighestPriorityFirst: return std::make_unique<CpuHpfPolicy>();
+    case kPolicyUtilizationPartition: return std::make_unique<UtilizationPartitionPolicy>();
+    case kPolicyProcessUtilizationPartition: return std::make_unique<ProcessUtilizationPartitionPolicy>();
+    case kPolicyKEarliestDeadlineFirst: return std::make_unique<KEarliestDeadlineFirstPolicy>();
+    case kPolicyActiveWindowFirst: return std::make_unique<ActiveWindowFirstPolicy>();
+    case kPolicyCompletelyFairScheduler: return std::make_unique<CompletelyFairPolicy>();
+    case kPolicyMultiLevelFeedbackQueue: return std::make_unique<MultiLevelFeedbackPolicy>();
+    default: return nullptr;       // kPolicyStrictProcessUtilizationPartition: declared by the reference, implemented nowhere
     }
 }
 

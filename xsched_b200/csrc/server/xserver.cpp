@@ -236,12 +236,12 @@ private:
 
 int main(int argc, char **argv) {
     if (argc < 2) {
-        std::fprintf(stderr, "usage: xserver <HPF|LAX> [port] [--status-interval-ms N]\n");
+        std::fprintf(stderr, "usage: xserver <HPF|HHPF|CHPF|UP|PUP|KEDF|LAX|AWF|CFS|MLFQ> [port] [--status-interval-ms N]\n");
         return 2;
     }
     const XPolicyType policy = xsched::protocol::GetPolicyType(argv[1]);
-    if (policy != kPolicyHighestPriorityFirst && policy != kPolicyLaxity) {
-        std::fprintf(stderr, "xserver: policy '%s' is not provided (HPF and LAX are)\n", argv[1]);
+    if (xsched::sched::CreatePolicy(policy) == nullptr) {
+        std::fprintf(stderr, "xserver: policy '%s' is not provided\n", argv[1]);
         return 2;
     }
     int status_ms = 0;
