@@ -373,7 +373,7 @@ def stop_lp(p, timeout: float = 120) -> dict:
 
 
 def config4(args) -> None:
-    """BASELINE config 4: one xserver under the laxity policy (LLF) with per-device state; every GPU hosts four
+    """Workload configuration 4 (8 GPUs, LLF): one xserver under the laxity policy (LLF) with per-device state; every GPU hosts four
     processes — a high-priority Llama-3-8B-shaped decode (unmodified PyTorch under the interposer, 20 ms deadline
     per decode step: laxity = 20 ms - standalone step time, relaxed priority 0, critical priority 1) and three
     low-priority level-2 loops (8192^3 bf16 GEMM, 2^31-element fp32 triad, 16 Mi-key int32 sort).  Weak scaling:
@@ -482,8 +482,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--level1", action="store_true", help="also run the co-run phase at preemption level 1")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-config2", action="store_true", help="skip the Llama-decode-vs-GEMM leg (BASELINE config 2)")
-    ap.add_argument("--no-config3", action="store_true", help="skip the triad-vs-sort leg (BASELINE config 3)")
+    ap.add_argument("--no-config2", action="store_true", help="skip the Llama-decode-vs-GEMM leg (workload configuration 2)")
+    ap.add_argument("--no-config3", action="store_true", help="skip the triad-vs-sort leg (workload configuration 3)")
     ap.add_argument("--no-variants", action="store_true", help="skip the one-process and native-priority comparison runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--config", type=int, default=1, help="1 = the headline workload (default); 4 = the LLF decode + three LP loops per GPU run")
@@ -587,7 +587,7 @@ def main() -> None:
                 except Exception as e:
                     extra["transparent_level1"] = {"error": str(e)[:400]}
         if not args.no_config3:
-            # BASELINE config 3 (memory-bound pair): LP = preemptible fp32 triad over 3 x 2^31 elements (24 GiB),
+            # Workload configuration 3 (memory-bound pair): LP = preemptible fp32 triad over 3 x 2^31 elements (24 GiB),
             # HP = int32 radix sort of 16 Mi keys every 5 ms.  Same two-process set-up under the same server.
             try:
                 tri_kw = dict(kernel="triad", n=1 << 31, depth=2, threshold=2, batch=1)
@@ -618,7 +618,7 @@ def main() -> None:
             except Exception as e:       # an extra leg must not take the headline down with it
                 extra["config3_triad_vs_sort"] = {"error": str(e)[:300]}
         if not args.no_config2 and world == 1:
-            # BASELINE config 2 (inference-shaped): HP = batch-1 decode of a random-init Llama-3-8B-shaped model in
+            # Workload configuration 2 (inference-shaped): HP = batch-1 decode of a random-init Llama-3-8B-shaped model in
             # PyTorch, run UNCHANGED under the libcuda interposer (its stream becomes a priority-1 XQueue); LP = the
             # preemptible GEMM stream (16384x4096)*(4096x14336) at level 2.  10 req/s x 128 tokens at batch 1 is ~3x
             # more than one GPU can serve sequentially, so requests arrive at 1/s here; the primary number is the

@@ -11,7 +11,7 @@ import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
 LIB = ROOT / "xsched_b200" / "lib"
-REF_PY = Path("/root/reference/python")
+REF_PY = Path(os.environ.get("XSCHED_REFERENCE_DIR", "/root/reference")) / "python"
 
 SCRIPT = r"""
 import ctypes, json, sys
