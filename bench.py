@@ -408,8 +408,8 @@ def config4(args) -> None:
         lp_alone = {k: run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=2, warmup_s=0.5, **kw), alone, 240)[-1] for k, kw in lps.items()}
         dec = [sys.executable, "-m", "xsched_b200.llama_decode", "--device", str(device), "--tokens", "128", "--deadline-ms", str(deadline_ms)]
         dec_alone = run_json(dec + ["--requests", "3", "--rate", "2.0"], dict(hp_env, XSCHED_SCHEDULER="APP"), 400)[-1]
-        # laxity = deadline - standalone step time (its P99) - 0.5 ms for the preemption and the context switch
-        laxity_us = max(0, int(deadline_ms * 1e3 - dec_alone["token_p99_ms"] * 1e3 - 500))
+        # laxity = deadline - standalone step time (its P99) - 1 ms for the preemption and the context switch
+        laxity_us = max(0, int(deadline_ms * 1e3 - dec_alone["token_p99_ms"] * 1e3 - 1000))
         if pg:
             pg.barrier()
         mark(f"config 4: co-run under {policy}, laxity {laxity_us} us")

@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <thread>
+#include <unordered_map>
 #include <immintrin.h>
 #include "hal_cuda/driver.h"
 #include "xsched/utils/xassert.h"
@@ -12,43 +13,34 @@
 
 namespace xsched::cuda {
 
-void CompletionCounter::Wait(uint64_t ticket, bool urgent) {
+void CompletionCounter::Wait(uint64_t ticket, int64_t expected_remaining_us) const {
     if (*host >= ticket) return;
-    const auto t0 = std::chrono::steady_clock::now();
-    auto elapsed_us = [&] { return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count(); };
-    auto done = [&] {
-        // moving average (1/4 new) of how long waits on this queue take
-        const uint32_t prev = typical_wait_us.load(std::memory_order_relaxed);
-        const uint32_t now = (uint32_t)std::min<int64_t>(elapsed_us(), 1000000);
-        typical_wait_us.store(prev - prev / 4 + now / 4, std::memory_order_relaxed);
-    };
-    // Phase 0: waits here have been long lately: sleep through the first half of the expected time.
-    const uint32_t typical = typical_wait_us.load(std::memory_order_relaxed);
-    if (!urgent && typical > 400) {
-        int64_t budget = std::min<int64_t>(typical / 2, 5000);
+    // Phase 0: the work is known to need a while longer: sleep through half of it, looking in between.
+    if (expected_remaining_us > 400) {
+        int64_t budget = std::min<int64_t>(expected_remaining_us / 2, 5000);
         while (budget > 0 && *host < ticket) {
             const int64_t slice = std::min<int64_t>(budget, 500);
             std::this_thread::sleep_for(std::chrono::microseconds(slice));
             budget -= slice;
         }
-        if (*host >= ticket) { done(); return; }
+        if (*host >= ticket) return;
     }
     // Phase 1: spin with pause for ~100 us (a completion is usually that close); phase 2: yield the core
     // between looks for up to ~1 ms; phase 3: sleep in 20 us slices so a long kernel does not burn a core.
-    const int64_t spin_from = elapsed_us();
+    const auto t0 = std::chrono::steady_clock::now();
+    auto elapsed_us = [&] { return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count(); };
     while (true) {
         for (int i = 0; i < 64; ++i) {
-            if (*host >= ticket) { done(); return; }
+            if (*host >= ticket) return;
             _mm_pause();
         }
-        if (elapsed_us() - spin_from > 100) break;
+        if (elapsed_us() > 100) break;
     }
-    while (elapsed_us() - spin_from < 1000) {
-        if (*host >= ticket) { done(); return; }
+    while (elapsed_us() < 1000) {
+        if (*host >= ticket) return;
         std::this_thread::yield();
     }
     while (*host < ticket) std::this_thread::sleep_for(std::chrono::microseconds(20));
-    done();
 }
 
 uint64_t CompletionCounter::Issue(CUstream stream, CUresult *res) {
@@ -63,7 +55,8 @@ uint64_t CompletionCounter::Issue(CUstream stream, CUresult *res) {
 
 void CudaCommand::Synchronize() {
     XASSERT(counter_ != nullptr && ticket_.load() != 0, "Synchronize() on a command that was not launched as waitable");
-    counter_->Wait(ticket_.load(std::memory_order_acquire));
+    counter_->Wait(ticket_.load(std::memory_order_acquire), ExpectedRemainingUs());
+    OnWaited();
 }
 
 CUresult CudaCommand::LaunchOn(CUstream stream, const std::shared_ptr<CompletionCounter> &counter) {
@@ -248,8 +241,37 @@ bool CudaXpkCommand::TaskCompleted() const {
     return info.status == XPK_STATUS_COMPLETED;
 }
 
+// Duration (launch -> wait returned) each task showed last time, so that the next wait for the same task
+// can sleep through most of it.  Tasks are re-submitted in loops; a preempted run only makes the figure larger
+// once, and the sleep is capped.
+namespace {
+std::mutex g_dur_mu;
+std::unordered_map<void *, int64_t> g_last_duration_us;
+int64_t SteadyNs() { return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
+}
+
+int64_t CudaXpkCommand::ExpectedRemainingUs() const {
+    int64_t last = 0;
+    {
+        std::lock_guard<std::mutex> lk(g_dur_mu);
+        auto it = g_last_duration_us.find(task_);
+        if (it != g_last_duration_us.end()) last = it->second;
+    }
+    if (last == 0 || launched_at_ns_ == 0) return 0;
+    return std::max<int64_t>(0, last - (SteadyNs() - launched_at_ns_) / 1000);
+}
+
+void CudaXpkCommand::OnWaited() {
+    if (launched_at_ns_ == 0) return;
+    const int64_t us = (SteadyNs() - launched_at_ns_) / 1000;
+    std::lock_guard<std::mutex> lk(g_dur_mu);
+    if (g_last_duration_us.size() > 4096) g_last_duration_us.clear();      // tasks come and go; keep the table small
+    g_last_duration_us[task_] = us;
+}
+
 CUresult CudaXpkCommand::Enqueue(CUstream stream) {
     xpkTask_t t = (xpkTask_t)task_;
+    launched_at_ns_ = SteadyNs();
     if (!launched_once_ && rewind_) {
         if (xpkTaskReset(t, stream) != XPK_SUCCESS) return CUDA_ERROR_LAUNCH_FAILED;
     }

@@ -26,11 +26,11 @@ struct CompletionCounter {
     std::mutex issue_mu;                   // ticket order must equal stream order of the writes
     /// Take the next ticket and enqueue its write on `stream`; returns the ticket (0 on failure).
     uint64_t Issue(CUstream stream, CUresult *res);
-    /// Wait until *host >= ticket.  Spin briefly, then back off; when recent waits on this queue were long
-    /// (a low-priority queue of millisecond kernels) most of the expected time is slept away first, so
-    /// that such a queue does not keep a core busy.  `urgent` skips that sleep (preemption path).
-    void Wait(uint64_t ticket, bool urgent = false);
-    std::atomic<uint32_t> typical_wait_us{0};   // moving average of recent wait times
+    /// Wait until *host >= ticket.  Spin briefly, then back off.  When the caller knows that the work
+    /// behind the ticket still needs about `expected_remaining_us` (a task that was timed on its previous
+    /// run), half of that is slept away first, so that a loop of millisecond kernels does not keep a core
+    /// busy; 0 = unknown, no sleep.
+    void Wait(uint64_t ticket, int64_t expected_remaining_us = 0) const;
 };
 
 class CudaCommand : public preempt::HwCommand {
@@ -48,6 +48,10 @@ public:
     virtual std::string Describe() const { return "command"; }
     /// Ticket of the completion write behind the latest launch of this command (0 = none).
     uint64_t Ticket() const { return ticket_.load(std::memory_order_acquire); }
+    /// Microseconds the work of this command is still expected to take; 0 = unknown.
+    virtual int64_t ExpectedRemainingUs() const { return 0; }
+    /// Called after a wait on this command returned.
+    virtual void OnWaited() {}
 
 protected:
     virtual CUresult Enqueue(CUstream stream) = 0;
@@ -187,12 +191,16 @@ public:
     /// Completed on the device (valid once the stream has drained).
     bool TaskCompleted() const;
     void *Task() const { return task_; }
+    /// From the duration the same task showed the last time a wait for it returned.
+    int64_t ExpectedRemainingUs() const override;
+    void OnWaited() override;
 protected:
     CUresult Enqueue(CUstream stream) override;
 private:
     void *task_;
     bool rewind_;
     bool launched_once_ = false;
+    int64_t launched_at_ns_ = 0;
 };
 
 } // namespace xsched::cuda

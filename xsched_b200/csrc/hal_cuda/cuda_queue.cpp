@@ -108,7 +108,7 @@ public:
                 tail_ticket_ = t;
             }
         }
-        counter_->Wait(t, /*urgent=*/deactivate_ns_.load(std::memory_order_relaxed) != 0);
+        counter_->Wait(t);
         const int64_t t0 = deactivate_ns_.exchange(0);
         if (t0) stats_.last_preempt_ns.store((uint64_t)(NowNs() - t0));
     }
