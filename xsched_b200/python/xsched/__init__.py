@@ -17,10 +17,6 @@ XDevice = XDeviceId = XQueueHandle = HwQueueHandle = HwCommandHandle = int
 Priority = Utilization = Timeslice = Laxity = Deadline = int
 
 
-def _enum(name: str, start: int = 0, **explicit) -> type:
-    return IntEnum(name, explicit)
-
-
 XResult = IntEnum("XResult", dict(kXSchedSuccess=0, kXSchedErrorHardware=1, kXSchedErrorInvalidValue=2, kXSchedErrorNotFound=3,
                                   kXSchedErrorNotAllowed=4, kXSchedErrorNotSupported=5, kXSchedErrorBadResponse=6, kXSchedErrorUnknown=999))
 XPlatform = IntEnum("XPlatform", dict(kPlatformUnknown=0, kPlatformVPI=1, kPlatformCUDA=2, kPlatformCUDLA=3, kPlatformHIP=4,
