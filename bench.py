@@ -713,6 +713,13 @@ def main() -> None:
                     j = json.loads(ro.stdout.strip().splitlines()[-1])
                     cpu_baseline[f"this_runtime_level{lvl}"] = {"value": round(j["p99_ratio"], 3), "hp_p99_us": j["corun"]["p99_us"], "lp_kept_pct": j["lp_kept_pct"]}
 
+        # Host-path cost of one command (zero-length commands on the host lane): the reference core and this runtime.
+        for key, drv in (("reference_host_path", REF_DRIVER), ("this_runtime_host_path", own)):
+            if drv.exists():
+                rt = subprocess.run([str(drv), "tput", "1", "200000", "16", "8"], capture_output=True, text=True, env=dict(os.environ, XLOG_LEVEL="ERRO"), timeout=120)
+                if rt.returncode == 0:
+                    cpu_baseline[key] = json.loads(rt.stdout.strip().splitlines()[-1])
+
     worst = max(allr, key=lambda r: r["ratio"])
     # Whole-job figure: P99 over the high-priority requests of ALL GPUs against the P99 of all their standalone
     # requests (pooled samples), not the maximum of per-GPU ratios, which grows with N by selection alone.

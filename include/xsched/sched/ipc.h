@@ -3,6 +3,7 @@
 // the client's pid — the reference's key assignment, protocol/include/xsched/protocol/def.h:35-37).
 // The reference uses its un-vendored `ipc` library here, whose transport is not part of its tree.
 #pragma once
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <vector>
@@ -37,7 +38,10 @@ private:
     int fd_ = -1;
     uint64_t key_ = 0;
     bool bound_ = false;
-    volatile bool closed_ = false;
+    std::atomic<bool> closed_{false};
+    // Own address, kept from Bind() so that Close() needs no allocation (it may run in a signal handler).
+    unsigned char self_addr_[128] = {};
+    unsigned self_addr_len_ = 0;
 };
 
 } // namespace xsched::sched

@@ -255,6 +255,41 @@ static int Drop(int64_t level, int count, int64_t spin_us) {
     return 0;
 }
 
+// ---- host-path cost: zero-length commands through one XQueue --------------------------------------
+// Submit rate of the application thread and end-to-end rate (submit .. last command retired) with the
+// window doing its work (every batch-th command is waited for).  Round trips: submit -> WaitAll of a
+// single zero-length command, the shortest path a synchronous caller sees.
+static int Tput(int64_t level, int count, int64_t th, int64_t bs) {
+    XQueueHandle xq = MakeQueue(level, th, bs);
+    for (int i = 0; i < 2000; ++i) { HwCommandHandle c = 0; CHECK(HostLaneCommandCreate(&c, 0)); HostLaneCommandRelease(c); CHECK(XQueueSubmit(xq, c)); }
+    CHECK(XQueueWaitAll(xq));
+    const int64_t t0 = NowNs();
+    for (int i = 0; i < count; ++i) {
+        HwCommandHandle c = 0;
+        CHECK(HostLaneCommandCreate(&c, 0));
+        HostLaneCommandRelease(c);
+        CHECK(XQueueSubmit(xq, c));
+    }
+    const int64_t t1 = NowNs();
+    CHECK(XQueueWaitAll(xq));
+    const int64_t t2 = NowNs();
+    std::vector<double> rt;
+    for (int i = 0; i < 2000; ++i) {
+        const int64_t a = NowNs();
+        HwCommandHandle c = 0;
+        CHECK(HostLaneCommandCreate(&c, 0));
+        HostLaneCommandRelease(c);
+        CHECK(XQueueSubmit(xq, c));
+        CHECK(XQueueWaitAll(xq));
+        rt.push_back((NowNs() - a) / 1e3);
+    }
+    std::printf("{\"level\": %" PRId64 ", \"count\": %d, \"submit_ns_per_cmd\": %.1f, \"end_to_end_ns_per_cmd\": %.1f, "
+                "\"round_trip_p50_us\": %.2f, \"round_trip_p99_us\": %.2f}\n",
+                level, count, (double)(t1 - t0) / count, (double)(t2 - t0) / count, Pct(rt, 0.5), Pct(rt, 0.99));
+    XQueueDestroy(xq);
+    return 0;
+}
+
 // ---- two queues under highest-priority-first ------------------------------------------------------
 struct HpResult { std::vector<double> lat_us; double lp_total_ms = 0; };
 
@@ -360,6 +395,7 @@ int main(int argc, char **argv) {
     if (s == "suspend") return Suspend(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "drop") return Drop(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "hpf") return Hpf(I(2, 1), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL");
+    if (s == "tput") return Tput(I(2, 1), (int)I(3, 200000), I(4, 16), I(5, 8));
     if (s == "lax") return Hpf(I(2, 2), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL", I(11, 5000));
     if (s == "config0") return Config0(I(2, 1), (int)I(3, 3000), I(4, 1000), I(5, 2000), (double)I(6, 20), (uint64_t)I(7, 42), I(8, 16), I(9, 8),
                                        argc > 10 ? argv[10] : "LCL");

@@ -14,7 +14,7 @@ struct GlobalScheduler::Impl {
     IpcEndpoint recv;
     IpcEndpoint send;
     std::thread worker;
-    bool running = false;
+    std::atomic<bool> running{false};
 };
 
 GlobalScheduler::GlobalScheduler() : Scheduler(kSchedulerGlobal), impl_(std::make_unique<Impl>()) {}

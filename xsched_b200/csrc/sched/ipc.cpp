@@ -38,6 +38,9 @@ bool IpcEndpoint::Bind(uint64_t key) {
     const socklen_t len = MakeAddr(key, addr);
     if (::bind(fd_, (sockaddr *)&addr, len) != 0) { ::close(fd_); fd_ = -1; return false; }
     key_ = key;
+    static_assert(sizeof(sockaddr_un) <= sizeof(self_addr_), "own address does not fit");
+    std::memcpy(self_addr_, &addr, sizeof(addr));
+    self_addr_len_ = (unsigned)len;
     bound_ = true;
     return true;
 }
@@ -91,17 +94,15 @@ long IpcEndpoint::ReceiveAuto(void *buf, size_t cap) {
     }
 }
 
+// Async-signal-safe (socket / sendto / close only): the server calls it from its signal handler.
 void IpcEndpoint::Close() {
-    if (closed_) return;
-    closed_ = true;
+    if (closed_.exchange(true)) return;
     if (fd_ >= 0 && bound_) {
         // wake a blocked Receive with an empty datagram to ourselves
         const int s = ::socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
         if (s >= 0) {
-            sockaddr_un addr;
-            const socklen_t len = MakeAddr(key_, addr);
             char z = 0;
-            ::sendto(s, &z, 0, 0, (sockaddr *)&addr, len);
+            ::sendto(s, &z, 0, 0, (const sockaddr *)self_addr_, (socklen_t)self_addr_len_);
             ::close(s);
         }
     }
