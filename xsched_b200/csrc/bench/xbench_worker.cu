@@ -4,6 +4,7 @@
 //                XQueue at the given preemption level until --duration-s elapses (or SIGTERM);
 //   --role hp    a high-priority request every --period-us (vecadd | sort), latency = submit -> wait;
 //   --role both  the two roles as two threads / two XQueues of ONE process (in-process scheduler);
+//   --role level-sweep   the reference's level-1 suspend-latency sweep over sleep kernels of 10..2000 us;
 //   --role preempt-latency
 //                the reference's preemption-latency experiment (platforms/cuda/test/main/level.cu:37-86):
 //                a background thread keeps the queue full while the main thread times
@@ -451,6 +452,64 @@ static int PreemptLatency(const Args &a) {
 
 #include <numeric>
 
+// ---- the reference's level-1 latency sweep ------------------------------------------------------------
+// Same experiment as the reference's platforms/cuda/test/main/level.cu:37-176 at preemption level 1: a
+// background thread keeps rounds of 64 `Sleep<<<64,64>>>` kernels of a fixed duration going through an
+// XQueue with launch configuration (8, 4); the main thread times `count` XQueueSuspend(SyncHwQueue) /
+// XQueueResume pairs at random moments.  At level 1 a suspension waits for the kernels already handed to
+// the driver, so the latency is about (commands in flight) x (kernel duration).
+__global__ void SleepKernel(long long ns) {
+    long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    while (true) {
+        long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 >= ns) break;
+    }
+}
+static XResult LaunchSleep(HwQueueHandle hwq, void *data) {
+    SleepKernel<<<64, 64, 0, (cudaStream_t)(uintptr_t)hwq>>>((long long)(intptr_t)data * 1000);
+    return cudaGetLastError() == cudaSuccess ? kXSchedSuccess : kXSchedErrorHardware;
+}
+static int LevelSweep(const Args &a) {
+    Args qa = a;
+    qa.threshold = 8; qa.batch = 4;
+    Queue q = MakeQueue(qa, kPreemptLevelBlock, 0);
+    std::printf("{\"role\": \"level-sweep\", \"level\": 1, \"launch_config\": [8, 4], \"pairs\": %d, \"sweep\": [", a.count);
+    bool first = true;
+    for (int64_t us : {10, 30, 90, 100, 500, 1000, 2000}) {
+        std::atomic<bool> stop{false};
+        std::thread bg([&] {
+            while (!stop.load()) {
+                for (int i = 0; i < 64; ++i) {
+                    HwCommandHandle c;
+                    XK(HwCommandCreateCallback(&c, LaunchSleep, (void *)(intptr_t)us));
+                    XK(XQueueSubmit(q.xq, c));
+                }
+                XK(XQueueWaitAll(q.xq));
+            }
+        });
+        SleepUs(50000);
+        std::mt19937 rng((unsigned)a.seed);
+        std::vector<double> pre;
+        for (int i = 0; i < a.count; ++i) {
+            SleepUs(rng() % (2 * us + 200));
+            const int64_t t0 = NowNs();
+            XK(XQueueSuspend(q.xq, kQueueSuspendFlagSyncHwQueue));
+            pre.push_back((NowNs() - t0) / 1e3);
+            SleepUs(200 + rng() % 300);
+            XK(XQueueResume(q.xq, kQueueResumeFlagNone));
+        }
+        stop.store(true);
+        bg.join();
+        std::printf("%s{\"kernel_us\": %lld, \"avg_us\": %.1f, \"p50_us\": %.1f, \"p95_us\": %.1f, \"p99_us\": %.1f}", first ? "" : ", ", (long long)us,
+                    std::accumulate(pre.begin(), pre.end(), 0.0) / std::max<size_t>(1, pre.size()), Pct(pre, 0.5), Pct(pre, 0.95), Pct(pre, 0.99));
+        first = false;
+    }
+    std::printf("]}\n");
+    return 0;
+}
+
 // ---- baseline without XSched: native CUDA stream priorities, one process, two streams ----------------
 // LP: the non-preemptible twin of the low-priority kernel back-to-back on a least-priority stream (two
 // launches kept in flight); HP: the high-priority kernel every period on a greatest-priority stream.
@@ -516,6 +575,7 @@ int main(int argc, char **argv) {
     prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);
     if (a.role == "preempt-latency") return PreemptLatency(a);
     if (a.role == "native-priority") return NativePriority(a);
+    if (a.role == "level-sweep") return LevelSweep(a);
     if (a.role == "lp") {
         Queue q = MakeQueue(a, a.level, a.prio);
         LpWork w = BuildLp(a, q, 0);
