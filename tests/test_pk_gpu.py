@@ -281,3 +281,41 @@ def test_gemm_preempt_resume_bit_exact(pk, ok, flags_name):
     assert t.query().tiles_done == t.query().tiles_total
     assert torch.equal(c, base)
     t.destroy()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_task_calls_from_a_thread_on_another_device(pk):
+    """Launch / reset / flag writes switch to the task's device for the call: a worker thread that never chose a
+    device (it is on device 0) can drive a task that lives on device 1."""
+    import threading
+    with torch.cuda.device(1):
+        n = 1 << 22
+        b = torch.rand(n, device="cuda:1"); c = torch.rand(n, device="cuda:1"); a = torch.empty(n, device="cuda:1")
+        stream = torch.cuda.Stream(device=1)
+        t = pk.Task.triad(a, b, c, 1.5)
+        torch.cuda.synchronize()
+    errors = []
+
+    def run():
+        try:
+            assert torch.cuda.current_device() == 0
+            t.reset(stream.cuda_stream)
+            t.set_flag(0)
+            t.launch(stream.cuda_stream)
+            info = t.wait()
+            assert info.status == pk.STATUS_COMPLETED
+            assert torch.cuda.current_device() == 0           # the caller's device is put back
+        except Exception as e:                                # noqa: BLE001
+            errors.append(e)
+    th = threading.Thread(target=run)
+    th.start(); th.join()
+    assert not errors, errors
+    torch.cuda.synchronize(1)
+    ref = torch.empty_like(a)
+    t2 = None
+    with torch.cuda.device(1):
+        t2 = pk.Task.triad(ref, b, c, 1.5, flags=pk.FLAG_NON_PREEMPTIBLE)
+        t2.launch(stream.cuda_stream); t2.wait()
+        torch.cuda.synchronize()
+    assert torch.equal(a, ref)
+    t.destroy(); t2.destroy()

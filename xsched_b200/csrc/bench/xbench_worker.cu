@@ -408,6 +408,7 @@ static int PreemptLatency(const Args &a) {
     LpWork w = BuildLp(la, q, 0);
     std::atomic<bool> stop{false};
     std::thread bg([&] {
+        CK(cudaSetDevice(a.device));
         size_t i = 0;
         const size_t depth = w.tasks.size();
         while (!stop.load()) {
@@ -480,6 +481,7 @@ static int LevelSweep(const Args &a) {
     for (int64_t us : {10, 30, 90, 100, 500, 1000, 2000}) {
         std::atomic<bool> stop{false};
         std::thread bg([&] {
+            CK(cudaSetDevice(a.device));
             while (!stop.load()) {
                 for (int i = 0; i < 64; ++i) {
                     HwCommandHandle c;
@@ -536,6 +538,7 @@ static int NativePriority(const Args &a) {
     std::atomic<bool> stop{false};
     std::atomic<uint64_t> iters{0};
     std::thread lp([&] {
+        CK(cudaSetDevice(a.device));
         cudaEvent_t ev[2];
         CK(cudaEventCreateWithFlags(&ev[0], cudaEventDisableTiming)); CK(cudaEventCreateWithFlags(&ev[1], cudaEventDisableTiming));
         uint64_t i = 0;
@@ -598,7 +601,7 @@ int main(int argc, char **argv) {
         HpWork hw = BuildHp(a, qh);
         std::atomic<bool> ready{false}, lp_done{false};
         LpResult lr;
-        std::thread lp([&] { lr = RunLp(a, ql, lw, &ready, a.duration_s); lp_done.store(true); });
+        std::thread lp([&] { CK(cudaSetDevice(a.device)); lr = RunLp(a, ql, lw, &ready, a.duration_s); lp_done.store(true); });
         while (!ready.load()) SleepUs(1000);
         HpResult hr = RunHp(a, qh, hw, a.count, &lp_done);
         g_stop.store(true);

@@ -106,6 +106,24 @@ DeviceState *device_state(int *dev_out) {
     return &d;
 }
 
+// Makes the task's device current for the duration of a call and puts the caller's device back.  The
+// entry points that take a task may be called from any thread (a worker thread that never called
+// cudaSetDevice is on device 0), while the task's memory and streams belong to the device it was
+// created on.
+class DeviceGuard {
+public:
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev_) != cudaSuccess) { prev_ = -1; return; }
+        if (prev_ != device) { if (cudaSetDevice(device) == cudaSuccess) switched_ = true; }
+    }
+    ~DeviceGuard() { if (switched_) cudaSetDevice(prev_); }
+    DeviceGuard(const DeviceGuard &) = delete;
+    DeviceGuard &operator=(const DeviceGuard &) = delete;
+private:
+    int prev_ = -1;
+    bool switched_ = false;
+};
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 xpkResult task_common(xpkTask_st *t, uint32_t kind, uint32_t flags, unsigned long long total, uint32_t *flag_dev) {
@@ -178,6 +196,14 @@ xpkResult xpkFlagDestroy(uint32_t *flag_dev) {
 
 xpkResult xpkFlagSet(uint32_t *flag_dev, uint32_t value, void *ctrl_stream) {
     if (!flag_dev) return XPK_ERR_INVALID_VALUE;
+    // The write goes through a stream of the device that owns the flag, whatever device the caller is on.
+    cudaPointerAttributes attr;
+    int owner = -1;
+    if (cudaPointerGetAttributes(&attr, flag_dev) == cudaSuccess && attr.type == cudaMemoryTypeDevice) owner = attr.device;
+    else cudaGetLastError();
+    int cur = 0;
+    cudaGetDevice(&cur);
+    DeviceGuard on_flag_device(owner >= 0 ? owner : cur);
     DeviceState *d = device_state(nullptr);
     if (!d) return XPK_ERR_CUDA;
     cudaStream_t s = ctrl_stream ? (cudaStream_t)ctrl_stream : d->ctrl;
@@ -284,6 +310,7 @@ xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void 
 
 xpkResult xpkTaskLaunch(xpkTask_t t, void *stream, int sm_limit) {
     if (!t) return XPK_ERR_INVALID_VALUE;
+    DeviceGuard on_task_device(t->device);
     DeviceState *d = device_state(nullptr);
     if (!d) return XPK_ERR_CUDA;
     cudaStream_t s = (cudaStream_t)stream;
@@ -374,6 +401,7 @@ xpkResult xpkTaskWait(xpkTask_t t, uint64_t timeout_us, xpkTaskInfo *info) {
 
 xpkResult xpkTaskReset(xpkTask_t t, void *stream) {
     if (!t) return XPK_ERR_INVALID_VALUE;
+    DeviceGuard on_task_device(t->device);
     cudaStream_t s = (cudaStream_t)stream;
     if (cudaMemsetAsync(t->ctl, 0, xpk::kCtlResetBytes, s) != cudaSuccess) return XPK_ERR_CUDA;
     if (t->kind == XPK_KIND_SORT) {
@@ -397,6 +425,7 @@ xpkResult xpkTaskKind(xpkTask_t t, uint32_t *kind) {
 
 xpkResult xpkTaskDestroy(xpkTask_t t) {
     if (!t) return XPK_ERR_INVALID_VALUE;
+    DeviceGuard on_task_device(t->device);
     task_free(t);
     return XPK_SUCCESS;
 }
