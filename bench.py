@@ -112,6 +112,53 @@ def run_json(cmd: list[str], env: dict, timeout: float) -> list[dict]:
     return [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
 
 
+def run_hp_marking(cmd: list[str], env: dict, timeout: float, lps: list) -> list[dict]:
+    """Run a high-priority process to completion while low-priority workers `lps` (Popen objects) are running.
+    When the HP process prints READY (warmed up, about to issue requests) every LP worker gets SIGUSR1 and
+    restarts its count; when it prints DONE (last request served; or, failing that, when it exits) they get a
+    second SIGUSR1 and freeze it: the LP rate then covers exactly the interval in which requests were being
+    served, not the HP process's start-up, verification and tear-down."""
+    import tempfile
+    err = tempfile.TemporaryFile(mode="w+")
+    hp = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=err, text=True, env=env)
+    lines: list[str] = []
+    marked = closed = False
+    t0 = time.time()
+
+    def mark_all():
+        for p in lps:
+            if p.poll() is None:
+                p.send_signal(signal.SIGUSR1)
+
+    def reader():
+        nonlocal marked, closed
+        for line in hp.stdout:
+            if line.startswith("READY") and not marked:
+                marked = True
+                mark_all()
+            elif line.startswith("DONE") and marked and not closed:
+                closed = True
+                mark_all()
+            lines.append(line)
+    th = threading.Thread(target=reader, daemon=True)
+    th.start()
+    try:
+        hp.wait(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        hp.kill()
+        err.seek(0)
+        raise RuntimeError(f"{' '.join(cmd[:4])} timed out after {timeout:.0f} s; stderr: {err.read()[-1500:]}")
+    th.join(timeout=10)
+    if marked and not closed:
+        mark_all()
+    elif not marked:
+        print(f"[bench] {cmd[0]} printed no READY line after {time.time() - t0:.0f} s: LP window not marked", file=sys.stderr)
+    if hp.returncode != 0:
+        err.seek(0)
+        raise RuntimeError(f"{' '.join(cmd[:4])} failed rc={hp.returncode}: {err.read()[-1500:]}")
+    return [json.loads(l) for l in lines if l.startswith("{")]
+
+
 def read_samples(path: str) -> list[float]:
     try:
         with open(path) as f:
@@ -166,8 +213,8 @@ def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, 
         # budget: every request takes at most a few periods even when things go badly
         hp_timeout = 60 + (steps + warmup) * period_us * 20 / 1e6
         samples_path = tempfile.mktemp(prefix="xsched_hp_", suffix=".txt")
-        hp = run_json(worker_cmd("hp", device, level=level, prio=1, count=steps + warmup, period_us=period_us, hp_n=HP_N,
-                                 e2e=int(e2e), samples=samples_path), hp_env, timeout=hp_timeout)[-1]
+        hp = run_hp_marking(worker_cmd("hp", device, level=level, prio=1, count=steps + warmup, period_us=period_us, hp_n=HP_N,
+                                       e2e=int(e2e), samples=samples_path), hp_env, hp_timeout, [lp])[-1]
         hp["samples_us"] = read_samples(samples_path)[warmup:]
         mark(f"corun level {level}: HP done")
     finally:
@@ -222,8 +269,8 @@ def transparent_corun(device: int, shim_lib: Path, steps: int, threshold: int, b
             if lp.poll() is not None or time.time() - t0 > 90:
                 lp_err.seek(0)
                 raise RuntimeError(f"transparent LP worker not ready (rc {lp.poll()}): " + lp_err.read()[-600:])
-        hp = run_json([pw, "--role", "hp", "--device", str(device), "--count", str(steps), "--period-us", str(PERIOD_US), "--hp-n", str(HP_N)],
-                      dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="1"), timeout=60 + steps * PERIOD_US * 30 / 1e6)[-1]
+        hp = run_hp_marking([pw, "--role", "hp", "--device", str(device), "--count", str(steps), "--period-us", str(PERIOD_US), "--hp-n", str(HP_N)],
+                            dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="1"), 60 + steps * PERIOD_US * 30 / 1e6, [lp])[-1]
     finally:
         lp.send_signal(signal.SIGTERM)
         try:
@@ -422,7 +469,8 @@ def config4(args) -> None:
             env_co = dict(hp_env)
             if policy == "LAX":
                 env_co["XSCHED_AUTO_XQUEUE_LAXITY"] = str(laxity_us)
-            dec_co = run_json(dec + ["--requests", str(args.config4_requests), "--rate", "2.0", "--samples", samples], env_co, 900)[-1]
+            dec_co = run_hp_marking(dec + ["--requests", str(args.config4_requests), "--rate", "2.0", "--samples", samples], env_co, 900,
+                                    [p for p, _ in procs.values()])[-1]
         finally:
             lp_co = {k: stop_lp(p) for k, (p, _) in procs.items()}
         res = {"elapsed": time.time() - t0, "dec_alone": dec_alone, "dec_co": dec_co, "tok_ms": read_samples(samples), "lp_alone": lp_alone, "lp_co": lp_co,
@@ -605,8 +653,8 @@ def main() -> None:
                     while not lp3.stdout.readline().startswith("READY"):
                         if lp3.poll() is not None or time.time() - t_wait > 90:
                             raise RuntimeError("config 3 LP worker not ready")
-                    sort_co = run_json(worker_cmd("hp", device, level=2, prio=1, count=300, period_us=5000, hp_kernel="sort", hp_n=1 << 24),
-                                       dict(env3, XSCHED_IPC_SPIN="OFF"), 180)[-1]
+                    sort_co = run_hp_marking(worker_cmd("hp", device, level=2, prio=1, count=300, period_us=5000, hp_kernel="sort", hp_n=1 << 24),
+                                             dict(env3, XSCHED_IPC_SPIN="OFF"), 180, [lp3])[-1]
                 finally:
                     lp3.send_signal(signal.SIGTERM)
                     out3, _ = lp3.communicate(timeout=120)
@@ -648,7 +696,7 @@ def main() -> None:
                     while not lp2.stdout.readline().startswith("READY"):
                         if lp2.poll() is not None or time.time() - t_wait > 90:
                             raise RuntimeError("config 2 LP worker not ready")
-                    dec_co = run_json(dec, env2, 600)[-1]
+                    dec_co = run_hp_marking(dec, env2, 600, [lp2])[-1]
                 finally:
                     lp2.send_signal(signal.SIGTERM)
                     out2, _ = lp2.communicate(timeout=120)

@@ -26,6 +26,9 @@
 
 static std::atomic<bool> g_stop{false};
 static void OnTerm(int) { g_stop.store(true); }
+// SIGUSR1: first = restart the count (co-run begins), second = freeze it (co-run over).
+static std::atomic<int> g_marks{0};
+static void OnMark(int) { g_marks.fetch_add(1); }
 static int64_t NowNs() { return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 static double Pct(std::vector<double> v, double p) {
     if (v.empty()) return 0;
@@ -52,6 +55,7 @@ int main(int argc, char **argv) {
         else if (k == "--M") M = std::atoi(v.c_str()); else if (k == "--N") N = std::atoi(v.c_str()); else if (k == "--K") K = std::atoi(v.c_str());
         else if (k == "--in-flight") in_flight = std::atoi(v.c_str()); else if (k == "--duration-s") duration_s = std::atof(v.c_str());
     }
+    std::signal(SIGUSR1, OnMark);
     std::signal(SIGTERM, OnTerm);
     std::signal(SIGINT, OnTerm);
     CK(cudaSetDevice(device));
@@ -71,10 +75,17 @@ int main(int argc, char **argv) {
             PK(xpkTaskCreateGemm(&tasks[i], C, A, B, M, N, K, XPK_FLAG_NON_PREEMPTIBLE, nullptr));
             CK(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
         }
-        uint64_t iters = 0, counted_from = 0;
-        int64_t t_begin = 0;
+        uint64_t iters = 0, counted_from = 0, frozen_at = 0;
+        int64_t t_begin = 0, t_frozen = 0;
+        int marks_seen = 0;
         const int64_t t_start = NowNs();
         while (!g_stop.load()) {
+            const int marks = g_marks.load();
+            if (marks != marks_seen && t_begin) {
+                if (marks_seen == 0) { counted_from = iters; t_begin = NowNs(); }
+                if (marks >= 2 && !t_frozen) { frozen_at = iters; t_frozen = NowNs(); }
+                marks_seen = marks;
+            }
             if (!t_begin && (NowNs() - t_start) > 500000000) {
                 CK(cudaStreamSynchronize(s));
                 counted_from = iters;
@@ -90,9 +101,10 @@ int main(int argc, char **argv) {
             ++iters;
         }
         CK(cudaStreamSynchronize(s));
-        const double sec = t_begin ? (NowNs() - t_begin) / 1e9 : 0;
-        std::printf("{\"role\": \"plain-lp\", \"iters\": %" PRIu64 ", \"seconds\": %.4f, \"rate\": %.3f, \"unit\": \"TFLOP/s\"}\n", iters - counted_from, sec,
-                    sec > 0 ? (iters - counted_from) * 2.0 * M * N * K / sec / 1e12 : 0.0);
+        const double sec = t_begin ? ((t_frozen ? t_frozen : NowNs()) - t_begin) / 1e9 : 0;
+        const uint64_t counted = (t_frozen ? frozen_at : iters) - counted_from;
+        std::printf("{\"role\": \"plain-lp\", \"iters\": %" PRIu64 ", \"seconds\": %.4f, \"rate\": %.3f, \"unit\": \"TFLOP/s\"}\n", counted, sec,
+                    sec > 0 ? counted * 2.0 * M * N * K / sec / 1e12 : 0.0);
         return 0;
     }
 
@@ -120,6 +132,7 @@ int main(int argc, char **argv) {
         lat.push_back(once());
         if (NowNs() > next + period_us * 1000) next = NowNs();
     }
+    std::printf("DONE\n"); std::fflush(stdout);
     float h[4];
     CK(cudaMemcpy(h, c + 1000, 16, cudaMemcpyDeviceToHost));
     const bool ok = h[0] == 3.0f * 1000 && h[1] == 3.0f * 1001;

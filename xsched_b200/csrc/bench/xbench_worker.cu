@@ -38,6 +38,11 @@
 
 static std::atomic<bool> g_stop{false};
 static void OnTerm(int) { g_stop.store(true); }
+// SIGUSR1 delimits the measurement window of a long-running low-priority loop: the first one restarts the
+// count (the high-priority process has warmed up and begins its requests now), the second one freezes it
+// (the requests are over), so that the reported rate covers exactly the co-run interval.
+static std::atomic<int> g_marks{0};
+static void OnMark(int) { g_marks.fetch_add(1); }
 static int64_t NowNs() { return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 static void SleepUs(int64_t us) { if (us > 0) std::this_thread::sleep_for(std::chrono::microseconds(us)); }
 static double Pct(std::vector<double> v, double p) {
@@ -229,22 +234,34 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
     const size_t depth = w.tasks.size();
     std::vector<uint64_t> uses(depth, 0);
     // A task object may be re-submitted only after its previous command completed.  That is read from
-    // the task's mailbox (no queue drain): the slot's k-th command is done once the task has been
-    // launched at least k times and its newest launch reports COMPLETED.
+    // the task's mailbox (no queue drain).  A preempted command is launched more than once, so the launch
+    // count alone does not tell which submission a COMPLETED status belongs to: the slot remembers the
+    // launch count at which its previous submission was seen complete, and the next one is complete when
+    // the task reports COMPLETED at a larger count (a completed task is not launched again before it is
+    // re-submitted).
+    std::vector<uint64_t> seen_complete_at(depth, 0);
+    for (size_t i = 0; i < depth; ++i) { xpkTaskInfo info; PK(xpkTaskQuery(w.tasks[i], &info)); seen_complete_at[i] = info.launches; }
     auto wait_slot = [&](size_t slot) {
         if (uses[slot] == 0) return;
         while (!g_stop.load()) {
             xpkTaskInfo info;
             PK(xpkTaskQuery(w.tasks[slot], &info));
-            if (info.launches >= uses[slot] && info.status == XPK_STATUS_COMPLETED) return;
+            if (info.launches > seen_complete_at[slot] && info.status == XPK_STATUS_COMPLETED) { seen_complete_at[slot] = info.launches; return; }
             if (info.status == XPK_STATUS_ERROR) { std::fprintf(stderr, "task error %#x\n", info.error); std::exit(7); }
             SleepUs(20);
         }
     };
-    int64_t t_begin = 0;
-    uint64_t submitted = 0, counted_from = 0;
+    int64_t t_begin = 0, t_frozen = 0;
+    uint64_t submitted = 0, counted_from = 0, frozen_at = 0;
+    int marks_seen = 0;
     const int64_t t_start = NowNs();
     while (!g_stop.load()) {
+        const int marks = g_marks.load();
+        if (marks != marks_seen && t_begin) {
+            if (marks_seen == 0) { counted_from = submitted; t_begin = NowNs(); }               // window opens
+            if (marks >= 2 && !t_frozen) { frozen_at = submitted; t_frozen = NowNs(); }        // window closes
+            marks_seen = marks;
+        }
         const double el = (NowNs() - t_start) / 1e9;
         if (t_begin == 0 && el >= a.warmup_s) {
             XK(XQueueWaitAll(q.xq));
@@ -262,8 +279,8 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
         ++submitted;
     }
     XK(XQueueWaitAll(q.xq));
-    r.seconds = t_begin ? (NowNs() - t_begin) / 1e9 : 0;
-    r.iters = submitted - counted_from;
+    r.seconds = t_begin ? ((t_frozen ? t_frozen : NowNs()) - t_begin) / 1e9 : 0;
+    r.iters = (t_frozen ? frozen_at : submitted) - counted_from;
     r.rate = r.seconds > 0 ? r.iters * w.work_per_iter / r.seconds : 0;
     r.got = DeviceChecksum(w.out, w.out_words, q.stream);
     for (auto t : w.tasks) { xpkTaskInfo info; PK(xpkTaskQuery(t, &info)); r.preemptions += info.preemptions; }
@@ -571,6 +588,7 @@ static int NativePriority(const Args &a) {
 
 int main(int argc, char **argv) {
     Args a = Parse(argc, argv);
+    std::signal(SIGUSR1, OnMark);
     std::signal(SIGTERM, OnTerm);
     std::signal(SIGINT, OnTerm);
     CK(cudaSetDevice(a.device));
@@ -591,6 +609,7 @@ int main(int argc, char **argv) {
         HpWork w = BuildHp(a, q);
         std::printf("READY\n"); std::fflush(stdout);
         HpResult r = RunHp(a, q, w, a.count, nullptr);
+        std::printf("DONE\n"); std::fflush(stdout);              // requests are over; what follows is verification
         PrintHp(a, w, r, VerifyHp(q, w));
         return 0;
     }

@@ -102,6 +102,7 @@ def main() -> None:
                 x, _ = step(x, (r * a.tokens + t) % a.kv)
                 tok_ms.append((time.perf_counter() - t0) * 1e3)
             req_ms.append((time.perf_counter() - t_arr) * 1e3)
+    print("DONE", flush=True)
     if a.samples:
         with open(a.samples, "w") as f:
             f.write("\n".join(f"{v:.4f}" for v in tok_ms))
