@@ -255,6 +255,100 @@ static int Drop(int64_t level, int count, int64_t spin_us) {
     return 0;
 }
 
+// ---- seeded random walk over the C API ------------------------------------------------------------
+// Two XQueues on one lane, a seeded sequence of API calls (submit bursts, wait, suspend/resume with random
+// flags, launch-config and level changes, hints, queries, profile counts).  Everything printed is
+// independent of timing: the result code of every call, the submitted-command counters, the queue state at
+// quiescent points, and at the end whether everything that was not dropped ran exactly once.
+static int Fuzz(uint64_t seed, int steps) {
+    CHECK(XHintSetScheduler(kSchedulerAppManaged, kPolicyUnknown));
+    std::mt19937_64 rng(seed);
+    struct Q { XQueueHandle xq; HwQueueHandle hwq; bool suspended = false; int64_t level; int64_t submitted = 0; bool dropped = false; };
+    Q q[2];
+    for (int i = 0; i < 2; ++i) { q[i].level = 1 + (int64_t)(rng() % 2); q[i].xq = MakeQueue(q[i].level, 4, 2, &q[i].hwq); }
+    std::printf("{\"seed\": %" PRIu64 ", \"codes\": [", seed);
+    bool first = true;
+    auto out = [&](const char *op, int64_t v) { std::printf("%s[\"%s\", %" PRId64 "]", first ? "" : ", ", op, v); first = false; };
+    const uint64_t exec0 = Executed();
+    int64_t total_submitted = 0;
+    for (int s = 0; s < steps; ++s) {
+        Q &x = q[rng() % 2];
+        switch (rng() % 10) {
+        case 0: case 1: case 2: {                                  // a burst of short commands
+            const int n = 1 + (int)(rng() % 6);
+            for (int i = 0; i < n; ++i) {
+                HwCommandHandle c = 0;
+                CHECK(HostLaneCommandCreate(&c, 50 + (int64_t)(rng() % 150)));
+                HostLaneCommandRelease(c);
+                out("submit", (int64_t)XQueueSubmit(x.xq, c));
+                ++x.submitted; ++total_submitted;
+            }
+            break;
+        }
+        case 3:
+            if (!x.suspended) {
+                out("wait_all", (int64_t)XQueueWaitAll(x.xq));
+                XQueueState st = kQueueStateUnknown;
+                out("query", (int64_t)XQueueQuery(x.xq, &st));
+                out("state_after_wait", (int64_t)st);
+            }
+            break;
+        case 4: {
+            const int64_t flags = (rng() % 2) ? kQueueSuspendFlagSyncHwQueue : kQueueSuspendFlagNone;
+            out("suspend", (int64_t)XQueueSuspend(x.xq, flags));
+            x.suspended = true;
+            break;
+        }
+        case 5: {
+            const bool drop = x.suspended && (rng() % 4 == 0);
+            out("resume", (int64_t)XQueueResume(x.xq, drop ? kQueueResumeFlagDropCommands : kQueueResumeFlagNone));
+            if (drop && x.level >= 2) x.dropped = true;                 // level 1 ignores the drop flag
+            x.suspended = false;
+            break;
+        }
+        case 6:
+            if (!x.suspended) {
+                const int64_t bs = 1 + (int64_t)(rng() % 4), th = bs + (int64_t)(rng() % 6);
+                out("config", (int64_t)XQueueSetLaunchConfig(x.xq, th, bs));
+            }
+            break;
+        case 7:
+            if (!x.suspended) {
+                const int64_t level = 1 + (int64_t)(rng() % 2);
+                const XResult r = XQueueSetPreemptLevel(x.xq, (XPreemptLevel)level);
+                out("level", (int64_t)r);
+                if (r == kXSchedSuccess) x.level = level;
+            }
+            break;
+        case 8: {
+            int64_t cnt = -1;
+            out("count_rc", (int64_t)XQueueProfileHwCommandCount(x.xq, &cnt));
+            out("count", cnt);
+            break;
+        }
+        default:
+            out("hint", (int64_t)XHintPriority(x.xq, (Priority)((int)(rng() % 600) - 300)));
+            break;
+        }
+        if (rng() % 3 == 0) SleepUs((int64_t)(rng() % 400));
+    }
+    bool any_drop = false;
+    for (Q &x : q) {
+        if (x.suspended) out("final_resume", (int64_t)XQueueResume(x.xq, kQueueResumeFlagNone));
+        out("final_wait", (int64_t)XQueueWaitAll(x.xq));
+        XQueueState st = kQueueStateUnknown;
+        XQueueQuery(x.xq, &st);
+        out("final_state", (int64_t)st);
+        any_drop = any_drop || x.dropped;
+    }
+    SleepUs(3000);
+    const uint64_t ran = Executed() - exec0;
+    std::printf("], \"submitted\": %" PRId64 ", \"all_ran_unless_dropped\": %d, \"none_ran_twice\": %d}\n", total_submitted,
+                (int)(any_drop || ran == (uint64_t)total_submitted), (int)(ran <= (uint64_t)total_submitted));
+    for (Q &x : q) { XQueueDestroy(x.xq); }
+    return 0;
+}
+
 // ---- host-path cost: zero-length commands through one XQueue --------------------------------------
 // Submit rate of the application thread and end-to-end rate (submit .. last command retired) with the
 // window doing its work (every batch-th command is waited for).  Round trips: submit -> WaitAll of a
@@ -395,6 +489,7 @@ int main(int argc, char **argv) {
     if (s == "suspend") return Suspend(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "drop") return Drop(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "hpf") return Hpf(I(2, 1), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL");
+    if (s == "fuzz") return Fuzz((uint64_t)I(2, 1), (int)I(3, 200));
     if (s == "tput") return Tput(I(2, 1), (int)I(3, 200000), I(4, 16), I(5, 8));
     if (s == "lax") return Hpf(I(2, 2), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL", I(11, 5000));
     if (s == "config0") return Config0(I(2, 1), (int)I(3, 3000), I(4, 1000), I(5, 2000), (double)I(6, 20), (uint64_t)I(7, 42), I(8, 16), I(9, 8),

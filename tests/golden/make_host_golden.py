@@ -24,6 +24,11 @@ SCENARIOS = {
     "suspend_l2": ["suspend", "2", "40", "500"],
     "drop_l1": ["drop", "1", "40", "500"],
     "drop_l2": ["drop", "2", "40", "500"],
+    # seeded random walks over the C API (result codes, counters and quiescent states only)
+    "fuzz_seed_1": ["fuzz", "1", "200"],
+    "fuzz_seed_2": ["fuzz", "2", "200"],
+    "fuzz_seed_3": ["fuzz", "3", "200"],
+    "fuzz_seed_11": ["fuzz", "11", "300"],
 }
 
 
