@@ -1,0 +1,124 @@
+"""The libcuda interposer and the CUDA HAL on a machine WITHOUT a GPU: a host-only stand-in for the driver
+(tests/fake_cuda/fake_cuda.cpp: streams are threads, kernels are host functions) sits where the real
+libcuda.so.1 would, and a driver-API program (tests/fake_cuda/driver_app.cpp) runs on it directly and under
+the interposer.  The program checks every result itself and prints a checksum; under the interposer the
+checksum must be the same and every stream operation must have gone through an XQueue.  The same stack is
+also rebuilt under ThreadSanitizer and must run without a report."""
+import json
+import os
+import shutil
+import subprocess
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+LIB = ROOT / "xsched_b200" / "lib"
+FAKE_DIR = ROOT / "tests" / "fake_cuda"
+FAKE, APP = FAKE_DIR / "libcuda_fake.so", FAKE_DIR / "driver_app"
+CSRC = ROOT / "xsched_b200" / "csrc"
+CUDA_INC = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+CXX = os.environ.get("XSCHED_CXX", "/usr/bin/g++" if Path("/usr/bin/g++").exists() else (shutil.which("g++") or "g++"))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    if not (FAKE.exists() and APP.exists()):
+        from xsched_b200 import build
+        build.build_host()
+        build.build_fake_driver()
+    assert FAKE.exists() and APP.exists()
+
+
+def as_libcuda(tmp: Path, target: Path) -> Path:
+    d = tmp / target.stem
+    d.mkdir(exist_ok=True)
+    for name in ("libcuda.so.1", "libcuda.so"):
+        if not (d / name).exists():
+            os.symlink(target, d / name)
+    return d
+
+
+def run_app(libdir: Path, fake: Path, app: Path, rounds: int = 30, **extra):
+    """Run `app` with `libdir` (holding libcuda.so.1) first on the loader path."""
+    env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+    env.update(FAKE_CUDA_LIB=str(fake), LD_LIBRARY_PATH=f"{libdir}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""), XLOG_LEVEL="WARN")
+    env.update({k: str(v) for k, v in extra.items()})
+    return subprocess.run([str(app), str(rounds)], capture_output=True, text=True, env=env, timeout=300)
+
+
+@pytest.mark.parametrize("level,threshold,batch", [(1, 4, 2), (1, 1, 1), (2, 16, 8)])
+def test_driver_program_under_the_interposer_without_a_gpu(tmp_path, level, threshold, batch):
+    plain = run_app(as_libcuda(tmp_path, FAKE), FAKE, APP)
+    assert plain.returncode == 0 and plain.stdout.startswith("OK "), plain.stdout + plain.stderr
+    stats = tmp_path / "stats.json"
+    r = run_app(as_libcuda(tmp_path, LIB / "libshimcuda.so"), FAKE, APP, XSCHED_CUDA_LIB=FAKE, XSCHED_AUTO_XQUEUE="ON", XSCHED_POLICY="HPF",
+                XSCHED_AUTO_XQUEUE_LEVEL=level, XSCHED_AUTO_XQUEUE_THRESHOLD=threshold, XSCHED_AUTO_XQUEUE_BATCH_SIZE=batch,
+                XSCHED_SHIM_STATS_FILE=stats)
+    assert r.returncode == 0, r.stdout + r.stderr[-3000:]
+    assert r.stdout == plain.stdout
+    st = json.loads(stats.read_text())
+    assert st["streams_with_xqueue"] == 2
+    assert st["launches_queued"] == 30 * 3 and st["launches_direct"] == 0 and st["launches_blocking"] == 0
+    assert st["copies_queued"] == 30 * 6 and st["copies_direct"] == 0
+    assert st["copies_waited"] == 30 * 2             # the two copies into pageable memory per round
+    assert st["events_queued"] == 30
+
+
+def test_xsched_aware_program_on_the_cuda_hal_without_a_gpu(tmp_path):
+    """XQueue C API + CudaQueueCreate on fake streams, in-process HPF, level 1 with window (4, 2): every command
+    runs exactly once, a suspension waits at most for the window (4 x 500 us) and nothing of the suspended queue
+    runs until it is resumed (the program checks that itself)."""
+    hal_app = FAKE_DIR / "hal_app"
+    assert hal_app.exists(), "tests/fake_cuda/hal_app not built (python -m xsched_b200.build)"
+    r = run_app(as_libcuda(tmp_path, FAKE), FAKE, hal_app, XSCHED_CUDA_LIB=FAKE)
+    assert r.returncode == 0, r.stdout + r.stderr[-3000:]
+    res = json.loads(r.stdout.strip().splitlines()[-1])
+    assert res["ran"] == res["expected"]
+    assert res["suspend_max_us"] <= 4 * 500 + 2500
+    assert 300 <= res["hp_min_us"] and res["hp_max_us"] <= 300 + 4000
+
+
+def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
+    """Everything between the program and the fake driver — interposer, CUDA HAL, XQueue runtime, scheduler —
+    compiled with -fsanitize=thread (the driver is opened without RTLD_DEEPBIND in such a build)."""
+    srcs = [CSRC / "shim" / "shim.cpp"] + [p for d in ("hal_cuda", "preempt", "sched") for p in sorted((CSRC / d).glob("*.cpp"))]
+    common = [CXX, "-O1", "-g", "-fsanitize=thread", "-fPIC", "-pthread", f"-I{ROOT / 'include'}", f"-I{CSRC}", f"-I{CUDA_INC}"]
+
+    def compile_one(src: Path):
+        obj = tmp_path / (src.parent.name + "_" + src.stem + ".o")
+        r = subprocess.run(common + ["-std=c++20", "-DXSCHED_NO_DEEPBIND", "-c", "-o", str(obj), str(src)], capture_output=True, text=True)
+        return obj, r
+    with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        objs = []
+        for obj, r in pool.map(compile_one, srcs):
+            assert r.returncode == 0, r.stderr[-2000:]
+            objs.append(str(obj))
+    shim = tmp_path / "libshim_tsan.so"
+    r = subprocess.run(common + ["-shared", "-Wl,-soname,libcuda.so.1", "-o", str(shim)] + objs + [f"-L{LIB}", f"-Wl,-rpath,{LIB}", "-lxpk", "-ldl", "-lrt"],
+                       capture_output=True, text=True)
+    if r.returncode != 0 and ("cannot find" in r.stderr or "unrecognized" in r.stderr):
+        pytest.skip("toolchain has no ThreadSanitizer runtime")
+    assert r.returncode == 0, r.stderr[-2000:]
+    fake, app = tmp_path / "libcuda_fake_tsan.so", tmp_path / "driver_app_tsan"
+    for cmd in (common + ["-std=c++17", "-shared", "-Wl,-soname,libcuda.so.1", "-o", str(fake), str(FAKE_DIR / "fake_cuda.cpp"), "-ldl"],
+                common + ["-std=c++17", "-o", str(app), str(FAKE_DIR / "driver_app.cpp"), f"-L{FAKE_DIR / 'link'}", "-lcuda", "-ldl"]):
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr[-2000:]
+    # the XSched-aware program: the same objects without the interposer in front
+    hal_tsan = tmp_path / "hal_app_tsan"
+    no_shim = [o for o in objs if not o.endswith("shim_shim.o")]
+    r = subprocess.run(common + ["-std=c++17", f"-I{ROOT / 'include'}", "-o", str(hal_tsan), str(FAKE_DIR / "hal_app.cpp")] + no_shim +
+                       [f"-L{FAKE_DIR / 'link'}", f"-L{LIB}", f"-Wl,-rpath,{LIB}", "-lxpk", "-lcuda", "-ldl", "-lrt"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    r = run_app(as_libcuda(tmp_path, fake), fake, hal_tsan, XSCHED_CUDA_LIB=fake, TSAN_OPTIONS="halt_on_error=0")
+    text = r.stdout + r.stderr
+    assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
+    assert r.returncode == 0, text[-2000:]
+    for level in (1, 2):
+        r = run_app(as_libcuda(tmp_path, shim), fake, app, XSCHED_CUDA_LIB=fake, XSCHED_AUTO_XQUEUE="ON", XSCHED_POLICY="HPF",
+                    XSCHED_AUTO_XQUEUE_LEVEL=level, XSCHED_AUTO_XQUEUE_THRESHOLD=4, XSCHED_AUTO_XQUEUE_BATCH_SIZE=2, TSAN_OPTIONS="halt_on_error=0")
+        text = r.stdout + r.stderr
+        assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
+        assert r.returncode == 0 and r.stdout.startswith("OK "), text[-2000:]

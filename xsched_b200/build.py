@@ -201,7 +201,32 @@ def build_test_apps(force: bool = False, verbose: bool = False) -> Path | None:
             continue
         if force or _stale(out, [src]):
             _run([NVCC, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, src], verbose)
+    build_fake_driver(force, verbose)
     return out
+
+
+def build_fake_driver(force: bool = False, verbose: bool = False) -> Path | None:
+    """tests/fake_cuda — a host-only stand-in for the CUDA driver and a driver-API program on top of it, so that
+    the CUDA HAL and the interposer can be exercised on a machine without a GPU (test infrastructure)."""
+    d = ROOT / "tests" / "fake_cuda"
+    src, app_src = d / "fake_cuda.cpp", d / "driver_app.cpp"
+    if not src.exists():
+        return None
+    lib, app = d / "libcuda_fake.so", d / "driver_app"
+    if force or _stale(lib, [src]):
+        _run([CXX, "-std=c++17", "-O1", "-g", "-shared", "-fPIC", "-pthread", f"-I{CUDA_HOME}/include", "-Wl,-soname,libcuda.so.1",
+              "-o", lib, src, "-ldl"], verbose)
+    link = d / "link"
+    link.mkdir(exist_ok=True)
+    if not (link / "libcuda.so").exists():
+        os.symlink("../libcuda_fake.so", link / "libcuda.so")
+    if force or _stale(app, [app_src, lib]):
+        _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", "-o", app, app_src, f"-L{link}", "-lcuda", "-ldl", "-pthread"], verbose)
+    hal_src, hal_app = d / "hal_app.cpp", d / "hal_app"
+    if hal_src.exists() and (LIB / "libhalcuda.so").exists() and (force or _stale(hal_app, [hal_src, lib, LIB / "libhalcuda.so", LIB / "libpreempt.so"])):
+        _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", f"-I{INC}", "-o", hal_app, hal_src, f"-L{link}", f"-L{LIB}",
+              f"-Wl,-rpath,{LIB}", "-lhalcuda", "-lpreempt", "-lcuda", "-ldl", "-pthread"], verbose)
+    return app
 
 
 def build_lane_driver(force: bool = False, verbose: bool = False) -> Path | None:

@@ -14,16 +14,16 @@
 namespace xsched::cuda {
 
 void CompletionCounter::Wait(uint64_t ticket, int64_t expected_remaining_us) const {
-    if (*host >= ticket) return;
+    if (Load() >= ticket) return;
     // Phase 0: the work is known to need a while longer: sleep through half of it, looking in between.
     if (expected_remaining_us > 400) {
         int64_t budget = std::min<int64_t>(expected_remaining_us / 2, 5000);
-        while (budget > 0 && *host < ticket) {
+        while (budget > 0 && Load() < ticket) {
             const int64_t slice = std::min<int64_t>(budget, 500);
             std::this_thread::sleep_for(std::chrono::microseconds(slice));
             budget -= slice;
         }
-        if (*host >= ticket) return;
+        if (Load() >= ticket) return;
     }
     // Phase 1: spin with pause for ~100 us (a completion is usually that close); phase 2: yield the core
     // between looks for up to ~1 ms; phase 3: sleep in 20 us slices so a long kernel does not burn a core.
@@ -31,16 +31,16 @@ void CompletionCounter::Wait(uint64_t ticket, int64_t expected_remaining_us) con
     auto elapsed_us = [&] { return std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count(); };
     while (true) {
         for (int i = 0; i < 64; ++i) {
-            if (*host >= ticket) return;
+            if (Load() >= ticket) return;
             _mm_pause();
         }
         if (elapsed_us() > 100) break;
     }
     while (elapsed_us() < 1000) {
-        if (*host >= ticket) return;
+        if (Load() >= ticket) return;
         std::this_thread::yield();
     }
-    while (*host < ticket) std::this_thread::sleep_for(std::chrono::microseconds(20));
+    while (Load() < ticket) std::this_thread::sleep_for(std::chrono::microseconds(20));
 }
 
 uint64_t CompletionCounter::Issue(CUstream stream, CUresult *res) {
@@ -62,7 +62,7 @@ void CudaCommand::Synchronize() {
 CUresult CudaCommand::LaunchOn(CUstream stream, const std::shared_ptr<CompletionCounter> &counter) {
     CUresult r = Enqueue(stream);
     if (r != CUDA_SUCCESS) return r;
-    if (want_sync_) {
+    if (want_sync_.load(std::memory_order_acquire)) {
         // A relaunch after a flush takes a fresh ticket: the old write already executed behind the
         // flushed kernel and proves nothing.
         counter_ = counter;

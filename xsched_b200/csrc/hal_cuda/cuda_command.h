@@ -31,6 +31,8 @@ struct CompletionCounter {
     /// run), half of that is slept away first, so that a loop of millisecond kernels does not keep a core
     /// busy; 0 = unknown, no sleep.
     void Wait(uint64_t ticket, int64_t expected_remaining_us = 0) const;
+    /// The counter as the GPU last wrote it.
+    uint64_t Load() const { return __atomic_load_n(const_cast<const uint64_t *>(host), __ATOMIC_ACQUIRE); }
 };
 
 class CudaCommand : public preempt::HwCommand {
@@ -39,8 +41,8 @@ public:
     ~CudaCommand() override = default;
 
     void Synchronize() override;
-    bool Synchronizable() override { return want_sync_; }
-    bool EnableSynchronization() override { want_sync_ = true; return true; }
+    bool Synchronizable() override { return want_sync_.load(std::memory_order_acquire); }
+    bool EnableSynchronization() override { want_sync_.store(true, std::memory_order_release); return true; }
 
     /// Enqueue the work on `stream`, then (if waitable) the counter write that marks its completion.
     CUresult LaunchOn(CUstream stream, const std::shared_ptr<CompletionCounter> &counter);
@@ -57,7 +59,7 @@ protected:
     virtual CUresult Enqueue(CUstream stream) = 0;
 
 private:
-    bool want_sync_ = false;
+    std::atomic<bool> want_sync_{false};       // set by the window worker, read by waiting application threads
     std::shared_ptr<CompletionCounter> counter_;
     std::atomic<uint64_t> ticket_{0};      // 0 = not issued yet
 };

@@ -151,7 +151,7 @@ public:
     CUdeviceptr Flag() const { return flag_; }
     CUstream Stream() const { return stream_; }
     void FillStats(CudaQueueStats *s) const {
-        s->launched = stats_.launched.load(); s->completed = *counter_->host; s->window_stalls = 0;
+        s->launched = stats_.launched.load(); s->completed = counter_->Load(); s->window_stalls = 0;
         s->deactivations = stats_.deactivations.load(); s->relaunches = stats_.relaunches.load();
         s->last_preempt_ns = stats_.last_preempt_ns.load();
     }

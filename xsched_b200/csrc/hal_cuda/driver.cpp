@@ -65,7 +65,14 @@ const DriverApi &Driver() {
         // Last resort: let the dynamic loader search by name (finds the driver in non-standard
         // locations listed in ld.so.conf / LD_LIBRARY_PATH; the marker check below rejects the shim).
         if (path.empty()) path = "libcuda.so.1";
-        void *h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL | RTLD_DEEPBIND);
+        // RTLD_DEEPBIND: the driver's own cross-calls must bind to itself, not to the interposer's exports of
+        // the same names.  Sanitizer runtimes refuse that flag; sanitizer builds define XSCHED_NO_DEEPBIND.
+#ifdef XSCHED_NO_DEEPBIND
+        const int deep = 0;
+#else
+        const int deep = RTLD_DEEPBIND;
+#endif
+        void *h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL | deep);
         if (!h) XERRO("cannot open the CUDA driver (%s): %s; set %s to the path of the real libcuda.so.1", path.c_str(), dlerror(), XSCHED_CUDA_LIB_ENV_NAME);
         if (dlsym(h, kShimMarker)) XERRO("%s is the XSched interposer, not the CUDA driver; set %s", path.c_str(), XSCHED_CUDA_LIB_ENV_NAME);
         api.handle = h;

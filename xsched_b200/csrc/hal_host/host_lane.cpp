@@ -55,7 +55,7 @@ public:
     std::atomic<int64_t> launch_ns_{0}, start_ns_{0}, finish_ns_{0};
 private:
     std::atomic<int32_t> stage_{kNew};
-    bool waitable_ = false;
+    std::atomic<bool> waitable_{false};
 };
 
 class Lane {
