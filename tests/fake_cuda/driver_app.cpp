@@ -86,9 +86,45 @@ int main(int argc, char **argv) {
             if (cuStreamQuery(s[0]) != CUDA_SUCCESS || cuEventQuery(ev) != CUDA_SUCCESS) { std::printf("FAIL queries after synchronize\n"); return 1; }
         }
     }
+    // A blocking stream and the legacy default stream: work on the NULL stream is ordered after everything
+    // submitted to the blocking stream before it.
+    {
+        CUstream sb; CK(cuStreamCreate(&sb, CU_STREAM_DEFAULT));
+        CUdeviceptr x, y, z;
+        CK(cuMemAlloc(&x, n * 4)); CK(cuMemAlloc(&y, n * 4)); CK(cuMemAlloc(&z, n * 4));
+        for (int r = 0; r < 5; ++r) {
+            CK(cuMemsetD32Async(x, (unsigned)(r + 1), n, sb));
+            CK(cuMemsetD32Async(y, 10, n, sb));
+            int count = n;
+            void *a1[] = {&z, &x, &y, &count};
+            CK(cuLaunchKernel(f_add, 4, 1, 1, 64, 1, 1, 0, sb, a1, nullptr));             // z = r + 11 on the blocking stream
+            int k2 = 2;
+            void *a2[] = {&z, &k2, &count};
+            CK(cuLaunchKernel(f_scale, 4, 1, 1, 64, 1, 1, 0, nullptr, a2, nullptr));        // z *= 2 on the legacy stream
+            CK(cuMemcpyDtoHAsync(hc0.data(), z, n * 4, nullptr));
+            if (hc0[0] != 2 * (r + 11) || hc0[n - 1] != 2 * (r + 11)) { std::printf("FAIL legacy-stream order, round %d: %d\n", r, hc0[0]); return 1; }
+            checksum = checksum * 31 + (unsigned)hc0[0];
+        }
+        CK(cuStreamSynchronize(sb));
+        CK(cuMemFree(x)); CK(cuMemFree(y)); CK(cuMemFree(z)); CK(cuStreamDestroy(sb));
+    }
+    // An event is destroyed while its record is still queued; a stream is destroyed with work pending.
+    {
+        CUstream st; CK(cuStreamCreate(&st, CU_STREAM_NON_BLOCKING));
+        CUdeviceptr w; CK(cuMemAlloc(&w, n * 4));
+        CUevent e2; CK(cuEventCreate(&e2, CU_EVENT_DISABLE_TIMING));
+        for (int i = 0; i < 20; ++i) CK(cuMemsetD32Async(w, (unsigned)i, n, st));
+        CK(cuEventRecord(e2, st));
+        CK(cuEventDestroy(e2));
+        CK(cuLaunchHostFunc(st, HostFn, nullptr));
+        CK(cuStreamDestroy(st));                       // implies completion of what was submitted
+        CK(cuMemcpyDtoHAsync(hc1.data(), w, 4, s[0]));
+        if (hc1[0] != 19) { std::printf("FAIL work pending at stream destruction was lost: %d\n", hc1[0]); return 1; }
+        CK(cuMemFree(w));
+    }
     CK(cuEventSynchronize(ev));
     CK(cuCtxSynchronize());
-    if (g_host_calls.load() != rounds) { std::printf("FAIL host function ran %d times\n", g_host_calls.load()); return 1; }
+    if (g_host_calls.load() != rounds + 1) { std::printf("FAIL host function ran %d times\n", g_host_calls.load()); return 1; }
     for (int k = 0; k < 2; ++k) { CK(cuMemFree(da[k])); CK(cuMemFree(db[k])); CK(cuMemFree(dc[k])); CK(cuStreamDestroy(s[k])); }
     CK(cuEventDestroy(ev));
     std::printf("OK %llx\n", checksum);

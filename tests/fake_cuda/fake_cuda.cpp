@@ -111,9 +111,19 @@ int TypeOf(const void *p) {
     return ((const char *)p < base + it->second.first) ? it->second.second : 0;
 }
 
+// Legacy-default-stream rule, simplified to the strict side: work for the legacy stream is accepted only after
+// everything already given to blocking streams (created without CU_STREAM_NON_BLOCKING) has finished, and work
+// for a blocking stream only after the legacy stream has drained.
 Stream *Of(CUstream s) {
-    if (s == nullptr || s == CU_STREAM_LEGACY || s == CU_STREAM_PER_THREAD) return &S().legacy;
-    return (Stream *)s;
+    if (s == nullptr || s == CU_STREAM_LEGACY || s == CU_STREAM_PER_THREAD) {
+        std::vector<Stream *> blocking;
+        { std::lock_guard<std::mutex> lk(S().mu); for (Stream *x : S().streams) if (!(x->flags & CU_STREAM_NON_BLOCKING)) blocking.push_back(x); }
+        for (Stream *x : blocking) x->Drain();
+        return &S().legacy;
+    }
+    Stream *st = (Stream *)s;
+    if (!(st->flags & CU_STREAM_NON_BLOCKING)) S().legacy.Drain();
+    return st;
 }
 
 CUresult CopyAsync(void *dst, const void *src, size_t n, CUstream s) {
@@ -233,10 +243,14 @@ API cuStreamWriteValue64(CUstream s, CUdeviceptr addr, cuuint64_t v, unsigned) {
 API cuLaunchHostFunc(CUstream s, CUhostFn fn, void *data) { Of(s)->Push([=] { fn(data); }); return CUDA_SUCCESS; }
 
 // ---- events ----
-API cuEventCreate(CUevent *e, unsigned) { *e = (CUevent) new Event(); return CUDA_SUCCESS; }
-API cuEventDestroy(CUevent e) { delete (Event *)e; return CUDA_SUCCESS; }
+// A CUevent is a heap-allocated shared_ptr: queued work keeps the event alive after cuEventDestroy, as the
+// real driver does for an event destroyed while a record or a wait on it is pending.
+using EventRef = std::shared_ptr<Event>;
+static EventRef Ev(CUevent e) { return *(EventRef *)e; }
+API cuEventCreate(CUevent *e, unsigned) { *e = (CUevent) new EventRef(std::make_shared<Event>()); return CUDA_SUCCESS; }
+API cuEventDestroy(CUevent e) { delete (EventRef *)e; return CUDA_SUCCESS; }
 static CUresult Record(CUevent e, CUstream s) {
-    Event *ev = (Event *)e;
+    EventRef ev = Ev(e);
     uint64_t seq;
     { std::lock_guard<std::mutex> lk(ev->mu); seq = ++ev->recorded; }
     Of(s)->Push([=] {
@@ -248,19 +262,19 @@ static CUresult Record(CUevent e, CUstream s) {
 API cuEventRecord(CUevent e, CUstream s) { return Record(e, s); }
 API cuEventRecordWithFlags(CUevent e, CUstream s, unsigned) { return Record(e, s); }
 API cuEventQuery(CUevent e) {
-    Event *ev = (Event *)e;
+    EventRef ev = Ev(e);
     std::lock_guard<std::mutex> lk(ev->mu);
     return ev->completed >= ev->recorded ? CUDA_SUCCESS : CUDA_ERROR_NOT_READY;
 }
 API cuEventSynchronize(CUevent e) {
-    Event *ev = (Event *)e;
+    EventRef ev = Ev(e);
     std::unique_lock<std::mutex> lk(ev->mu);
     const uint64_t target = ev->recorded;
     ev->cv.wait(lk, [&] { return ev->completed >= target; });
     return CUDA_SUCCESS;
 }
 API cuStreamWaitEvent(CUstream s, CUevent e, unsigned) {
-    Event *ev = (Event *)e;
+    EventRef ev = Ev(e);
     uint64_t target;
     { std::lock_guard<std::mutex> lk(ev->mu); target = ev->recorded; }
     Of(s)->Push([=] {

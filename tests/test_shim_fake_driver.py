@@ -59,11 +59,13 @@ def test_driver_program_under_the_interposer_without_a_gpu(tmp_path, level, thre
     assert r.returncode == 0, r.stdout + r.stderr[-3000:]
     assert r.stdout == plain.stdout
     st = json.loads(stats.read_text())
-    assert st["streams_with_xqueue"] == 2
-    assert st["launches_queued"] == 30 * 3 and st["launches_direct"] == 0 and st["launches_blocking"] == 0
-    assert st["copies_queued"] == 30 * 6 and st["copies_direct"] == 0
-    assert st["copies_waited"] == 30 * 2             # the two copies into pageable memory per round
-    assert st["events_queued"] == 30
+    assert st["streams_with_xqueue"] == 4            # two worker streams, the blocking stream, the short-lived one
+    # 3 launches per round + 5 on the blocking stream go through XQueues; the 5 on the legacy stream go straight
+    # to the driver after the blocking streams' XQueues were drained
+    assert st["launches_queued"] == 30 * 3 + 5 and st["launches_direct"] == 5 and st["launches_blocking"] == 0
+    assert st["copies_queued"] == 30 * 6 + 1 and st["copies_direct"] == 5
+    assert st["copies_waited"] == 30 * 2 + 1         # every copy into pageable memory on an XQueue stream
+    assert st["events_queued"] == 30 + 1
 
 
 def test_xsched_aware_program_on_the_cuda_hal_without_a_gpu(tmp_path):
