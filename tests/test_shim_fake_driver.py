@@ -124,3 +124,54 @@ def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
         text = r.stdout + r.stderr
         assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
         assert r.returncode == 0 and r.stdout.startswith("OK "), text[-2000:]
+
+
+@pytest.mark.parametrize("spin", ["OFF", "ON"])
+def test_transparent_two_process_scheduling_without_a_gpu(tmp_path, spin):
+    """Two XSched-unaware processes under the interposer, one xserver (HPF), priorities 0 and 1 from the
+    environment — the reference's transparent mode, end to end on the fake driver: while the high-priority
+    process has a request in flight the low-priority process's stream must stand still (at level 1: after the
+    at most `threshold` kernels already handed to the driver have drained)."""
+    import signal
+    import time
+    loop_app = FAKE_DIR / "loop_app"
+    assert loop_app.exists(), "tests/fake_cuda/loop_app not built (python -m xsched_b200.build)"
+    ns = f"fk{os.getpid()}{spin}."
+    libdir = as_libcuda(tmp_path, LIB / "libshimcuda.so")
+    base = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+    base.update(FAKE_CUDA_LIB=str(FAKE), XSCHED_CUDA_LIB=str(FAKE), LD_LIBRARY_PATH=f"{libdir}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""),
+                XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns, XSCHED_IPC_SPIN=spin, XSCHED_SCHEDULER="GLB", XSCHED_AUTO_XQUEUE="ON",
+                XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_THRESHOLD="4", XSCHED_AUTO_XQUEUE_BATCH_SIZE="2")
+    srv_env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+    srv_env.update(XSCHED_IPC_NAMESPACE=ns, XSCHED_IPC_SPIN=spin, XLOG_LEVEL="WARN")
+    server = subprocess.Popen([str(LIB / "xserver"), "HPF", "50000"], stdout=subprocess.PIPE, text=True, env=srv_env)
+    lp = None
+    try:
+        assert "ready" in server.stdout.readline()
+        lp_log, hp_log = tmp_path / "lp.log", tmp_path / "hp.log"
+        lp = subprocess.Popen([str(loop_app), "--role", "lp", "--log", str(lp_log)], stdout=subprocess.PIPE, text=True,
+                              env=dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="0"))
+        assert lp.stdout.readline().startswith("READY")
+        time.sleep(0.1)
+        hp = subprocess.run([str(loop_app), "--role", "hp", "--count", "6", "--log", str(hp_log)], capture_output=True, text=True, timeout=120,
+                            env=dict(base, XSCHED_AUTO_XQUEUE_PRIORITY="1"))
+        assert hp.returncode == 0 and "DONE" in hp.stdout, hp.stdout + hp.stderr[-2000:]
+        time.sleep(0.1)
+    finally:
+        if lp is not None:
+            lp.send_signal(signal.SIGTERM)
+            lp.communicate(timeout=60)
+        server.send_signal(signal.SIGTERM)
+        server.wait(timeout=10)
+    starts = [int(x) for x in lp_log.read_text().split()]
+    requests = [tuple(map(int, line.split())) for line in hp_log.read_text().splitlines()]
+    assert len(requests) == 6 and len(starts) > 100
+    for t0, t1 in requests:
+        assert t1 - t0 >= 10 * 300
+        # grace: the ready event has to reach the server and the suspend the other process, then up to four
+        # kernels of 300 us that were already with the driver finish
+        inside = [t for t in starts if t0 + 4 * 300 + 2500 < t < t1 - 200]
+        assert not inside, f"low-priority kernels started {len(inside)} times inside a high-priority request of {t1 - t0} us"
+    # and it does run between the requests
+    gaps = [(requests[i][1], requests[i + 1][0]) for i in range(len(requests) - 1)]
+    assert all(sum(1 for t in starts if a + 3000 < t < b) > 10 for a, b in gaps)

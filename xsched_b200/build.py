@@ -222,6 +222,9 @@ def build_fake_driver(force: bool = False, verbose: bool = False) -> Path | None
         os.symlink("../libcuda_fake.so", link / "libcuda.so")
     if force or _stale(app, [app_src, lib]):
         _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", "-o", app, app_src, f"-L{link}", "-lcuda", "-ldl", "-pthread"], verbose)
+    loop_src, loop_app = d / "loop_app.cpp", d / "loop_app"
+    if loop_src.exists() and (force or _stale(loop_app, [loop_src, lib])):
+        _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", "-o", loop_app, loop_src, f"-L{link}", "-lcuda", "-ldl", "-pthread"], verbose)
     hal_src, hal_app = d / "hal_app.cpp", d / "hal_app"
     if hal_src.exists() and (LIB / "libhalcuda.so").exists() and (force or _stale(hal_app, [hal_src, lib, LIB / "libhalcuda.so", LIB / "libpreempt.so"])):
         _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", f"-I{INC}", "-o", hal_app, hal_src, f"-L{link}", f"-L{LIB}",
