@@ -1,6 +1,6 @@
 // loop_app — TEST INFRASTRUCTURE: an XSched-unaware driver-API program for multi-process tests on the fake
 // driver.  --role lp: one stream, back-to-back 300 us "kernels" until SIGTERM; every kernel appends its start
-// time (microseconds since the epoch) to --log.  --role hp: `count` requests, each a burst of 10 such kernels
+// time (microseconds since the epoch) to --log.  --role hp: `count` requests, each a burst of 40 such kernels
 // followed by cuStreamSynchronize; request intervals go to --log.  Prints READY when warmed up.
 #include <cuda.h>
 
@@ -25,7 +25,8 @@ static void Busy(void **p, unsigned, unsigned) {
     const int us = *(int *)p[0];
     const int64_t t0 = EpochUs();
     { std::lock_guard<std::mutex> lk(g_mu); g_starts.push_back(t0); }
-    while (EpochUs() - t0 < us) {}
+    // sleeps rather than spins: several of these programs plus a polling server share a small test host
+    std::this_thread::sleep_for(std::chrono::microseconds(us));
 }
 static std::atomic<bool> g_stop{false};
 static void OnTerm(int) { g_stop.store(true); }
@@ -70,7 +71,7 @@ int main(int argc, char **argv) {
         for (int r = 0; r < count; ++r) {
             std::this_thread::sleep_for(std::chrono::milliseconds(25));
             const int64_t t0 = EpochUs();
-            for (int k = 0; k < 10; ++k) CK(cuLaunchKernel(busy, 1, 1, 1, 1, 1, 1, 0, s, args, nullptr));
+            for (int k = 0; k < 40; ++k) CK(cuLaunchKernel(busy, 1, 1, 1, 1, 1, 1, 0, s, args, nullptr));
             CK(cuStreamSynchronize(s));
             if (f) std::fprintf(f, "%lld %lld\n", (long long)t0, (long long)EpochUs());
         }
