@@ -6,7 +6,9 @@
 //   * copies from pageable host memory whose source is overwritten right after the call returns, and copies
 //     into pageable memory whose destination is read right after the call returns;
 //   * launch arguments that live on the caller's stack;
-//   * stream / event queries and synchronisation.
+//   * stream / event queries and synchronisation;
+//   * the legacy default stream against a blocking stream, stream capture and graph launches, destruction of
+//     events and streams with work pending.
 // Prints "OK <checksum>" — the same line with and without the interposer in front of the driver.
 #include <cuda.h>
 
@@ -107,6 +109,37 @@ int main(int argc, char **argv) {
         }
         CK(cuStreamSynchronize(sb));
         CK(cuMemFree(x)); CK(cuMemFree(y)); CK(cuMemFree(z)); CK(cuStreamDestroy(sb));
+    }
+    // Stream capture: three launches recorded into a graph (x -> 2x + 3), the graph launched between ordinary work.
+    {
+        CUdeviceptr v; CK(cuMemAlloc(&v, n * 4));
+        CK(cuMemsetD32Async(v, 1, n, s[0]));                                               // queued before the capture
+        int one_n = n, two = 2;
+        CUdeviceptr ones; CK(cuMemAlloc(&ones, n * 4)); CK(cuMemsetD32Async(ones, 1, n, s[0]));
+        CUgraph graph; CUgraphExec exec;
+        CK(cuStreamBeginCapture(s[0], CU_STREAM_CAPTURE_MODE_THREAD_LOCAL));
+        { void *a[] = {&v, &v, &ones, &one_n}; CK(cuLaunchKernel(f_add, 4, 1, 1, 64, 1, 1, 0, s[0], a, nullptr)); }      // +1
+        // ending a capture on a stream that is not capturing fails and must not end the one in progress
+        CUgraph wrong = nullptr;
+        if (cuStreamEndCapture(s[1], &wrong) == CUDA_SUCCESS) { std::printf("FAIL ending a capture on a stream that is not capturing succeeded\n"); return 1; }
+        { void *a[] = {&v, &two, &one_n}; CK(cuLaunchKernel(f_scale, 4, 1, 1, 64, 1, 1, 0, s[0], a, nullptr)); }         // *2
+        { void *a[] = {&v, &v, &ones, &one_n}; CK(cuLaunchKernel(f_add, 4, 1, 1, 64, 1, 1, 0, s[0], a, nullptr)); }      // +1
+        CK(cuStreamEndCapture(s[0], &graph));
+        CK(cuGraphInstantiate(&exec, graph, 0));
+        CK(cuMemcpyDtoHAsync(hc0.data(), v, 4, s[0]));
+        if (hc0[0] != 1) { std::printf("FAIL captured work ran during the capture: %d\n", hc0[0]); return 1; }
+        int expect = 1;
+        for (int r = 0; r < 5; ++r) {
+            CK(cuGraphLaunch(exec, s[0]));                                                   // x -> 2(x + 1) + 1
+            { void *a[] = {&v, &v, &ones, &one_n}; CK(cuLaunchKernel(f_add, 4, 1, 1, 64, 1, 1, 0, s[0], a, nullptr)); }  // +1
+            expect = 2 * (expect + 1) + 1 + 1;
+        }
+        CK(cuMemcpyDtoHAsync(hc0.data(), v, n * 4, s[0]));
+        if (hc0[0] != expect || hc0[n - 1] != expect) { std::printf("FAIL graph launches: %d (want %d)\n", hc0[0], expect); return 1; }
+        checksum = checksum * 31 + (unsigned)hc0[0];
+        CK(cuGraphExecDestroy(exec)); CK(cuGraphDestroy(graph));
+        CK(cuStreamSynchronize(s[0]));
+        CK(cuMemFree(v)); CK(cuMemFree(ones));
     }
     // An event is destroyed while its record is still queued; a stream is destroyed with work pending.
     {

@@ -9,7 +9,8 @@
 //   * copies that involve memory the fake does not know ("pageable") are synchronous for the caller, like
 //     the real driver's: a pageable source is read before the call returns, a pageable destination is
 //     written before it returns;
-//   * events, cross-stream waits, host functions, 32/64-bit stream memory writes, memsets.
+//   * events, cross-stream waits, host functions, 32/64-bit stream memory writes, memsets;
+//   * stream capture into a graph (the recorded closures) and graph launches.
 // Only the entry points the HAL loads and the test programs call exist.  Nothing here is shipped.
 #include <cuda.h>
 
@@ -67,8 +68,14 @@ struct Stream {
         cv.notify_all();
         if (th.joinable()) th.join();
     }
+    // While a stream is capturing, work given to it is recorded instead of run.
+    std::shared_ptr<std::vector<std::function<void()>>> capture;
     void Push(std::function<void()> f) {
-        { std::lock_guard<std::mutex> lk(mu); q.push_back(std::move(f)); }
+        {
+            std::lock_guard<std::mutex> lk(mu);
+            if (capture) { capture->push_back(std::move(f)); return; }
+            q.push_back(std::move(f));
+        }
         cv.notify_one();
     }
     void Drain() {
@@ -355,6 +362,43 @@ API cuLaunchKernel(CUfunction f, unsigned gx, unsigned, unsigned, unsigned bx, u
     return Launch(f, gx, bx, s, params);
 }
 API cuLaunchKernelEx(const CUlaunchConfig *c, CUfunction f, void **params, void **) { return Launch(f, c->gridDimX, c->blockDimX, c->hStream, params); }
+
+// ---- stream capture and graphs: a graph is the list of closures recorded while the stream was capturing ----
+using Recorded = std::vector<std::function<void()>>;
+API cuStreamBeginCapture(CUstream s, CUstreamCaptureMode) {
+    Stream *st = (Stream *)s;
+    std::lock_guard<std::mutex> lk(st->mu);
+    if (st->capture) return CUDA_ERROR_ILLEGAL_STATE;
+    st->capture = std::make_shared<Recorded>();
+    return CUDA_SUCCESS;
+}
+API cuStreamIsCapturing(CUstream s, CUstreamCaptureStatus *status) {
+    Stream *st = (s == nullptr || s == CU_STREAM_LEGACY || s == CU_STREAM_PER_THREAD) ? &S().legacy : (Stream *)s;
+    std::lock_guard<std::mutex> lk(st->mu);
+    *status = st->capture ? CU_STREAM_CAPTURE_STATUS_ACTIVE : CU_STREAM_CAPTURE_STATUS_NONE;
+    return CUDA_SUCCESS;
+}
+API cuStreamEndCapture(CUstream s, CUgraph *g) {
+    Stream *st = (Stream *)s;
+    std::lock_guard<std::mutex> lk(st->mu);
+    if (!st->capture) return CUDA_ERROR_STREAM_CAPTURE_UNMATCHED;
+    *g = (CUgraph) new std::shared_ptr<Recorded>(st->capture);
+    st->capture.reset();
+    return CUDA_SUCCESS;
+}
+API cuGraphInstantiate(CUgraphExec *exec, CUgraph g, unsigned long long) {
+    *exec = (CUgraphExec) new std::shared_ptr<Recorded>(*(std::shared_ptr<Recorded> *)g);
+    return CUDA_SUCCESS;
+}
+API cuGraphUpload(CUgraphExec, CUstream) { return CUDA_SUCCESS; }
+API cuGraphLaunch(CUgraphExec exec, CUstream s) {
+    std::shared_ptr<Recorded> rec = *(std::shared_ptr<Recorded> *)exec;
+    Stream *st = Of(s);
+    for (const auto &f : *rec) st->Push(f);
+    return CUDA_SUCCESS;
+}
+API cuGraphExecDestroy(CUgraphExec exec) { delete (std::shared_ptr<Recorded> *)exec; return CUDA_SUCCESS; }
+API cuGraphDestroy(CUgraph g) { delete (std::shared_ptr<Recorded> *)g; return CUDA_SUCCESS; }
 
 // ---- symbol lookup ----
 API cuGetProcAddress(const char *symbol, void **pfn, int, cuuint64_t, CUdriverProcAddressQueryResult *status) {

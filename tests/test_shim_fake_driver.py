@@ -60,11 +60,13 @@ def test_driver_program_under_the_interposer_without_a_gpu(tmp_path, level, thre
     assert r.stdout == plain.stdout
     st = json.loads(stats.read_text())
     assert st["streams_with_xqueue"] == 4            # two worker streams, the blocking stream, the short-lived one
-    # 3 launches per round + 5 on the blocking stream go through XQueues; the 5 on the legacy stream go straight
-    # to the driver after the blocking streams' XQueues were drained
-    assert st["launches_queued"] == 30 * 3 + 5 and st["launches_direct"] == 5 and st["launches_blocking"] == 0
-    assert st["copies_queued"] == 30 * 6 + 1 and st["copies_direct"] == 5
-    assert st["copies_waited"] == 30 * 2 + 1         # every copy into pageable memory on an XQueue stream
+    # 3 launches per round + 5 on the blocking stream + 5 between the graph launches go through XQueues; the 5 on
+    # the legacy stream go straight to the driver after the blocking streams' XQueues were drained, and so do the
+    # 3 launches recorded while a stream was capturing (a failed cuStreamEndCapture in between must not end the bypass)
+    assert st["launches_queued"] == 30 * 3 + 5 + 5 and st["launches_direct"] == 5 + 3 and st["launches_blocking"] == 0
+    assert st["graphs_queued"] == 5 and st["calls_queued"] == 5
+    assert st["copies_queued"] == 30 * 6 + 3 and st["copies_direct"] == 5
+    assert st["copies_waited"] == 30 * 2 + 3         # every copy into pageable memory on an XQueue stream
     assert st["events_queued"] == 30 + 1
 
 

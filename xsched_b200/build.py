@@ -84,7 +84,7 @@ SHIM_HANDLED = {
     "cuGetProcAddress_v2", "cuLaunchKernelEx", "cuLaunchCooperativeKernel", "cuMemAllocAsync", "cuMemFreeAsync", "cuMemcpy2DAsync_v2",
     "cuMemcpyPeerAsync", "cuMemsetD16Async", "cuGraphLaunch", "cuStreamAddCallback", "cuMemcpy", "cuMemcpyDtoH_v2", "cuMemcpyHtoD_v2",
     "cuMemcpyDtoD_v2", "cuMemcpy3DAsync_v2", "cuMemsetD2D8Async", "cuMemsetD2D16Async", "cuMemsetD2D32Async", "cuGraphUpload",
-    "cuEventRecordWithFlags",
+    "cuEventRecordWithFlags", "cuStreamBeginCaptureToGraph",
 }
 
 

@@ -424,19 +424,52 @@ SHIM_API CUresult CUDAAPI cuStreamDestroy(CUstream s) {
     return Driver().cuStreamDestroy(s);
 }
 
+// Stream capture.  While any stream is being captured every entry point bypasses the XQueues (Route() returns
+// nullptr): a command launched later by a worker thread would be recorded into the graph, and the completion
+// write behind it would be as well.  Before the first capture starts, everything queued so far is drained, so
+// that nothing submitted earlier runs inside the capture and direct launches cannot overtake queued ones.
+// (The reference keeps the same counter, platforms/cuda/shim/src/shim.cpp:61-119.)
+static std::mutex g_capture_mu;
+static void CaptureBegins() {
+    std::lock_guard<std::mutex> lk(g_capture_mu);
+    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();
+    g_capturing.fetch_add(1);
+}
+static void CaptureEnded() {
+    std::lock_guard<std::mutex> lk(g_capture_mu);
+    if (g_capturing.load() > 0) g_capturing.fetch_sub(1);
+}
+
 SHIM_API CUresult CUDAAPI cuStreamBeginCapture(CUstream s, CUstreamCaptureMode mode) {
     REAL(cuStreamBeginCapture, "cuStreamBeginCapture_v2");
-    if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();     // nothing queued may leak into the graph
-    g_capturing.fetch_add(1);
+    CaptureBegins();
     const CUresult r = real(s, mode);
-    if (r != CUDA_SUCCESS) g_capturing.fetch_sub(1);
+    if (r != CUDA_SUCCESS) CaptureEnded();
     return r;
 }
 
+SHIM_API CUresult CUDAAPI cuStreamBeginCaptureToGraph(CUstream s, CUgraph g, const CUgraphNode *deps, const CUgraphEdgeData *dep_data, size_t n_deps,
+                                                      CUstreamCaptureMode mode) {
+    REAL(cuStreamBeginCaptureToGraph, "cuStreamBeginCaptureToGraph");
+    CaptureBegins();
+    const CUresult r = real(s, g, deps, dep_data, n_deps, mode);
+    if (r != CUDA_SUCCESS) CaptureEnded();
+    return r;
+}
+
+// The counter goes down only when this call really ended a capture: ending on the wrong stream, or on one that
+// was not capturing, leaves the capture (and the bypass) in place.
 SHIM_API CUresult CUDAAPI cuStreamEndCapture(CUstream s, CUgraph *g) {
     REAL(cuStreamEndCapture, "cuStreamEndCapture");
+    using IsCapturingFn = CUresult (*)(CUstream, CUstreamCaptureStatus *);
+    static const IsCapturingFn is_capturing = (IsCapturingFn)Driver().Sym("cuStreamIsCapturing");
+    CUstreamCaptureStatus before = CU_STREAM_CAPTURE_STATUS_NONE, after = CU_STREAM_CAPTURE_STATUS_NONE;
+    const bool known = is_capturing && is_capturing(s, &before) == CUDA_SUCCESS;
     const CUresult r = real(s, g);
-    if (g_capturing.load() > 0) g_capturing.fetch_sub(1);
+    if (!known) { if (r == CUDA_SUCCESS) CaptureEnded(); return r; }
+    if (before != CU_STREAM_CAPTURE_STATUS_NONE && r != CUDA_ERROR_STREAM_CAPTURE_UNMATCHED &&
+        is_capturing(s, &after) == CUDA_SUCCESS && after == CU_STREAM_CAPTURE_STATUS_NONE)
+        CaptureEnded();
     return r;
 }
 
@@ -483,6 +516,7 @@ static const Hook kHooks[] = {
     {"cuStreamCreateWithPriority", (void *)&cuStreamCreateWithPriority, 5050},
     {"cuStreamDestroy", (void *)&cuStreamDestroy, 4000},
     {"cuStreamBeginCapture", (void *)&cuStreamBeginCapture, 10010},
+    {"cuStreamBeginCaptureToGraph", (void *)&cuStreamBeginCaptureToGraph, 12030},
     {"cuStreamEndCapture", (void *)&cuStreamEndCapture, 10000},
 };
 
