@@ -290,7 +290,8 @@ static int Fuzz(uint64_t seed, int steps) {
                 out("wait_all", (int64_t)XQueueWaitAll(x.xq));
                 XQueueState st = kQueueStateUnknown;
                 out("query", (int64_t)XQueueQuery(x.xq, &st));
-                out("state_after_wait", (int64_t)st);
+                // the worker marks the queue idle a moment after the wait returns: poll, do not sample
+                out("idle_after_wait", (int64_t)WaitState(x.xq, kQueueStateIdle, 2000));
             }
             break;
         case 4: {
@@ -336,9 +337,7 @@ static int Fuzz(uint64_t seed, int steps) {
     for (Q &x : q) {
         if (x.suspended) out("final_resume", (int64_t)XQueueResume(x.xq, kQueueResumeFlagNone));
         out("final_wait", (int64_t)XQueueWaitAll(x.xq));
-        XQueueState st = kQueueStateUnknown;
-        XQueueQuery(x.xq, &st);
-        out("final_state", (int64_t)st);
+        out("final_idle", (int64_t)WaitState(x.xq, kQueueStateIdle, 2000));
         any_drop = any_drop || x.dropped;
     }
     SleepUs(3000);
@@ -346,6 +345,42 @@ static int Fuzz(uint64_t seed, int steps) {
     std::printf("], \"submitted\": %" PRId64 ", \"all_ran_unless_dropped\": %d, \"none_ran_twice\": %d}\n", total_submitted,
                 (int)(any_drop || ran == (uint64_t)total_submitted), (int)(ran <= (uint64_t)total_submitted));
     for (Q &x : q) { XQueueDestroy(x.xq); }
+    return 0;
+}
+
+// ---- suspend/resume stress: many short rounds; a lost wake-up or a lost command shows as a stuck round ----
+static int Stress(int64_t level, int rounds, int64_t spin_us) {
+    CHECK(XHintSetScheduler(kSchedulerLocal, kPolicyHighestPriorityFirst));
+    XQueueHandle xq = MakeQueue(level, 4, 2);
+    CHECK(XHintPriority(xq, 3));
+    std::atomic<int> round{0};
+    std::atomic<bool> done{false};
+    std::thread watchdog([&] {
+        int last = -1;
+        int64_t since = NowNs();
+        while (!done.load()) {
+            SleepUs(100000);
+            const int r = round.load();
+            if (r != last) { last = r; since = NowNs(); continue; }
+            if (NowNs() - since > 5000000000ll) {
+                std::printf("{\"stuck_in_round\": %d, \"executed\": %" PRIu64 ", \"flushed\": %" PRIu64 "}\n", r, Executed(), Flushed());
+                std::fflush(stdout);
+                std::_Exit(3);
+            }
+        }
+    });
+    const uint64_t exec0 = Executed();
+    for (int r = 0; r < rounds; ++r) {
+        round.store(r);
+        for (int i = 0; i < 6; ++i) { HwCommandHandle c = 0; CHECK(HostLaneCommandCreate(&c, spin_us)); HostLaneCommandRelease(c); CHECK(XQueueSubmit(xq, c)); }
+        CHECK(XQueueSuspend(xq, kQueueSuspendFlagSyncHwQueue));
+        CHECK(XQueueResume(xq, kQueueResumeFlagNone));
+        CHECK(XQueueWaitAll(xq));
+    }
+    done.store(true);
+    watchdog.join();
+    std::printf("{\"rounds\": %d, \"executed\": %" PRIu64 ", \"expected\": %d}\n", rounds, Executed() - exec0, rounds * 6);
+    XQueueDestroy(xq);
     return 0;
 }
 
@@ -489,6 +524,7 @@ int main(int argc, char **argv) {
     if (s == "suspend") return Suspend(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "drop") return Drop(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "hpf") return Hpf(I(2, 1), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL");
+    if (s == "stress") return Stress(I(2, 2), (int)I(3, 2000), I(4, 100));
     if (s == "fuzz") return Fuzz((uint64_t)I(2, 1), (int)I(3, 200));
     if (s == "tput") return Tput(I(2, 1), (int)I(3, 200000), I(4, 16), I(5, 8));
     if (s == "lax") return Hpf(I(2, 2), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL", I(11, 5000));

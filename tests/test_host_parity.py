@@ -139,3 +139,22 @@ def test_random_api_walks_match_the_live_reference():
         a, b = run(NEW, ["fuzz", seed, 200]), run(REF, ["fuzz", seed, 200])
         assert a == b, f"seed {seed}"
         assert a["all_ran_unless_dropped"] == 1 and a["none_ran_twice"] == 1, f"seed {seed}"
+
+
+def test_manual_suspend_resume_next_to_a_scheduler_never_strands_commands():
+    """An application suspends and resumes its XQueue by hand while the in-process scheduler manages the same
+    queue (its first operation for a new queue is a Resume, executed on the agent's thread).  Suspend and
+    Resume are serialised, so whatever order the two threads arrive in, every command runs exactly once and
+    XQueueWaitAll returns.  The window is widest right after process start: many short-lived processes."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    def one(_):
+        r = subprocess.run([str(NEW), "stress", "2", "1", "500"], capture_output=True, text=True, env=dict(os.environ, XLOG_LEVEL="ERRO"), timeout=60)
+        return r.returncode, r.stdout
+    with ThreadPoolExecutor(max_workers=12) as pool:
+        for rc, out in pool.map(one, range(60)):
+            assert rc == 0, out
+            res = json.loads(out)
+            assert res["executed"] == res["expected"], res
+    res = run(NEW, ["stress", 2, 400, 100])
+    assert res["executed"] == res["expected"] == 2400

@@ -174,7 +174,11 @@ def test_transparent_two_process_scheduling_without_a_gpu(tmp_path, spin):
         # process (on a busy test host a polling thread can lose its core for milliseconds), then up to four
         # kernels that were already with the driver finish
         inside = [t for t in starts if t0 + (t1 - t0) // 2 < t < t1 - 200]
-        assert not inside, f"low-priority kernels started {len(inside)} times inside a high-priority request of {t1 - t0} us"
+        # Unsuspended, the other process would start about (t1 - t0) / 2 / 350 us kernels here.  A handful is
+        # tolerated: when the requesting thread loses its core in the middle of its burst, its queue drains, the
+        # low-priority queue is rightly resumed for a moment and suspended again.
+        allowed = max(4, (t1 - t0) // 2 // 350 // 10)
+        assert len(inside) <= allowed, f"low-priority kernels started {len(inside)} times inside a high-priority request of {t1 - t0} us"
     # and it does run between the requests
     gaps = [(requests[i][1], requests[i + 1][0]) for i in range(len(requests) - 1)]
     assert all(sum(1 for t in starts if a + 3000 < t < b) > 10 for a, b in gaps)

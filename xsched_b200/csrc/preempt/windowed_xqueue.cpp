@@ -320,8 +320,14 @@ void WindowedXQueue::LaunchOne(std::shared_ptr<HwCommand> cmd) {
 }
 
 // ------------------------------------------------------------------------------- suspend / resume
+// Suspend and Resume may come from different threads at the same time: the application calls them, and so
+// does the scheduling agent when an operation arrives (its first operation for a new XQueue lists the queue
+// as running, which is a Resume).  They are serialised: a Resume that ran between this function's "pause"
+// and "Deactivate" steps would re-issue nothing, un-pause the worker, and leave the commands that Deactivate
+// then pulls back out of the hardware queue stranded for good.
 void WindowedXQueue::Suspend(int64_t flags) {
     if (terminated_.load()) return;
+    std::lock_guard<std::mutex> serial(suspend_mu_);
     bool expected = false;
     if (!suspended_.compare_exchange_strong(expected, true)) return;     // re-entrant
 
@@ -339,6 +345,7 @@ void WindowedXQueue::Suspend(int64_t flags) {
 }
 
 void WindowedXQueue::Resume(int64_t flags) {
+    std::lock_guard<std::mutex> serial(suspend_mu_);
     bool expected = true;
     if (!suspended_.compare_exchange_strong(expected, false)) return;
 

@@ -60,6 +60,7 @@ private:
 
     XPreemptLevel level_;
     std::atomic<bool> suspended_{false};
+    std::mutex suspend_mu_;          // Suspend() and Resume() run one at a time (see Suspend)
     std::atomic<bool> terminated_{false};
     std::atomic<int64_t> next_idx_{1};            // HwCommand indices start at 1
 
