@@ -384,6 +384,62 @@ static int Stress(int64_t level, int rounds, int64_t spin_us) {
     return 0;
 }
 
+// ---- concurrent callers: one thread submits and waits, one suspends and resumes, one queries and hints ----
+// Nothing is dropped, so every command must run exactly once and the submitter's waits must all return.
+static int MtFuzz(uint64_t seed, int64_t level, int bursts) {
+    CHECK(XHintSetScheduler(kSchedulerLocal, kPolicyHighestPriorityFirst));
+    XQueueHandle xq = MakeQueue(level, 4, 2);
+    std::atomic<bool> done{false};
+    std::atomic<int> progress{0};
+    const uint64_t exec0 = Executed();
+    int64_t submitted = 0;
+    std::thread submitter([&] {
+        std::mt19937_64 rng(seed);
+        for (int b = 0; b < bursts; ++b) {
+            const int n = 1 + (int)(rng() % 8);
+            for (int i = 0; i < n; ++i) { HwCommandHandle c = 0; CHECK(HostLaneCommandCreate(&c, 20 + (int64_t)(rng() % 120))); HostLaneCommandRelease(c); CHECK(XQueueSubmit(xq, c)); ++submitted; }
+            if (rng() % 2) CHECK(XQueueWaitAll(xq));
+            progress.fetch_add(1);
+        }
+        CHECK(XQueueWaitAll(xq));
+        done.store(true);
+    });
+    std::thread suspender([&] {
+        std::mt19937_64 rng(seed * 31 + 7);
+        while (!done.load()) {
+            SleepUs((int64_t)(rng() % 600));
+            CHECK(XQueueSuspend(xq, (rng() % 2) ? kQueueSuspendFlagSyncHwQueue : kQueueSuspendFlagNone));
+            SleepUs((int64_t)(rng() % 300));
+            CHECK(XQueueResume(xq, kQueueResumeFlagNone));
+        }
+    });
+    std::thread prober([&] {
+        std::mt19937_64 rng(seed * 131 + 3);
+        while (!done.load()) {
+            XQueueState st; int64_t cnt;
+            CHECK(XQueueQuery(xq, &st));
+            CHECK(XQueueProfileHwCommandCount(xq, &cnt));
+            CHECK(XHintPriority(xq, (Priority)(rng() % 5)));
+            SleepUs((int64_t)(rng() % 200));
+        }
+    });
+    std::thread watchdog([&] {
+        int last = -1;
+        int64_t since = NowNs();
+        while (!done.load()) {
+            SleepUs(100000);
+            const int p = progress.load();
+            if (p != last) { last = p; since = NowNs(); continue; }
+            if (NowNs() - since > 8000000000ll) { std::printf("{\"stuck_at_burst\": %d}\n", p); std::fflush(stdout); std::_Exit(3); }
+        }
+    });
+    submitter.join(); suspender.join(); prober.join(); watchdog.join();
+    SleepUs(2000);
+    std::printf("{\"submitted\": %" PRId64 ", \"executed\": %" PRIu64 "}\n", submitted, Executed() - exec0);
+    XQueueDestroy(xq);
+    return 0;
+}
+
 // ---- host-path cost: zero-length commands through one XQueue --------------------------------------
 // Submit rate of the application thread and end-to-end rate (submit .. last command retired) with the
 // window doing its work (every batch-th command is waited for).  Round trips: submit -> WaitAll of a
@@ -524,6 +580,7 @@ int main(int argc, char **argv) {
     if (s == "suspend") return Suspend(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "drop") return Drop(I(2, 1), (int)I(3, 40), I(4, 500));
     if (s == "hpf") return Hpf(I(2, 1), (int)I(3, 400), I(4, 1000), (int)I(5, 10), I(6, 2000), I(7, 30000), I(8, 16), I(9, 8), argc > 10 ? argv[10] : "LCL");
+    if (s == "mtfuzz") return MtFuzz((uint64_t)I(2, 1), I(3, 2), (int)I(4, 300));
     if (s == "stress") return Stress(I(2, 2), (int)I(3, 2000), I(4, 100));
     if (s == "fuzz") return Fuzz((uint64_t)I(2, 1), (int)I(3, 200));
     if (s == "tput") return Tput(I(2, 1), (int)I(3, 200000), I(4, 16), I(5, 8));
