@@ -128,22 +128,23 @@ def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
         assert r.returncode == 0 and r.stdout.startswith("OK "), text[-2000:]
 
 
-@pytest.mark.parametrize("spin", ["OFF", "ON"])
-def test_transparent_two_process_scheduling_without_a_gpu(tmp_path, spin):
+@pytest.mark.parametrize("spin,level", [("OFF", 1), ("ON", 1), ("OFF", 2)])
+def test_transparent_two_process_scheduling_without_a_gpu(tmp_path, spin, level):
     """Two XSched-unaware processes under the interposer, one xserver (HPF), priorities 0 and 1 from the
     environment — the reference's transparent mode, end to end on the fake driver: while the high-priority
-    process has a request in flight the low-priority process's stream must stand still (at level 1: after the
-    at most `threshold` kernels already handed to the driver have drained)."""
+    process has a request in flight the low-priority process's stream must stand still (after the at most
+    `threshold` kernels already handed to the driver have drained: ordinary kernels cannot be deactivated, so
+    level 2 behaves like level 1 for them, but the queue's Deactivate / Reactivate path runs)."""
     import signal
     import time
     loop_app = FAKE_DIR / "loop_app"
     assert loop_app.exists(), "tests/fake_cuda/loop_app not built (python -m xsched_b200.build)"
-    ns = f"fk{os.getpid()}{spin}."
+    ns = f"fk{os.getpid()}{spin}{level}."
     libdir = as_libcuda(tmp_path, LIB / "libshimcuda.so")
     base = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
     base.update(FAKE_CUDA_LIB=str(FAKE), XSCHED_CUDA_LIB=str(FAKE), LD_LIBRARY_PATH=f"{libdir}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""),
                 XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns, XSCHED_IPC_SPIN=spin, XSCHED_SCHEDULER="GLB", XSCHED_AUTO_XQUEUE="ON",
-                XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_THRESHOLD="4", XSCHED_AUTO_XQUEUE_BATCH_SIZE="2")
+                XSCHED_AUTO_XQUEUE_LEVEL=str(level), XSCHED_AUTO_XQUEUE_THRESHOLD="4", XSCHED_AUTO_XQUEUE_BATCH_SIZE="2")
     srv_env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
     srv_env.update(XSCHED_IPC_NAMESPACE=ns, XSCHED_IPC_SPIN=spin, XLOG_LEVEL="WARN")
     server = subprocess.Popen([str(LIB / "xserver"), "HPF", "50000"], stdout=subprocess.PIPE, text=True, env=srv_env)
