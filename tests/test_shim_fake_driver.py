@@ -84,6 +84,20 @@ def test_xsched_aware_program_on_the_cuda_hal_without_a_gpu(tmp_path):
     assert 300 <= res["hp_min_us"] and res["hp_max_us"] <= 300 + 4000
 
 
+def test_level2_preempt_and_resume_on_the_cuda_hal_without_a_gpu(tmp_path):
+    """Level 2 of the CUDA HAL with fake preemptible tasks (tests/fake_cuda/fake_xpk.cpp stands in for libxpk): the
+    low-priority queue is deactivated for every high-priority request, tasks stop at a tile boundary and are
+    relaunched from their cursor; every tile of every task must have run exactly once."""
+    app = FAKE_DIR / "level2_app"
+    assert app.exists(), "tests/fake_cuda/level2_app not built (python -m xsched_b200.build)"
+    r = run_app(as_libcuda(tmp_path, FAKE), FAKE, app, XSCHED_CUDA_LIB=FAKE)
+    assert r.returncode == 0, r.stdout + r.stderr[-3000:]
+    res = json.loads(r.stdout.strip().splitlines()[-1])
+    assert res["finished"] == res["expected"] and res["bad_tiles"] == 0, res
+    assert res["preemptions"] > 10 and res["relaunches"] >= res["preemptions"] and res["deactivations"] >= 10, res
+    assert res["hp_p50_us"] < 300 + 200 + 2000            # about one tile, never one 8 ms task
+
+
 def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
     """Everything between the program and the fake driver — interposer, CUDA HAL, XQueue runtime, scheduler —
     compiled with -fsanitize=thread (the driver is opened without RTLD_DEEPBIND in such a build)."""
@@ -120,6 +134,15 @@ def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
     text = r.stdout + r.stderr
     assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
     assert r.returncode == 0, text[-2000:]
+    # level 2 with fake preemptible tasks (fake_xpk.cpp instead of libxpk)
+    l2_tsan = tmp_path / "level2_app_tsan"
+    r = subprocess.run(common + ["-std=c++20", f"-I{ROOT / 'include'}", "-o", str(l2_tsan), str(FAKE_DIR / "level2_app.cpp"), str(FAKE_DIR / "fake_xpk.cpp")] +
+                       no_shim + [f"-L{FAKE_DIR / 'link'}", "-lcuda", "-ldl", "-lrt"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    r = run_app(as_libcuda(tmp_path, fake), fake, l2_tsan, XSCHED_CUDA_LIB=fake, TSAN_OPTIONS="halt_on_error=0")
+    text = r.stdout + r.stderr
+    assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
+    assert r.returncode == 0 and '"bad_tiles": 0' in r.stdout, text[-2000:]
     for level in (1, 2):
         r = run_app(as_libcuda(tmp_path, shim), fake, app, XSCHED_CUDA_LIB=fake, XSCHED_AUTO_XQUEUE="ON", XSCHED_POLICY="HPF",
                     XSCHED_AUTO_XQUEUE_LEVEL=level, XSCHED_AUTO_XQUEUE_THRESHOLD=4, XSCHED_AUTO_XQUEUE_BATCH_SIZE=2, TSAN_OPTIONS="halt_on_error=0")
