@@ -65,7 +65,8 @@ CUresult CudaCommand::LaunchOn(CUstream stream, const std::shared_ptr<Completion
     if (want_sync_.load(std::memory_order_acquire)) {
         // A relaunch after a flush takes a fresh ticket: the old write already executed behind the
         // flushed kernel and proves nothing.
-        counter_ = counter;
+        // (assigned once: a relaunch from the scheduler's thread may overlap a waiter reading it)
+        if (counter_ == nullptr) counter_ = counter;
         const uint64_t t = counter->Issue(stream, &r);
         if (t) ticket_.store(t, std::memory_order_release);
     }
@@ -257,13 +258,15 @@ int64_t CudaXpkCommand::ExpectedRemainingUs() const {
         auto it = g_last_duration_us.find(task_);
         if (it != g_last_duration_us.end()) last = it->second;
     }
-    if (last == 0 || launched_at_ns_ == 0) return 0;
-    return std::max<int64_t>(0, last - (SteadyNs() - launched_at_ns_) / 1000);
+    const int64_t at = launched_at_ns_.load(std::memory_order_relaxed);
+    if (last == 0 || at == 0) return 0;
+    return std::max<int64_t>(0, last - (SteadyNs() - at) / 1000);
 }
 
 void CudaXpkCommand::OnWaited() {
-    if (launched_at_ns_ == 0) return;
-    const int64_t us = (SteadyNs() - launched_at_ns_) / 1000;
+    const int64_t at = launched_at_ns_.load(std::memory_order_relaxed);
+    if (at == 0) return;
+    const int64_t us = (SteadyNs() - at) / 1000;
     std::lock_guard<std::mutex> lk(g_dur_mu);
     if (g_last_duration_us.size() > 4096) g_last_duration_us.clear();      // tasks come and go; keep the table small
     g_last_duration_us[task_] = us;
@@ -271,7 +274,7 @@ void CudaXpkCommand::OnWaited() {
 
 CUresult CudaXpkCommand::Enqueue(CUstream stream) {
     xpkTask_t t = (xpkTask_t)task_;
-    launched_at_ns_ = SteadyNs();
+    launched_at_ns_.store(SteadyNs(), std::memory_order_relaxed);
     if (!launched_once_ && rewind_) {
         if (xpkTaskReset(t, stream) != XPK_SUCCESS) return CUDA_ERROR_LAUNCH_FAILED;
     }

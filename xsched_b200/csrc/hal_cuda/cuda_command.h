@@ -202,7 +202,7 @@ private:
     void *task_;
     bool rewind_;
     bool launched_once_ = false;
-    int64_t launched_at_ns_ = 0;
+    std::atomic<int64_t> launched_at_ns_{0};    // written at every (re)launch, read by waiters
 };
 
 } // namespace xsched::cuda
