@@ -98,11 +98,18 @@ def test_level2_preempt_and_resume_on_the_cuda_hal_without_a_gpu(tmp_path):
     assert res["hp_p50_us"] < 300 + 200 + 2000            # about one tile, never one 8 ms task
 
 
-def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
+@pytest.mark.parametrize("sanitizer", ["thread", "address,undefined"])
+def test_interposer_and_hal_are_clean_under_sanitizers(tmp_path, sanitizer):
     """Everything between the program and the fake driver — interposer, CUDA HAL, XQueue runtime, scheduler —
-    compiled with -fsanitize=thread (the driver is opened without RTLD_DEEPBIND in such a build)."""
+    compiled with ThreadSanitizer, then with AddressSanitizer + UBSan (the driver is opened without RTLD_DEEPBIND
+    in such builds; leak checking is off: the process-lifetime singletons are never freed by design)."""
     srcs = [CSRC / "shim" / "shim.cpp"] + [p for d in ("hal_cuda", "preempt", "sched") for p in sorted((CSRC / d).glob("*.cpp"))]
-    common = [CXX, "-O1", "-g", "-fsanitize=thread", "-fPIC", "-pthread", f"-I{ROOT / 'include'}", f"-I{CSRC}", f"-I{CUDA_INC}"]
+    common = [CXX, "-O1", "-g", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer", "-fPIC", "-pthread", f"-I{ROOT / 'include'}", f"-I{CSRC}", f"-I{CUDA_INC}"]
+    san_env = dict(TSAN_OPTIONS="halt_on_error=0", ASAN_OPTIONS="detect_leaks=0")
+    markers = ("WARNING: ThreadSanitizer", "ERROR: AddressSanitizer", "runtime error:")
+
+    def clean(text: str) -> bool:
+        return not any(m in text for m in markers)
 
     def compile_one(src: Path):
         obj = tmp_path / (src.parent.name + "_" + src.stem + ".o")
@@ -117,7 +124,7 @@ def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
     r = subprocess.run(common + ["-shared", "-Wl,-soname,libcuda.so.1", "-o", str(shim)] + objs + [f"-L{LIB}", f"-Wl,-rpath,{LIB}", "-lxpk", "-ldl", "-lrt"],
                        capture_output=True, text=True)
     if r.returncode != 0 and ("cannot find" in r.stderr or "unrecognized" in r.stderr):
-        pytest.skip("toolchain has no ThreadSanitizer runtime")
+        pytest.skip(f"toolchain has no -fsanitize={sanitizer} runtime")
     assert r.returncode == 0, r.stderr[-2000:]
     fake, app = tmp_path / "libcuda_fake_tsan.so", tmp_path / "driver_app_tsan"
     for cmd in (common + ["-std=c++17", "-shared", "-Wl,-soname,libcuda.so.1", "-o", str(fake), str(FAKE_DIR / "fake_cuda.cpp"), "-ldl"],
@@ -130,24 +137,24 @@ def test_interposer_and_hal_are_clean_under_thread_sanitizer(tmp_path):
     r = subprocess.run(common + ["-std=c++17", f"-I{ROOT / 'include'}", "-o", str(hal_tsan), str(FAKE_DIR / "hal_app.cpp")] + no_shim +
                        [f"-L{FAKE_DIR / 'link'}", f"-L{LIB}", f"-Wl,-rpath,{LIB}", "-lxpk", "-lcuda", "-ldl", "-lrt"], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]
-    r = run_app(as_libcuda(tmp_path, fake), fake, hal_tsan, XSCHED_CUDA_LIB=fake, TSAN_OPTIONS="halt_on_error=0")
+    r = run_app(as_libcuda(tmp_path, fake), fake, hal_tsan, XSCHED_CUDA_LIB=fake, **san_env)
     text = r.stdout + r.stderr
-    assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
+    assert clean(text), text[-4000:]
     assert r.returncode == 0, text[-2000:]
     # level 2 with fake preemptible tasks (fake_xpk.cpp instead of libxpk)
     l2_tsan = tmp_path / "level2_app_tsan"
     r = subprocess.run(common + ["-std=c++20", f"-I{ROOT / 'include'}", "-o", str(l2_tsan), str(FAKE_DIR / "level2_app.cpp"), str(FAKE_DIR / "fake_xpk.cpp")] +
                        no_shim + [f"-L{FAKE_DIR / 'link'}", "-lcuda", "-ldl", "-lrt"], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]
-    r = run_app(as_libcuda(tmp_path, fake), fake, l2_tsan, XSCHED_CUDA_LIB=fake, TSAN_OPTIONS="halt_on_error=0")
+    r = run_app(as_libcuda(tmp_path, fake), fake, l2_tsan, XSCHED_CUDA_LIB=fake, **san_env)
     text = r.stdout + r.stderr
-    assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
+    assert clean(text), text[-4000:]
     assert r.returncode == 0 and '"bad_tiles": 0' in r.stdout, text[-2000:]
     for level in (1, 2):
         r = run_app(as_libcuda(tmp_path, shim), fake, app, XSCHED_CUDA_LIB=fake, XSCHED_AUTO_XQUEUE="ON", XSCHED_POLICY="HPF",
-                    XSCHED_AUTO_XQUEUE_LEVEL=level, XSCHED_AUTO_XQUEUE_THRESHOLD=4, XSCHED_AUTO_XQUEUE_BATCH_SIZE=2, TSAN_OPTIONS="halt_on_error=0")
+                    XSCHED_AUTO_XQUEUE_LEVEL=level, XSCHED_AUTO_XQUEUE_THRESHOLD=4, XSCHED_AUTO_XQUEUE_BATCH_SIZE=2, **san_env)
         text = r.stdout + r.stderr
-        assert "WARNING: ThreadSanitizer" not in text, text[-4000:]
+        assert clean(text), text[-4000:]
         assert r.returncode == 0 and r.stdout.startswith("OK "), text[-2000:]
 
 
