@@ -367,7 +367,7 @@ def impl_reference(args) -> None:
     n = max(1, r["corun"]["n"])
     line = {
         "impl": "reference", "metric": "hp_p99_latency_vs_standalone", "value": round(r["p99_ratio"], 3), "unit": "x",
-        "n_gpus": args.gpus, "steps": n, "warmup": args.warmup, "ms_per_step": round(wall * 1e3 / n, 3), "higher_is_better": False,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "hp_samples": n, "ms_per_step": round(wall * 1e3 / n, 3), "higher_is_better": False,
         "scaling": "weak", "vs_baseline": None, "dtype": "n/a (host busy-spin commands)", "data": "synthetic",
         "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "preempt_level": 1, "hp_period_us": period_us,
                    "replay": f"host-only lane: {lp_count} LP commands of {lp_us} us back-to-back, HP commands of {hp_us} us every {period_us} us, "
