@@ -42,7 +42,10 @@ int main() {
     CK(cuInit(0));
     CUdevice dev; CK(cuDeviceGet(&dev, 0));
     CUcontext ctx; CK(cuDevicePrimaryCtxRetain(&ctx, dev)); CK(cuCtxSetCurrent(ctx));
-    XK(XHintSetScheduler(kSchedulerLocal, kPolicyHighestPriorityFirst));
+    // L2_LP_ONLY=1: only the low-priority loop, under whatever scheduler the environment selects (a high-priority
+    // process elsewhere, one xserver); otherwise both queues in this process under the in-process HPF scheduler.
+    const bool lp_only = std::getenv("L2_LP_ONLY") != nullptr;
+    if (!lp_only) XK(XHintSetScheduler(kSchedulerLocal, kPolicyHighestPriorityFirst));
     CUstream s_lp, s_hp;
     CK(cuStreamCreate(&s_lp, CU_STREAM_NON_BLOCKING)); CK(cuStreamCreate(&s_hp, CU_STREAM_NON_BLOCKING));
     HwQueueHandle hq_lp, hq_hp; XQueueHandle lp, hp;
@@ -54,7 +57,7 @@ int main() {
     XK(CudaQueueGetPreemptFlag(hq_lp, &flag));
 
     const uint64_t tiles = 40;
-    const int tile_us = 200, depth = 3, iterations = 24;
+    const int tile_us = 200, depth = 3, iterations = std::getenv("L2_ITERATIONS") ? std::atoi(std::getenv("L2_ITERATIONS")) : 24;
     std::vector<xpkTask_t> tasks;
     for (int i = 0; i < depth; ++i) tasks.push_back(fakeXpkTaskCreate(tiles, tile_us, flag));
     std::atomic<int> bad_tiles{0}, finished{0};
@@ -83,7 +86,8 @@ int main() {
         lp_done.store(true);
     });
     std::vector<double> lat;
-    while (!lp_done.load()) {
+    if (lp_only) std::printf("READY\n"), std::fflush(stdout);
+    while (!lp_only && !lp_done.load()) {
         std::this_thread::sleep_for(std::chrono::milliseconds(7));
         const int64_t t0 = NowUs();
         HwCommandHandle c; XK(HwCommandCreateCallback(&c, LaunchBusy, nullptr)); XK(XQueueSubmit(hp, c));

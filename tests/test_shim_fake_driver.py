@@ -98,6 +98,42 @@ def test_level2_preempt_and_resume_on_the_cuda_hal_without_a_gpu(tmp_path):
     assert res["hp_p50_us"] < 300 + 200 + 2000            # about one tile, never one 8 ms task
 
 
+def test_level2_low_priority_process_preempted_by_a_transparent_process(tmp_path):
+    """The deployment shape of the benchmark's inference configuration, without a GPU: a low-priority process that
+    uses the XQueue API with preemptible (fake) tasks at level 2, a high-priority XSched-unaware process under the
+    interposer, one xserver with HPF.  Every request of the latter deactivates the former's queue; its tasks are
+    relaunched from their cursors and every tile still runs exactly once."""
+    import signal
+    import time
+    ns = f"l2{os.getpid()}."
+    srv_env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+    srv_env.update(XSCHED_IPC_NAMESPACE=ns, XLOG_LEVEL="WARN")
+    server = subprocess.Popen([str(LIB / "xserver"), "HPF", "50000"], stdout=subprocess.PIPE, text=True, env=srv_env)
+    lp = None
+    try:
+        assert "ready" in server.stdout.readline()
+        common = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+        common.update(FAKE_CUDA_LIB=str(FAKE), XSCHED_CUDA_LIB=str(FAKE), XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns, XSCHED_SCHEDULER="GLB")
+        lp_env = dict(common, LD_LIBRARY_PATH=f"{as_libcuda(tmp_path, FAKE)}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""), L2_LP_ONLY="1", L2_ITERATIONS="90")
+        lp = subprocess.Popen([str(FAKE_DIR / "level2_app")], stdout=subprocess.PIPE, text=True, env=lp_env)
+        assert lp.stdout.readline().startswith("READY")
+        hp_env = dict(common, LD_LIBRARY_PATH=f"{as_libcuda(tmp_path, LIB / 'libshimcuda.so')}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""),
+                      XSCHED_AUTO_XQUEUE="ON", XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_PRIORITY="1")
+        hp = subprocess.run([str(FAKE_DIR / "loop_app"), "--role", "hp", "--count", "8", "--log", str(tmp_path / "hp.log")], capture_output=True, text=True,
+                            timeout=120, env=hp_env)
+        assert hp.returncode == 0 and "DONE" in hp.stdout, hp.stdout + hp.stderr[-2000:]
+        out, _ = lp.communicate(timeout=120)
+        assert lp.returncode == 0, out
+    finally:
+        if lp is not None and lp.poll() is None:
+            lp.kill()
+        server.send_signal(signal.SIGTERM)
+        server.wait(timeout=10)
+    res = json.loads(out.strip().splitlines()[-1])
+    assert res["finished"] == res["expected"] == 90 and res["bad_tiles"] == 0, res
+    assert res["deactivations"] >= 4 and res["relaunches"] >= res["preemptions"] >= 1, res
+
+
 @pytest.mark.parametrize("sanitizer", ["thread", "address,undefined"])
 def test_interposer_and_hal_are_clean_under_sanitizers(tmp_path, sanitizer):
     """Everything between the program and the fake driver — interposer, CUDA HAL, XQueue runtime, scheduler —
