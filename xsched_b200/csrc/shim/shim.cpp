@@ -382,17 +382,21 @@ SHIM_API CUresult CUDAAPI cuStreamWaitEvent(CUstream s, CUevent ev, unsigned fla
     return Driver().cuStreamWaitEvent(s, ev, flags);
 }
 
+// The XQueue is waited for first (its commands may not have reached the driver yet), then the stream itself:
+// stream-ordered calls that are not turned into commands (the generated trampolines) are only known to the
+// driver.  (The reference stops after the XQueue, platforms/cuda/shim/src/shim.cpp:413-419.)
 SHIM_API CUresult CUDAAPI cuStreamSynchronize(CUstream s) {
     if (auto xq = Route(s)) {
         xq->WaitAll();
         g_stats.syncs_via_xqueue++;
-        return CUDA_SUCCESS;
     }
     return Driver().cuStreamSynchronize(s);
 }
 
 SHIM_API CUresult CUDAAPI cuStreamQuery(CUstream s) {
-    if (auto xq = Route(s)) return xq->Query() == kQueueStateIdle ? CUDA_SUCCESS : CUDA_ERROR_NOT_READY;
+    if (auto xq = Route(s)) {
+        if (xq->Query() != kQueueStateIdle) return CUDA_ERROR_NOT_READY;
+    }
     return Driver().cuStreamQuery(s);
 }
 
