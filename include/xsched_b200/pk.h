@@ -121,7 +121,11 @@ xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void 
                             uint32_t M, uint32_t N, uint32_t K, uint32_t flags,
                             uint32_t *flag_dev);
 
-/* ---- task control ------------------------------------------------------------------- */
+/* ---- task control ------------------------------------------------------------------- *
+ * A task belongs to the device that was current when it was created.  xpkTaskLaunch,
+ * xpkTaskReset and xpkTaskDestroy (and xpkFlagSet, for the flag's device) make that device
+ * current for the duration of the call and restore the caller's, so they may be called
+ * from any thread; `stream` must be a stream of the task's device.                       */
 
 /* Enqueue the task's kernel on `stream`.  A fresh or reset task starts at tile 0; a
  * PREEMPTED task continues from its cursor; a COMPLETED task launches nothing.  Never
