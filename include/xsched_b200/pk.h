@@ -17,7 +17,8 @@
  * All entry points take plain pointers and sizes.  Device pointers are raw CUDA device
  * addresses; streams are CUstream/cudaStream_t passed as void*.  Every function returns
  * an xpkResult; nothing here allocates behind the caller's back except xpkTaskCreate*
- * (one 4 KiB device control block + one 64-byte mapped host mailbox per task).
+ * (one device control block of about 16.6 KB — claim state plus two lists of handed-back
+ * tiles — and one 64-byte mapped host mailbox per task).
  */
 #pragma once
 #include <stddef.h>
@@ -128,7 +129,8 @@ xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void 
  * from any thread; `stream` must be a stream of the task's device.                       */
 
 /* Enqueue the task's kernel on `stream`.  A fresh or reset task starts at tile 0; a
- * PREEMPTED task continues from its cursor; a COMPLETED task launches nothing.  Never
+ * PREEMPTED task continues from its cursor; a COMPLETED task that is launched again without
+ * a reset runs a kernel that finds no tile to claim and publishes COMPLETED again.  Never
  * blocks.  `sm_limit` > 0 caps the persistent grid to that many SMs (0 = all).          */
 xpkResult xpkTaskLaunch(xpkTask_t task, void *stream, int sm_limit);
 
@@ -164,6 +166,11 @@ xpkResult xpkTaskDestroy(xpkTask_t task);
  *   - Calls no cudaMalloc/cudaFree/cudaHostAlloc and no library routine that allocates.
  *   - The first call on each device resolves the array's address (cudaGetSymbolAddress) and sets a
  *     kernel attribute; make that first call outside any stream capture.
+ *   - `stream` must be a stream of the device that is current in the calling thread: the array
+ *     that is used is the current device's copy.
+ *   - There is no status channel: a bounded wait inside the kernel that gives up (none has been
+ *     seen to) leaves the keys unsorted and is not reported; callers that need a status use the
+ *     task form (xpkTaskCreateSort / xpkTaskWait).
  *   - All calls on one device share the one array.  It keeps the previous call's contents (the entry
  *     point clears what it needs), and two calls whose kernels overlap on the GPU — different
  *     streams, or different host threads without ordering between their streams — race on it:
@@ -171,7 +178,8 @@ xpkResult xpkTaskDestroy(xpkTask_t task);
 #define XPK_SORT_NOALLOC_MAX_KEYS (4ull << 20)
 xpkResult xpkSortNoAlloc(int32_t *keys, int32_t *tmp, uint64_t n, void *stream);
 
-/* Kernels launched by this library in this process since load (all tasks). */
+/* Kernels launched by this library in this process since load (all tasks, and the sort kernels
+ * of xpkSortNoAlloc). */
 uint64_t xpkLaunchCount(void);
 
 #ifdef __cplusplus

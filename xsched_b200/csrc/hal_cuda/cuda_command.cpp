@@ -40,7 +40,29 @@ void CompletionCounter::Wait(uint64_t ticket, int64_t expected_remaining_us) con
         if (Load() >= ticket) return;
         std::this_thread::yield();
     }
-    while (Load() < ticket) std::this_thread::sleep_for(std::chrono::microseconds(20));
+    // Phase 3 also looks at the stream itself every ~4 ms.
+    int idle_looks = 0;
+    for (uint32_t n = 1; Load() < ticket; ++n) {
+        std::this_thread::sleep_for(std::chrono::microseconds(20));
+        if ((n % 64u) != 0 || stream == nullptr) continue;
+        const CUresult r = QueryStream();
+        if (r == CUDA_ERROR_NOT_READY) { idle_looks = 0; continue; }
+        if (Load() >= ticket) return;
+        if (r != CUDA_SUCCESS)
+            XERRO("waiting for completion ticket %llu: the stream's context reports error %d (%s)", (unsigned long long)ticket, (int)r, ErrorString(r));
+        if (++idle_looks >= 3)
+            XERRO("waiting for completion ticket %llu: the stream is idle but its counter stands at %llu (the write never ran)",
+                  (unsigned long long)ticket, (unsigned long long)Load());
+    }
+}
+
+CUresult CompletionCounter::QueryStream() const {
+    const DriverApi &d = Driver();
+    if (ctx && d.cuCtxPushCurrent(ctx) != CUDA_SUCCESS) return CUDA_ERROR_INVALID_CONTEXT;
+    const CUresult r = d.cuStreamQuery(stream);
+    CUcontext old;
+    if (ctx) d.cuCtxPopCurrent(&old);
+    return r;
 }
 
 uint64_t CompletionCounter::Issue(CUstream stream, CUresult *res) {

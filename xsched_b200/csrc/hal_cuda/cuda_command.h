@@ -24,13 +24,21 @@ struct CompletionCounter {
     CUdeviceptr dev = 0;                   // its device address
     std::atomic<uint64_t> next_ticket{0};
     std::mutex issue_mu;                   // ticket order must equal stream order of the writes
+    CUstream stream = nullptr;             // the queue's stream and context: asked for errors during long waits
+    CUcontext ctx = nullptr;
     /// Take the next ticket and enqueue its write on `stream`; returns the ticket (0 on failure).
     uint64_t Issue(CUstream stream, CUresult *res);
     /// Wait until *host >= ticket.  Spin briefly, then back off.  When the caller knows that the work
     /// behind the ticket still needs about `expected_remaining_us` (a task that was timed on its previous
     /// run), half of that is slept away first, so that a loop of millisecond kernels does not keep a core
-    /// busy; 0 = unknown, no sleep.
+    /// busy; 0 = unknown, no sleep.  A wait that lasts asks the driver about the stream every few
+    /// milliseconds: a context that has taken an error never executes the write, and neither does a stream
+    /// that went idle without it; both end the process with the driver's error, which is what a failed
+    /// cuEventSynchronize does in the reference (platforms/cuda/hal/src/common/cuda_command.cpp:39-44 under
+    /// CUDA_ASSERT).
     void Wait(uint64_t ticket, int64_t expected_remaining_us = 0) const;
+    /// CUDA_SUCCESS / CUDA_ERROR_NOT_READY, or the error the stream's context is in.
+    CUresult QueryStream() const;
     /// The counter as the GPU last wrote it.
     uint64_t Load() const { return __atomic_load_n(const_cast<const uint64_t *>(host), __ATOMIC_ACQUIRE); }
 };

@@ -61,6 +61,8 @@ public:
         CUDA_ASSERT(d.cuMemHostAlloc(&host, 64, CU_MEMHOSTALLOC_DEVICEMAP | CU_MEMHOSTALLOC_PORTABLE));
         *(volatile uint64_t *)host = 0;
         counter_->host = (volatile uint64_t *)host;
+        counter_->stream = stream_;
+        counter_->ctx = ctx_;
         CUDA_ASSERT(d.cuMemHostGetDevicePointer(&counter_->dev, host, 0));
 
         CUDA_ASSERT(d.cuMemAlloc(&flag_, 256));
@@ -160,6 +162,8 @@ private:
     void LaunchAndNote(const std::shared_ptr<CudaCommand> &c) {
         std::lock_guard<std::mutex> lk(tail_mu_);      // the stream's tail changes only under this lock
         const CUresult r = c->LaunchOn(stream_, counter_);
+        // A refused command ends the process here (XERRO does not return), as a failed launch does under the
+        // reference's CUDA_ASSERT: no command is ever registered as waitable without its completion write.
         if (UNLIKELY(r != CUDA_SUCCESS)) XERRO("the CUDA driver refused a queued command: %d (%s): %s", (int)r, ErrorString(r), c->Describe().c_str());
         tail_ticket_ = c->Synchronizable() ? c->Ticket() : 0;
     }

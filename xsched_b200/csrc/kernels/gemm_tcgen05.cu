@@ -21,7 +21,7 @@
 // eight epilogue warps keep that window to a few microseconds per ~120 us tile.
 //
 // Preemption.  Between tiles the producer stops claiming once the flag is up; tiles already
-// claimed are finished.  With kAbort it also polls the flag every 8 k-blocks inside a tile
+// claimed are finished.  With kAbort it also polls the flag every kAbortPollEvery (4) k-blocks inside a tile
 // and, when raised, stops loading, hands the tile back (xpk::abandon_tile) and tells the MMA
 // and epilogue warps which k-block / tile sequence number was the first not issued; they
 // finish everything older and drop the abandoned tile, whose C is untouched and which is

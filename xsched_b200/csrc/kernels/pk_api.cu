@@ -4,6 +4,7 @@
 #include "pk_common.cuh"
 
 #include <cuda.h>
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cstring>
@@ -20,7 +21,7 @@ int stream_ctas_per_sm();
 // radix_sort.cu
 size_t sort_smem_bytes();
 cudaError_t sort_prepare();
-int sort_ctas_per_sm();
+int sort_ctas_per_sm(bool preemptible);
 unsigned long long sort_tiles(unsigned long long n);
 cudaError_t launch_sort(bool preemptible, Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint32_t *state,
                         unsigned long long n, unsigned long long launch_no, int grid, cudaStream_t stream);
@@ -45,9 +46,11 @@ struct xpkTask_st {
     Mailbox *mb_dev = nullptr;        // device alias
     uint32_t *flag = nullptr;         // flag the kernels poll
     unsigned long long total = 0;
-    unsigned long long launches = 0;        // launch counter echoed by the mailbox
-    unsigned long long reset_at = 0;        // value of `launches` at the last reset
-    cudaStream_t last_stream = nullptr;     // stream of the most recent launch
+    // Written by whichever thread launches or resets the task (an XQueue worker, the scheduler's thread on a
+    // relaunch), read by application threads in xpkTaskQuery / xpkTaskWait.
+    std::atomic<unsigned long long> launches{0};        // launch counter echoed by the mailbox
+    std::atomic<unsigned long long> reset_at{0};        // value of `launches` at the last reset
+    std::atomic<cudaStream_t> last_stream{nullptr};     // stream of the most recent launch
     // operands
     void *p0 = nullptr; const void *p1 = nullptr; const void *p2 = nullptr;
     float s = 0.f;
@@ -63,6 +66,9 @@ struct xpkTask_st {
 namespace {
 
 std::atomic<uint64_t> g_launches{0};
+} // namespace
+namespace xpk { void note_launches(unsigned n) { g_launches.fetch_add(n); } }
+namespace {
 
 constexpr size_t kSortScratchHeader = 4096;   // hist[4][256] u32
 
@@ -273,7 +279,7 @@ xpkResult xpkTaskCreateSort(xpkTask_t *task, int32_t *keys, int32_t *tmp, void *
         std::lock_guard<std::mutex> lk(g_dev_mtx);
         if (!d->sort_ready) {
             if (xpk::sort_prepare() != cudaSuccess) { task_free(t); return XPK_ERR_CUDA; }
-            d->sort_ctas = xpk::sort_ctas_per_sm();
+            d->sort_ctas = std::min(xpk::sort_ctas_per_sm(true), xpk::sort_ctas_per_sm(false));
             d->sort_ready = true;
         }
     }
@@ -317,7 +323,7 @@ xpkResult xpkTaskLaunch(xpkTask_t t, void *stream, int sm_limit) {
     const bool preemptible = !(t->flags & XPK_FLAG_NON_PREEMPTIBLE);
     int sms = t->sm_count;
     if (sm_limit > 0 && sm_limit < sms) sms = sm_limit;
-    const unsigned long long launch_no = ++t->launches;
+    const unsigned long long launch_no = t->launches.fetch_add(1) + 1;
     cudaError_t e = cudaSuccess;
     unsigned long long grid;
     switch (t->kind) {
@@ -345,7 +351,7 @@ xpkResult xpkTaskLaunch(xpkTask_t t, void *stream, int sm_limit) {
         return XPK_ERR_INVALID_VALUE;
     }
     if (e != cudaSuccess) return XPK_ERR_CUDA;
-    t->last_stream = s;
+    t->last_stream.store(s);
     g_launches.fetch_add(1);
     return XPK_SUCCESS;
 }
@@ -353,18 +359,20 @@ xpkResult xpkTaskLaunch(xpkTask_t t, void *stream, int sm_limit) {
 xpkResult xpkTaskQuery(xpkTask_t t, xpkTaskInfo *info) {
     if (!t || !info) return XPK_ERR_INVALID_VALUE;
     volatile Mailbox *m = t->mb_host;
+    // One reading of each counter per query: a launch from another thread may land in between.
+    const unsigned long long launches = t->launches.load(), reset_at = t->reset_at.load();
     const unsigned long long seq = m->seq;
     std::atomic_thread_fence(std::memory_order_acquire);
     info->tiles_total = t->total;
-    info->launches = t->launches;
-    if (t->launches == t->reset_at) {            // nothing launched since creation / reset
+    info->launches = launches;
+    if (launches == reset_at) {                  // nothing launched since creation / reset
         info->status = XPK_STATUS_IDLE;
         info->error = 0; info->tiles_done = 0; info->preemptions = 0;
-    } else if (seq < t->launches) {              // the newest launch has not published yet
+    } else if (seq < launches) {                 // the newest launch has not published yet
         info->status = XPK_STATUS_RUNNING;
         info->error = 0;
-        info->tiles_done = seq > t->reset_at ? m->tiles_done : 0;
-        info->preemptions = seq > t->reset_at ? m->preemptions : 0;
+        info->tiles_done = seq > reset_at ? m->tiles_done : 0;
+        info->preemptions = seq > reset_at ? m->preemptions : 0;
     } else {
         info->status = m->status;
         info->error = m->error;
@@ -379,12 +387,12 @@ xpkResult xpkTaskWait(xpkTask_t t, uint64_t timeout_us, xpkTaskInfo *info) {
     volatile Mailbox *m = t->mb_host;
     const auto t0 = std::chrono::steady_clock::now();
     uint32_t spins = 0;
-    while (t->launches != t->reset_at && m->seq < t->launches) {
+    while (t->launches.load() != t->reset_at.load() && m->seq < t->launches.load()) {
         if (++spins > 2000) {
             std::this_thread::yield();
             if ((spins & 1023u) == 0) {
                 // A faulted context never publishes: surface the CUDA error instead of timing out.
-                const cudaError_t qe = cudaStreamQuery(t->last_stream);
+                const cudaError_t qe = cudaStreamQuery(t->last_stream.load());
                 if (qe != cudaSuccess && qe != cudaErrorNotReady) return XPK_ERR_CUDA;
                 const auto us = std::chrono::duration_cast<std::chrono::microseconds>(
                                     std::chrono::steady_clock::now() - t0).count();
@@ -407,7 +415,7 @@ xpkResult xpkTaskReset(xpkTask_t t, void *stream) {
     if (t->kind == XPK_KIND_SORT) {
         if (cudaMemsetAsync(t->sort_hist, 0, t->sort_scratch_bytes, s) != cudaSuccess) return XPK_ERR_CUDA;
     }
-    t->reset_at = t->launches;
+    t->reset_at.store(t->launches.load());
     return XPK_SUCCESS;
 }
 

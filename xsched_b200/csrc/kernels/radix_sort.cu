@@ -35,6 +35,8 @@
 
 namespace xpk {
 
+void note_launches(unsigned n);      // pk_api.cu: the library-wide launch counter
+
 constexpr int kSortThreads = 512;
 constexpr int kSortWarps   = kSortThreads / 32;
 constexpr int kSortItems   = 16;
@@ -308,9 +310,10 @@ cudaError_t sort_prepare() {
     return cudaFuncSetAttribute(radix_sort_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
 }
 
-int sort_ctas_per_sm() {
+int sort_ctas_per_sm(bool preemptible) {
     int a = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&a, radix_sort_kernel<true>, kSortThreads, sizeof(SortSmem));
+    if (preemptible) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&a, radix_sort_kernel<true>, kSortThreads, sizeof(SortSmem));
+    else             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&a, radix_sort_kernel<false>, kSortThreads, sizeof(SortSmem));
     return a < 1 ? 1 : a;
 }
 
@@ -387,7 +390,7 @@ extern "C" xpkResult xpkSortNoAlloc(int32_t *keys, int32_t *tmp, uint64_t n, voi
             if (xpk::sort_prepare() != cudaSuccess) return XPK_ERR_CUDA;
             int sms = 0;
             if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return XPK_ERR_CUDA;
-            g_noalloc_dev[dev].grid_limit = sms * xpk::sort_ctas_per_sm();
+            g_noalloc_dev[dev].grid_limit = sms * xpk::sort_ctas_per_sm(/*preemptible=*/false);
             g_noalloc_dev[dev].base = static_cast<unsigned char *>(p);
         }
         d = g_noalloc_dev[dev];
@@ -407,5 +410,6 @@ extern "C" xpkResult xpkSortNoAlloc(int32_t *keys, int32_t *tmp, uint64_t n, voi
     if (xpk::launch_sort(/*preemptible=*/false, ctl, reinterpret_cast<uint32_t *>(keys), reinterpret_cast<uint32_t *>(tmp), hist, state, n,
                          /*launch_no=*/1, (int)grid, s) != cudaSuccess)
         return XPK_ERR_CUDA;
+    xpk::note_launches(2);       // the control-block set-up kernel and the sort kernel
     return XPK_SUCCESS;
 }

@@ -20,10 +20,6 @@
 #include <mutex>
 #include <unordered_map>
 #include <cuda.h>
-#include <csignal>
-#include <execinfo.h>
-#include <ucontext.h>
-#include <unistd.h>
 
 #include "hal_cuda/cuda_command.h"
 #include "hal_cuda/driver.h"
@@ -574,31 +570,8 @@ const FwdEntry kForwarders[] = {
 };
 #undef XSHIM_FWD
 
-// XSCHED_SHIM_BACKTRACE=ON: print a native backtrace on SIGSEGV (diagnostic aid for interposer problems).
-void SegvBacktrace(int sig, siginfo_t *info, void *uctx) {
-    const ucontext_t *uc = static_cast<const ucontext_t *>(uctx);
-    const uintptr_t rip = (uintptr_t)uc->uc_mcontext.gregs[REG_RIP], rsp = (uintptr_t)uc->uc_mcontext.gregs[REG_RSP];
-    char line[256];
-    const int len = std::snprintf(line, sizeof(line), "[xsched shim] SIGSEGV: fault address %p, rip %p, return address %p\n", info->si_addr,
-                                  (void *)rip, rsp ? *(void **)rsp : nullptr);
-    if (write(2, line, (size_t)len) < 0) {}
-    void *frames[64];
-    frames[0] = rsp ? *(void **)rsp : nullptr;
-    backtrace_symbols_fd(frames, 1, 2);
-    const int n = backtrace(frames, 64);
-    backtrace_symbols_fd(frames, n, 2);
-    signal(sig, SIG_DFL);
-    raise(sig);
-}
-
 struct Init {
     Init() {
-        if (GetEnvOption("XSCHED_SHIM_BACKTRACE", false)) {
-            struct sigaction sa {};
-            sa.sa_sigaction = SegvBacktrace;
-            sa.sa_flags = SA_SIGINFO;
-            sigaction(SIGSEGV, &sa, nullptr);
-        }
         const DriverApi &d = Driver();
         for (const FwdEntry &e : kForwarders) {
             void *p = d.Sym(e.name);
