@@ -141,6 +141,11 @@ xpkResult xpkTaskQuery(xpkTask_t task, xpkTaskInfo *info);
  * published COMPLETED, PREEMPTED or ERROR, or `timeout_us` elapses (XPK_ERR_BUSY).      */
 xpkResult xpkTaskWait(xpkTask_t task, uint64_t timeout_us, xpkTaskInfo *info);
 
+/* Device-clock stamps (%globaltimer, nanoseconds) of the launch whose result the mailbox holds: when its
+ * first CTA started and when its last CTA left.  For latency break-downs; XPK_ERR_BUSY before any launch
+ * has published.  The GPU clock is not the host's: callers calibrate an offset themselves.            */
+xpkResult xpkTaskTimes(xpkTask_t task, uint64_t *start_ns, uint64_t *exit_ns);
+
 /* Rewind the cursor to tile 0 (enqueued on `stream`, ordered after prior work on it). */
 xpkResult xpkTaskReset(xpkTask_t task, void *stream);
 

@@ -69,6 +69,7 @@ __attribute__((visibility("default"))) xpkResult xpkTaskLaunch(xpkTask_t t, void
     { std::lock_guard<std::mutex> lk(t->mu); no = ++t->launches; }
     return cuLaunchHostFunc((CUstream)stream, RunTask, new LaunchArg{t, no}) == CUDA_SUCCESS ? XPK_SUCCESS : XPK_ERR_CUDA;
 }
+__attribute__((visibility("default"))) xpkResult xpkTaskTimes(xpkTask_t, uint64_t *, uint64_t *) { return XPK_ERR_BUSY; }
 __attribute__((visibility("default"))) xpkResult xpkTaskQuery(xpkTask_t t, xpkTaskInfo *info) {
     std::lock_guard<std::mutex> lk(t->mu);
     info->tiles_total = t->tiles;

@@ -121,6 +121,53 @@ def test_triad_preempt_resume_bit_exact(pk, ok):
     t.destroy()
 
 
+def _free_gb():
+    free, _ = torch.cuda.mem_get_info()
+    return free / 2**30
+
+
+@pytest.mark.parametrize("n", [1 << 31, (1 << 31) - 5])
+def test_triad_2p31_elements_against_the_cpu_loop(pk, ok, n):
+    """The size of the memory-bound workload configuration: 3 arrays of 2^31 fp32 (8 GiB each, byte offsets past
+    2^32, so the 64-bit index path).  One forced preemption, then the WHOLE output is compared bit for bit with
+    the CPU loop, chunk by chunk (the inputs are copied back from the device, so both sides see the same bits);
+    the windows named below are the ones most likely to show an index that wrapped."""
+    import psutil
+    if _free_gb() < 30 or psutil.virtual_memory().available < 8 * 2**30:
+        pytest.skip("needs 30 GB of device memory and 8 GB of host memory")
+    g = torch.Generator(device="cuda").manual_seed(31)
+    b = torch.rand(n, device="cuda", generator=g).mul_(2).sub_(1)
+    c = torch.rand(n, device="cuda", generator=g).mul_(2).sub_(1)
+    a = torch.full((n,), float("nan"), device="cuda")
+    s = 0.4375
+    t = pk.Task.triad(a, b, c, s)
+    info = _preempt_once(t, pk, sm_limit=2)
+    assert info.status == pk.STATUS_PREEMPTED and 0 <= info.tiles_done < info.tiles_total
+    assert bool(torch.isnan(a[-1]))                    # the cut really left work undone
+    _run_to_completion(t, pk)
+    assert t.query().tiles_done == t.query().tiles_total
+
+    def same(lo, hi):
+        want = ok.triad(b[lo:hi].cpu().numpy(), c[lo:hi].cpu().numpy(), s)
+        return np.array_equal(a[lo:hi].cpu().numpy().view(np.uint32), want.view(np.uint32))
+    M1 = 1 << 20
+    assert same(0, M1)                                  # first 1 Mi elements
+    assert same((1 << 30) - M1 // 2, (1 << 30) + M1 // 2)   # straddles element 2^30 = byte offset 2^32
+    assert same(n - M1 - 3, n)                          # last 1 Mi and the ragged tail
+    chunk = 1 << 27
+    h_gpu = h_cpu = 0
+    for lo in range(0, n, chunk):
+        hi = min(n, lo + chunk)
+        bh, ch = b[lo:hi].cpu().numpy(), c[lo:hi].cpu().numpy()
+        want = ok.triad(bh, ch, s)
+        got = a[lo:hi].cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"chunk at {lo}"
+        h_gpu = (h_gpu + ok.checksum_u32(got)) & (2**64 - 1)
+        h_cpu = (h_cpu + ok.checksum_u32(want)) & (2**64 - 1)
+    assert h_gpu == h_cpu                               # checksum of checksums over the full array
+    t.destroy()
+
+
 def test_flag_raised_before_launch_makes_no_progress(pk):
     n = 1 << 20
     a = torch.zeros(n, device="cuda")
@@ -280,6 +327,73 @@ def test_gemm_preempt_resume_bit_exact(pk, ok, flags_name):
     _run_to_completion(t, pk)
     assert t.query().tiles_done == t.query().tiles_total
     assert torch.equal(c, base)
+    t.destroy()
+
+
+def _check_rows_scaled(ok, c_gpu, a, b, rows, scale):
+    """Sampled rows against the fp64 product.  Tolerance: bf16 output rounding (2^-9 relative, doubled) plus
+    1e-3 * sqrt(K) * scale absolute, scale = product of the operands' standard deviations (fp32 accumulation
+    error is orders of magnitude below that)."""
+    K = a.shape[1]
+    a_bits = a.view(torch.int16).numpy().view(np.uint16)
+    b_bits = b.view(torch.int16).numpy().view(np.uint16)
+    ref = ok.gemm_bf16_rows(a_bits, b_bits, np.asarray(rows, dtype=np.uint32))
+    got = c_gpu[rows].float().cpu().numpy().astype(np.float64)
+    tol = np.abs(ref) * 2.0**-8 + 1e-3 * math.sqrt(K) * scale
+    bad = np.abs(got - ref) > tol
+    assert not bad.any(), f"{bad.sum()} of {bad.size} elements outside tolerance; max err {np.abs(got-ref).max()}"
+    assert np.abs(ref).max() > 10 * tol.min()           # the rows are not trivially within tolerance
+
+
+@pytest.mark.parametrize("shape,b_std", [((8192, 8192, 8192), 1.0), ((16384, 14336, 4096), 0.02)],
+                         ids=["8192cubed", "16384x4096_by_4096x14336_weights_0.02"])
+def test_gemm_baseline_shapes_against_fp64_rows(pk, ok, shape, b_std):
+    """The two GEMM shapes of the workload configurations (8192^3 with N(0,1) operands; the inference-shaped
+    (16384x4096)(4096x14336) with weights ~ N(0, 0.02)): eight sampled rows — first and last row of the first and
+    last row-block, rows either side of the 128-row accumulator boundary — against the fp64 product, for a straight
+    run and for a run cut at least three times with in-flight abort; the two runs must also agree bit for bit."""
+    M, N, K = shape
+    g = torch.Generator(device="cpu").manual_seed(M + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    b = (torch.randn(N, K, generator=g) * b_std).to(torch.bfloat16)
+    ad, bd = a.cuda(), b.cuda()
+    rows = [0, 127, 128, 255, M // 2 + 1, M - 256, M - 129, M - 1]
+    base = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    t0 = pk.Task.gemm(base, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT)
+    assert _run_to_completion(t0, pk) == 1
+    t0.destroy()
+    assert not bool(torch.isnan(base).any())
+    _check_rows_scaled(ok, base, a, b, rows, b_std)
+
+    c = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    t = pk.Task.gemm(c, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT)
+    cuts = 0
+    for sm_limit in (4, 16, 64, 148, 148):
+        info = _preempt_once(t, pk, sm_limit=sm_limit)
+        if info.status == pk.STATUS_COMPLETED:
+            break
+        assert info.status == pk.STATUS_PREEMPTED, f"err {info.error:#x}"
+        cuts += 1
+    assert cuts >= 3
+    _run_to_completion(t, pk)
+    assert t.query().tiles_done == t.query().tiles_total
+    assert torch.equal(c, base)
+    _check_rows_scaled(ok, c, a, b, rows, b_std)
+    t.destroy()
+
+
+def test_sort_64m_keys_against_numpy(pk):
+    """One size well above the workload's 16 Mi keys (the look-back words hold 30-bit counts): 64 Mi keys over the
+    full int32 range, cut twice, against numpy's sort."""
+    n = 1 << 26
+    k = np.random.default_rng(64).integers(-2**31, 2**31, size=n, dtype=np.int64).astype(np.int32)
+    keys, tmp, scratch = _sort_buffers(pk, k)
+    t = pk.Task.sort(keys, tmp, scratch)
+    for _ in range(2):
+        info = _preempt_once(t, pk, sm_limit=6)
+        assert info.status in (pk.STATUS_PREEMPTED, pk.STATUS_COMPLETED), f"err {info.error:#x}"
+    _run_to_completion(t, pk)
+    assert np.array_equal(keys.cpu().numpy(), np.sort(k))
     t.destroy()
 
 

@@ -4,6 +4,9 @@
 //                XQueue at the given preemption level until --duration-s elapses (or SIGTERM);
 //   --role hp    a high-priority request every --period-us (vecadd | sort), latency = submit -> wait;
 //   --role both  the two roles as two threads / two XQueues of ONE process (in-process scheduler);
+//   --role idle  a process that holds a CUDA context, buffers and a suspended queue but runs nothing, and
+//   --role spin-lp  one that runs --kernel-us sleep kernels back to back on a plain stream (no XQueue): the two
+//                control arms beside which a high-priority process shows what another context costs by itself;
 //   --role level-sweep   the reference's level-1 suspend-latency sweep over sleep kernels of 10..2000 us;
 //   --role preempt-latency
 //                the reference's preemption-latency experiment (platforms/cuda/test/main/level.cu:37-86):
@@ -23,6 +26,7 @@
 #include <random>
 #include <string>
 #include <thread>
+#include <numeric>
 #include <vector>
 #include <cuda_runtime.h>
 #include <sys/prctl.h>
@@ -31,6 +35,7 @@
 #include "xsched/xsched.h"
 #include "xsched/cuda/hal.h"
 #include "xsched_b200/pk.h"
+#include "xsched/utils/trace.h"
 
 #define CK(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { std::fprintf(stderr, "%s -> %s\n", #x, cudaGetErrorString(e_)); std::exit(3); } } while (0)
 #define XK(x) do { XResult r_ = (x); if (r_ != kXSchedSuccess) { std::fprintf(stderr, "%s -> %d\n", #x, (int)r_); std::exit(4); } } while (0)
@@ -55,10 +60,12 @@ struct Args {
     std::string role = "lp", kernel = "gemm", hp_kernel = "vecadd";
     int level = 2, prio = 0, threshold = 16, batch = 8, depth = 8, abort_inflight = 1, count = 500, device = 0, e2e = 0;
     int M = 8192, N = 8192, K = 8192;
+    float b_std = 1.0f;       // standard deviation of the GEMM's B operand (0.02 = weight-like)
     uint64_t n = 1ull << 26, hp_n = 1ull << 26, seed = 1;
     double duration_s = 5, warmup_s = 0.5;
     int64_t period_us = 10000, kernel_us = 500, laxity_us = -1;
     int poisson = 0;
+    int tamper_at = -1;       // self-test of the output check: spoil one sample of the output of this iteration before it is verified
     std::string samples_path;
 };
 
@@ -73,12 +80,14 @@ static Args Parse(int argc, char **argv) {
         else if (k == "--count") a.count = std::atoi(v.c_str()); else if (k == "--device") a.device = std::atoi(v.c_str());
         else if (k == "--M") a.M = std::atoi(v.c_str()); else if (k == "--N") a.N = std::atoi(v.c_str()); else if (k == "--K") a.K = std::atoi(v.c_str());
         else if (k == "--n") a.n = std::strtoull(v.c_str(), nullptr, 10); else if (k == "--hp-n") a.hp_n = std::strtoull(v.c_str(), nullptr, 10);
+        else if (k == "--b-std") a.b_std = (float)std::atof(v.c_str());
         else if (k == "--seed") a.seed = std::strtoull(v.c_str(), nullptr, 10);
         else if (k == "--duration-s") a.duration_s = std::atof(v.c_str()); else if (k == "--warmup-s") a.warmup_s = std::atof(v.c_str());
         else if (k == "--period-us") a.period_us = std::atoll(v.c_str()); else if (k == "--kernel-us") a.kernel_us = std::atoll(v.c_str());
         else if (k == "--laxity-us") a.laxity_us = std::atoll(v.c_str());
         else if (k == "--poisson") a.poisson = std::atoi(v.c_str()); else if (k == "--e2e") a.e2e = std::atoi(v.c_str());
         else if (k == "--samples") a.samples_path = v;
+        else if (k == "--tamper-at") a.tamper_at = std::atoi(v.c_str());
         else { std::fprintf(stderr, "unknown option %s\n", k.c_str()); std::exit(2); }
     }
     return a;
@@ -104,23 +113,87 @@ __global__ void FillKeys(int32_t *p, uint64_t n, uint64_t seed) {            // 
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
         p[i] = (int32_t)(Mix(i + seed * 0x9E3779B97F4A7C15ull) & 0x7FFFFFFFu);
 }
-// Order-sensitive 64-bit checksum of 32-bit words (same formula as the CPU oracle's checksum).
-__global__ void Checksum(const uint32_t *p, uint64_t n, unsigned long long *out) {
-    unsigned long long h = 0;
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
-        h += (unsigned long long)p[i] * ((i & 0xFFFFu) + 1u);
-    for (int o = 16; o; o >>= 1) h += __shfl_down_sync(0xffffffffu, h, o);
-    if ((threadIdx.x & 31) == 0) atomicAdd(out, h);
+// Output check of the low-priority loops.  A tile that a preempted-and-resumed iteration never wrote must be
+// visible, so every iteration's output starts out spoiled and is looked at before the buffer is reused:
+//   * SamplePoison writes a NaN pattern into one 32-byte sector every `stride_words` words of the buffer,
+//     SampleHash reads exactly those sectors back (order-sensitive 64-bit sum, the formula of the CPU oracle's
+//     checksum restricted to the sampled words).  The stride is chosen so that every
+//     row of every GEMM tile (512 bytes) and every quarter of a streaming tile (16 KiB) holds a sample: a tile
+//     that was skipped, or written only in part, keeps poison in at least one of them.
+//   * both run on a side stream, on a buffer no in-flight task touches (each slot of the loop owns its output).
+// A whole-buffer hash (stride 8 words = every sector) is taken where it is cheap against the iteration.
+constexpr uint32_t kPoisonWord = 0xFFFFFFFFu;            // NaN as bf16 pair and as fp32; never produced by a sort of non-negative keys
+__global__ void SamplePoison(uint32_t *p, uint64_t words, uint64_t stride_words) {
+    const uint64_t samples = (words + stride_words - 1) / stride_words;
+    for (uint64_t k = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; k < samples; k += (uint64_t)gridDim.x * blockDim.x)
+        for (uint64_t w = k * stride_words; w < k * stride_words + 8 && w < words; ++w) p[w] = kPoisonWord;
 }
-static unsigned long long DeviceChecksum(const void *p, uint64_t words, cudaStream_t s) {
-    unsigned long long *d, h = 0;
-    CK(cudaMalloc(&d, 8));
-    CK(cudaMemsetAsync(d, 0, 8, s));
-    Checksum<<<592, 256, 0, s>>>((const uint32_t *)p, words, d);
-    CK(cudaMemcpyAsync(&h, d, 8, cudaMemcpyDeviceToHost, s));
-    CK(cudaStreamSynchronize(s));
-    CK(cudaFree(d));
-    return h;
+__global__ void SampleHash(const uint32_t *p, uint64_t words, uint64_t stride_words, unsigned long long *out) {
+    const uint64_t samples = (words + stride_words - 1) / stride_words;
+    unsigned long long h = 0;
+    for (uint64_t k = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; k < samples; k += (uint64_t)gridDim.x * blockDim.x)
+        for (uint64_t w = k * stride_words; w < k * stride_words + 8 && w < words; ++w)
+            h += (unsigned long long)p[w] * ((w & 0xFFFFu) + 1u);
+    for (int o = 16; o; o >>= 1) h += __shfl_down_sync(0xffffffffu, h, o);
+    if ((threadIdx.x & 31) == 0 && h) atomicAdd(out, h);
+}
+struct Verifier {
+    cudaStream_t side = nullptr;
+    unsigned long long *dev = nullptr, *host = nullptr;
+    void Init() {
+        CK(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+        CK(cudaMalloc(&dev, 8));
+        CK(cudaMallocHost(&host, 8));
+    }
+    unsigned long long Hash(const void *p, uint64_t words, uint64_t stride_words) {
+        CK(cudaMemsetAsync(dev, 0, 8, side));
+        SampleHash<<<592, 256, 0, side>>>((const uint32_t *)p, words, stride_words, dev);
+        CK(cudaMemcpyAsync(host, dev, 8, cudaMemcpyDeviceToHost, side));
+        CK(cudaStreamSynchronize(side));
+        return *host;
+    }
+    void Poison(void *p, uint64_t words, uint64_t stride_words) {
+        SamplePoison<<<592, 256, 0, side>>>((uint32_t *)p, words, stride_words);
+        CK(cudaStreamSynchronize(side));
+    }
+};
+
+// ---- timeline support: device clock against the host's monotonic clock --------------------------------------
+// A one-thread kernel publishes %globaltimer to a mapped host word for a fraction of a millisecond while the
+// host reads the word and its own clock; the smallest (host - device) difference seen is the offset plus the
+// shortest time a device write takes to become visible to the host (well under a microsecond).
+__global__ void PublishClock(volatile unsigned long long *out, int rounds) {
+    for (int i = 0; i < rounds; ++i) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        *out = t;
+        __threadfence_system();
+    }
+}
+static void CalibrateGpuClock() {
+    if (!XTraceEnabled()) return;
+    unsigned long long *h = nullptr, *d = nullptr;
+    CK(cudaHostAlloc(&h, 64, cudaHostAllocMapped));
+    *h = 0;
+    CK(cudaHostGetDevicePointer(&d, h, 0));
+    cudaStream_t s;
+    CK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    int64_t best = INT64_MAX, worst_seen = 0;
+    for (int rep = 0; rep < 3; ++rep) {
+        PublishClock<<<1, 1, 0, s>>>(d, 20000);
+        unsigned long long last = 0;
+        while (cudaStreamQuery(s) == cudaErrorNotReady) {
+            for (int i = 0; i < 200; ++i) {
+                const unsigned long long v = *(volatile unsigned long long *)h;
+                const int64_t now = NowNs();
+                if (v != 0 && v != last) { const int64_t diff = now - (int64_t)v; if (diff < best) best = diff; if (diff > worst_seen) worst_seen = diff; last = v; }
+            }
+        }
+        CK(cudaStreamSynchronize(s));
+    }
+    XTraceStamp(xsched::utils::kTraceGpuClockOffset, (uint64_t)best, 1000);
+    CK(cudaStreamDestroy(s));
+    CK(cudaFreeHost(h));
 }
 
 struct Queue {
@@ -143,9 +216,11 @@ static Queue MakeQueue(const Args &a, int level, int prio) {
 
 // ---- low-priority workload ------------------------------------------------------------------------
 struct LpWork {
-    std::vector<xpkTask_t> tasks;       // `depth` tasks over the same buffers
-    void *out = nullptr;
+    std::vector<xpkTask_t> tasks;       // `depth` tasks over the same inputs, each with an output buffer of its own
+    std::vector<void *> outs;           // output of task i (the sort has one task and sorts in place)
     uint64_t out_words = 0;
+    uint64_t sample_stride_words = 8;   // distance between the sampled sectors of the per-iteration check (8 = every sector)
+    bool full_hash_cheap = true;        // also hash the whole output after every iteration
     double work_per_iter = 0;           // flop or bytes
     const char *unit = "";
     // sort needs its input restored before every iteration
@@ -157,30 +232,39 @@ static LpWork BuildLp(const Args &a, const Queue &q, uint32_t task_flags) {
     LpWork w;
     cudaStream_t s = q.stream;
     if (a.kernel == "gemm") {
-        __nv_bfloat16 *A, *B, *C;
-        CK(cudaMalloc(&A, (size_t)a.M * a.K * 2)); CK(cudaMalloc(&B, (size_t)a.N * a.K * 2)); CK(cudaMalloc(&C, (size_t)a.M * a.N * 2));
+        __nv_bfloat16 *A, *B;
+        CK(cudaMalloc(&A, (size_t)a.M * a.K * 2)); CK(cudaMalloc(&B, (size_t)a.N * a.K * 2));
         FillNormalBf16<<<1184, 256, 0, s>>>(A, (uint64_t)a.M * a.K, a.seed, 1.0f);
-        FillNormalBf16<<<1184, 256, 0, s>>>(B, (uint64_t)a.N * a.K, a.seed + 7, 1.0f);
+        FillNormalBf16<<<1184, 256, 0, s>>>(B, (uint64_t)a.N * a.K, a.seed + 7, a.b_std);
         CK(cudaStreamSynchronize(s));
         for (int i = 0; i < a.depth; ++i) {
             xpkTask_t t;
+            void *C;
+            CK(cudaMalloc(&C, (size_t)a.M * a.N * 2));
             PK(xpkTaskCreateGemm(&t, C, A, B, a.M, a.N, a.K, task_flags | (a.abort_inflight ? XPK_FLAG_ABORT_INFLIGHT : 0), q.flag));
             w.tasks.push_back(t);
+            w.outs.push_back(C);
         }
-        w.out = C; w.out_words = (uint64_t)a.M * a.N / 2;
+        w.out_words = (uint64_t)a.M * a.N / 2;
+        w.sample_stride_words = 128;          // one sector per 512 bytes: every row of every 256-column tile
         w.work_per_iter = 2.0 * a.M * a.N * a.K; w.unit = "TFLOP/s";
     } else if (a.kernel == "triad") {
-        float *x, *y, *z;
-        CK(cudaMalloc(&x, a.n * 4)); CK(cudaMalloc(&y, a.n * 4)); CK(cudaMalloc(&z, a.n * 4));
+        float *y, *z;
+        CK(cudaMalloc(&y, a.n * 4)); CK(cudaMalloc(&z, a.n * 4));
         FillUniform<<<1184, 256, 0, s>>>(y, a.n, a.seed);
         FillUniform<<<1184, 256, 0, s>>>(z, a.n, a.seed + 11);
         CK(cudaStreamSynchronize(s));
         for (int i = 0; i < a.depth; ++i) {
             xpkTask_t t;
+            float *x;
+            CK(cudaMalloc(&x, a.n * 4));
             PK(xpkTaskCreateTriad(&t, x, y, z, 1.5f, a.n, 0, task_flags, q.flag));
             w.tasks.push_back(t);
+            w.outs.push_back(x);
         }
-        w.out = x; w.out_words = a.n;
+        w.out_words = a.n;
+        w.sample_stride_words = 4096;         // one sector per 16 KiB: four per 16 Ki-element tile
+        w.full_hash_cheap = a.n <= (1ull << 28);   // re-reading 8 GiB per iteration would take a third of the loop's bandwidth
         w.work_per_iter = 12.0 * a.n; w.unit = "GB/s";
     } else if (a.kernel == "sort") {
         int32_t *tmp; void *scratch;
@@ -192,7 +276,7 @@ static LpWork BuildLp(const Args &a, const Queue &q, uint32_t task_flags) {
         PK(xpkTaskCreateSort(&t, w.keys, tmp, scratch, a.n, task_flags, q.flag));
         w.tasks.push_back(t);
         w.nkeys = a.n;
-        w.out = w.keys; w.out_words = a.n;
+        w.outs.push_back(w.keys); w.out_words = a.n;
         w.work_per_iter = 36.0 * a.n; w.unit = "GB/s";
     } else {
         std::fprintf(stderr, "unknown --kernel %s\n", a.kernel.c_str());
@@ -201,7 +285,10 @@ static LpWork BuildLp(const Args &a, const Queue &q, uint32_t task_flags) {
     return w;
 }
 
-struct LpResult { uint64_t iters = 0; double seconds = 0, rate = 0; unsigned long long want = 0, got = 0; uint64_t preemptions = 0; CudaQueueStats stats{}; };
+struct LpResult {
+    uint64_t iters = 0; double seconds = 0, rate = 0; unsigned long long want = 0, got = 0; uint64_t preemptions = 0; CudaQueueStats stats{};
+    uint64_t verified_iters = 0, verified_preempted_iters = 0, mismatched_iters = 0;    // per-iteration output checks
+};
 
 static XResult RestoreKeys(HwQueueHandle hwq, void *data) {
     LpWork *w = (LpWork *)data;
@@ -209,18 +296,37 @@ static XResult RestoreKeys(HwQueueHandle hwq, void *data) {
                ? kXSchedSuccess : kXSchedErrorHardware;
 }
 
-static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool> *ready, double duration_s) {
-    LpResult r;
-    // Reference result: one straight run with the flag never raised, outside any XQueue.
+// Expected hashes of one task's output: a straight run with the flag never raised, outside any XQueue.
+struct LpExpect { unsigned long long full = 0, sampled = 0; };
+static LpExpect StraightRun(const Queue &q, LpWork &w, Verifier &v) {
     if (w.keys) CK(cudaMemcpyAsync(w.keys, w.keys0, w.nkeys * 4, cudaMemcpyDeviceToDevice, q.stream));
     PK(xpkTaskReset(w.tasks[0], q.stream));
     PK(xpkTaskLaunch(w.tasks[0], q.stream, 0));
     CK(cudaStreamSynchronize(q.stream));
-    r.want = DeviceChecksum(w.out, w.out_words, q.stream);
-    CK(cudaMemsetAsync(w.out, 0, w.out_words * 4, q.stream));
-    CK(cudaStreamSynchronize(q.stream));
+    LpExpect e;
+    e.full = v.Hash(w.outs[0], w.out_words, 8);
+    e.sampled = v.Hash(w.outs[0], w.out_words, w.sample_stride_words);
+    return e;
+}
 
-    std::vector<HwCommandHandle> ring(w.tasks.size(), 0);
+// Looks at the output of the iteration that just completed in `slot` and spoils the buffer for the next one.
+// Returns false when the output is not the straight run's.
+static bool CheckSlot(const LpWork &w, Verifier &v, size_t slot, const LpExpect &want, bool tamper) {
+    if (tamper) v.Poison((uint32_t *)w.outs[slot] + (w.out_words / 2 / w.sample_stride_words) * w.sample_stride_words, 8, 8);
+    bool ok = v.Hash(w.outs[slot], w.out_words, w.sample_stride_words) == want.sampled;
+    if (w.full_hash_cheap && w.sample_stride_words != 8) ok = ok && v.Hash(w.outs[slot], w.out_words, 8) == want.full;
+    if (!w.keys) v.Poison(w.outs[slot], w.out_words, w.sample_stride_words);      // the sort's input is restored by its own command
+    return ok;
+}
+
+static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool> *ready, double duration_s) {
+    LpResult r;
+    Verifier v;
+    v.Init();
+    const LpExpect want = StraightRun(q, w, v);
+    r.want = want.full;
+    for (void *o : w.outs) if (!w.keys) v.Poison(o, w.out_words, w.sample_stride_words);
+
     auto submit = [&](size_t slot) {
         if (w.keys) {                                   // sort: restore the unsorted input first
             HwCommandHandle c;
@@ -232,7 +338,8 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
         XK(XQueueSubmit(q.xq, c));
     };
     const size_t depth = w.tasks.size();
-    std::vector<uint64_t> uses(depth, 0);
+    std::vector<uint64_t> uses(depth, 0), preempt_seen(depth, 0);
+    std::vector<bool> unchecked(depth, false);
     // A task object may be re-submitted only after its previous command completed.  That is read from
     // the task's mailbox (no queue drain).  A preempted command is launched more than once, so the launch
     // count alone does not tell which submission a COMPLETED status belongs to: the slot remembers the
@@ -240,13 +347,30 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
     // the task reports COMPLETED at a larger count (a completed task is not launched again before it is
     // re-submitted).
     std::vector<uint64_t> seen_complete_at(depth, 0);
-    for (size_t i = 0; i < depth; ++i) { xpkTaskInfo info; PK(xpkTaskQuery(w.tasks[i], &info)); seen_complete_at[i] = info.launches; }
+    for (size_t i = 0; i < depth; ++i) { xpkTaskInfo info; PK(xpkTaskQuery(w.tasks[i], &info)); seen_complete_at[i] = info.launches; preempt_seen[i] = info.preemptions; }
+    uint64_t checked = 0;
+    // Every completed iteration is checked before its buffer is handed out again: the output must hash to the
+    // straight run's, and it was spoiled before the iteration, so a tile the iteration (or the replay after a
+    // preemption) never wrote shows.
+    auto check_slot = [&](size_t slot) {
+        if (!unchecked[slot]) return;
+        xpkTaskInfo info;
+        PK(xpkTaskQuery(w.tasks[slot], &info));
+        const bool was_preempted = info.preemptions != preempt_seen[slot];
+        preempt_seen[slot] = info.preemptions;
+        const bool ok = CheckSlot(w, v, slot, want, a.tamper_at >= 0 && checked == (uint64_t)a.tamper_at);
+        ++checked;
+        ++r.verified_iters;
+        if (was_preempted) ++r.verified_preempted_iters;
+        if (!ok) ++r.mismatched_iters;
+        unchecked[slot] = false;
+    };
     auto wait_slot = [&](size_t slot) {
         if (uses[slot] == 0) return;
         while (!g_stop.load()) {
             xpkTaskInfo info;
             PK(xpkTaskQuery(w.tasks[slot], &info));
-            if (info.launches > seen_complete_at[slot] && info.status == XPK_STATUS_COMPLETED) { seen_complete_at[slot] = info.launches; return; }
+            if (info.launches > seen_complete_at[slot] && info.status == XPK_STATUS_COMPLETED) { seen_complete_at[slot] = info.launches; check_slot(slot); return; }
             if (info.status == XPK_STATUS_ERROR) { std::fprintf(stderr, "task error %#x\n", info.error); std::exit(7); }
             SleepUs(20);
         }
@@ -275,6 +399,7 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
         wait_slot(slot);
         if (g_stop.load()) break;
         submit(slot);
+        unchecked[slot] = true;
         ++uses[slot];
         ++submitted;
     }
@@ -282,18 +407,23 @@ static LpResult RunLp(const Args &a, const Queue &q, LpWork &w, std::atomic<bool
     r.seconds = t_begin ? ((t_frozen ? t_frozen : NowNs()) - t_begin) / 1e9 : 0;
     r.iters = (t_frozen ? frozen_at : submitted) - counted_from;
     r.rate = r.seconds > 0 ? r.iters * w.work_per_iter / r.seconds : 0;
-    r.got = DeviceChecksum(w.out, w.out_words, q.stream);
+    // The iterations still unchecked (at most one per slot), then a whole-buffer hash of the newest output.
+    const size_t last = submitted ? (submitted - 1) % depth : 0;
+    r.got = submitted ? v.Hash(w.outs[last], w.out_words, 8) : want.full;
+    for (size_t i = 0; i < depth; ++i) check_slot(i);
     for (auto t : w.tasks) { xpkTaskInfo info; PK(xpkTaskQuery(t, &info)); r.preemptions += info.preemptions; }
     CudaQueueGetStats(q.hwq, &r.stats);
     return r;
 }
+static bool LpOk(const LpResult &r) { return r.want == r.got && r.mismatched_iters == 0; }
 
 static void PrintLp(const Args &a, const LpWork &w, const LpResult &r) {
     const double scale = std::strcmp(w.unit, "TFLOP/s") == 0 ? 1e12 : 1e9;
     std::printf("{\"role\": \"lp\", \"kernel\": \"%s\", \"level\": %d, \"iters\": %" PRIu64 ", \"seconds\": %.4f, \"rate\": %.3f, \"unit\": \"%s\", "
-                "\"bit_exact\": %s, \"checksum\": \"%llx\", \"deactivations\": %" PRIu64 ", \"relaunches\": %" PRIu64 ", \"launched\": %" PRIu64 ", "
-                "\"xpk_launches\": %" PRIu64 "}\n",
-                a.kernel.c_str(), a.level, r.iters, r.seconds, r.rate / scale, w.unit, r.want == r.got ? "true" : "false", r.got,
+                "\"bit_exact\": %s, \"checksum\": \"%llx\", \"verified_iters\": %" PRIu64 ", \"verified_preempted_iters\": %" PRIu64 ", \"mismatched_iters\": %" PRIu64 ", "
+                "\"deactivations\": %" PRIu64 ", \"relaunches\": %" PRIu64 ", \"launched\": %" PRIu64 ", \"xpk_launches\": %" PRIu64 "}\n",
+                a.kernel.c_str(), a.level, r.iters, r.seconds, r.rate / scale, w.unit, LpOk(r) ? "true" : "false", r.got,
+                r.verified_iters, r.verified_preempted_iters, r.mismatched_iters,
                 (uint64_t)r.stats.deactivations, (uint64_t)r.stats.relaunches, (uint64_t)r.stats.launched, (uint64_t)xpkLaunchCount());
     std::fflush(stdout);
 }
@@ -353,7 +483,9 @@ static HpWork BuildHp(const Args &a, const Queue &q) {
     return w;
 }
 
-static double HpOnce(const Queue &q, HpWork &w) {
+static double HpOnce(const Queue &q, HpWork &w, uint64_t index = 0) {
+    const bool trace = XTraceEnabled() != 0;
+    if (trace) XTraceStamp(xsched::utils::kTraceAppSubmit, index, 0);
     const int64_t t0 = NowNs();
     HwCommandHandle c;
     if (w.e2e || w.keys) { XK(HwCommandCreateCallback(&c, HpCopyIn, &w)); XK(XQueueSubmit(q.xq, c)); }
@@ -361,7 +493,13 @@ static double HpOnce(const Queue &q, HpWork &w) {
     XK(XQueueSubmit(q.xq, c));
     if (w.e2e && !w.keys) { XK(HwCommandCreateCallback(&c, HpCopyOut, &w)); XK(XQueueSubmit(q.xq, c)); }
     XK(XQueueWaitAll(q.xq));
-    return (NowNs() - t0) / 1e3;
+    const double us = (NowNs() - t0) / 1e3;
+    if (trace) {
+        XTraceStamp(xsched::utils::kTraceAppDone, index, 0);
+        uint64_t start_ns = 0, exit_ns = 0;
+        if (xpkTaskTimes(w.task, &start_ns, &exit_ns) == XPK_SUCCESS) XTraceStamp(xsched::utils::kTraceAppGpuTimes, start_ns, exit_ns);
+    }
+    return us;
 }
 
 struct HpResult { std::vector<double> lat_us; double seconds = 0; };
@@ -379,7 +517,7 @@ static HpResult RunHp(const Args &a, const Queue &q, HpWork &w, int count, std::
             const int64_t left = next - NowNs();
             if (left > 200000) SleepUs(left / 2000); else std::this_thread::yield();
         }
-        r.lat_us.push_back(HpOnce(q, w));
+        r.lat_us.push_back(HpOnce(q, w, (uint64_t)i + 1));
         if (NowNs() > next + a.period_us * 1000) next = NowNs();      // overrun: do not accumulate a backlog
     }
     r.seconds = (NowNs() - t_begin) / 1e9;
@@ -423,19 +561,40 @@ static int PreemptLatency(const Args &a) {
     Queue q = MakeQueue(a, a.level, 0);
     Args la = a;
     LpWork w = BuildLp(la, q, 0);
+    Verifier v;
+    v.Init();
+    const LpExpect want = StraightRun(q, w, v);
+    for (void *o : w.outs) if (!w.keys) v.Poison(o, w.out_words, w.sample_stride_words);
     std::atomic<bool> stop{false};
+    std::atomic<uint64_t> rounds_checked{0}, mismatches{0}, preempted_checked{0};
     std::thread bg([&] {
         CK(cudaSetDevice(a.device));
         size_t i = 0;
         const size_t depth = w.tasks.size();
+        std::vector<uint64_t> preempt_seen(depth, 0);
+        // Rounds of `depth` submissions; after each round every output is compared with the straight run's
+        // (each was spoiled before the round) and spoiled again.
+        auto check_round = [&](size_t used) {
+            for (size_t sl = 0; sl < used; ++sl) {
+                xpkTaskInfo info;
+                PK(xpkTaskQuery(w.tasks[sl], &info));
+                if (info.preemptions != preempt_seen[sl]) preempted_checked.fetch_add(1);
+                preempt_seen[sl] = info.preemptions;
+                const bool tamper = a.tamper_at >= 0 && rounds_checked.load() == (uint64_t)a.tamper_at && sl == 0;
+                if (!CheckSlot(w, v, sl, want, tamper)) mismatches.fetch_add(1);
+            }
+            rounds_checked.fetch_add(1);
+        };
         while (!stop.load()) {
-            if (i && i % depth == 0) XK(XQueueWaitAll(q.xq));
+            if (i && i % depth == 0) { XK(XQueueWaitAll(q.xq)); check_round(depth); }
+            if (w.keys) { HwCommandHandle c; XK(HwCommandCreateCallback(&c, RestoreKeys, &w)); XK(XQueueSubmit(q.xq, c)); }
             HwCommandHandle c;
             XK(CudaXpkCommandCreate(&c, w.tasks[i % depth], 1));
             XK(XQueueSubmit(q.xq, c));
             ++i;
         }
         XK(XQueueWaitAll(q.xq));
+        check_round(i % depth == 0 ? depth : i % depth);
     });
     SleepUs(300000);
     std::mt19937 rng((unsigned)a.seed);
@@ -452,20 +611,18 @@ static int PreemptLatency(const Args &a) {
     }
     stop.store(true);
     bg.join();
-    const unsigned long long got = DeviceChecksum(w.out, w.out_words, q.stream);
-    PK(xpkTaskReset(w.tasks[0], q.stream));
-    PK(xpkTaskLaunch(w.tasks[0], q.stream, 0));
-    CK(cudaStreamSynchronize(q.stream));
-    const unsigned long long want = DeviceChecksum(w.out, w.out_words, q.stream);
     CudaQueueStats st{};
     CudaQueueGetStats(q.hwq, &st);
+    const bool ok = mismatches.load() == 0 && rounds_checked.load() > 0;
     std::printf("{\"role\": \"preempt-latency\", \"kernel\": \"%s\", \"level\": %d, \"abort\": %d, \"n\": %zu, \"preempt_avg_us\": %.2f, \"preempt_p50_us\": %.2f, "
                 "\"preempt_p95_us\": %.2f, \"preempt_p99_us\": %.2f, \"preempt_max_us\": %.2f, \"resume_avg_us\": %.2f, \"resume_p99_us\": %.2f, "
-                "\"bit_exact\": %s, \"deactivations\": %" PRIu64 ", \"relaunches\": %" PRIu64 "}\n",
+                "\"bit_exact\": %s, \"rounds_checked\": %" PRIu64 ", \"preempted_outputs_checked\": %" PRIu64 ", \"mismatched_outputs\": %" PRIu64 ", "
+                "\"deactivations\": %" PRIu64 ", \"relaunches\": %" PRIu64 ", \"xpk_launches\": %" PRIu64 "}\n",
                 a.kernel.c_str(), a.level, a.abort_inflight, pre.size(), std::accumulate(pre.begin(), pre.end(), 0.0) / std::max<size_t>(1, pre.size()),
                 Pct(pre, 0.5), Pct(pre, 0.95), Pct(pre, 0.99), Pct(pre, 1.0), std::accumulate(res.begin(), res.end(), 0.0) / std::max<size_t>(1, res.size()),
-                Pct(res, 0.99), got == want ? "true" : "false", (uint64_t)st.deactivations, (uint64_t)st.relaunches);
-    return 0;
+                Pct(res, 0.99), ok ? "true" : "false", rounds_checked.load(), preempted_checked.load(), mismatches.load(),
+                (uint64_t)st.deactivations, (uint64_t)st.relaunches, (uint64_t)xpkLaunchCount());
+    return ok ? 0 : 6;
 }
 
 #include <numeric>
@@ -586,6 +743,37 @@ static int NativePriority(const Args &a) {
     return 0;
 }
 
+// ---- control arms: what a second process costs the high-priority one when nothing is ever preempted -------
+// idle: the process owns a context, the GEMM's buffers and a level-2 queue, and never launches anything.
+static int IdleContext(const Args &a) {
+    Queue q = MakeQueue(a, a.level, 0);
+    LpWork w = BuildLp(a, q, 0);
+    (void)w;
+    std::printf("READY\n"); std::fflush(stdout);
+    while (!g_stop.load()) SleepUs(2000);
+    std::printf("{\"role\": \"idle\"}\n");
+    return 0;
+}
+// spin-lp: sleep kernels of --kernel-us, two in flight, on a plain stream outside XSched.
+static int SpinLp(const Args &a) {
+    cudaStream_t s;
+    CK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    cudaEvent_t ev[2];
+    CK(cudaEventCreateWithFlags(&ev[0], cudaEventDisableTiming)); CK(cudaEventCreateWithFlags(&ev[1], cudaEventDisableTiming));
+    std::printf("READY\n"); std::fflush(stdout);
+    uint64_t i = 0;
+    const int64_t t0 = NowNs();
+    while (!g_stop.load()) {
+        if (i >= 2) CK(cudaEventSynchronize(ev[i & 1]));
+        SleepKernel<<<64, 64, 0, s>>>((long long)a.kernel_us * 1000);
+        CK(cudaEventRecord(ev[i & 1], s));
+        ++i;
+    }
+    CK(cudaStreamSynchronize(s));
+    std::printf("{\"role\": \"spin-lp\", \"kernel_us\": %lld, \"kernels\": %" PRIu64 ", \"seconds\": %.3f}\n", (long long)a.kernel_us, i, (NowNs() - t0) / 1e9);
+    return 0;
+}
+
 int main(int argc, char **argv) {
     Args a = Parse(argc, argv);
     std::signal(SIGUSR1, OnMark);
@@ -594,6 +782,9 @@ int main(int argc, char **argv) {
     CK(cudaSetDevice(a.device));
     CK(cudaFree(0));
     prctl(PR_SET_TIMERSLACK, 1000UL, 0, 0, 0);
+    CalibrateGpuClock();
+    if (a.role == "idle") return IdleContext(a);
+    if (a.role == "spin-lp") return SpinLp(a);
     if (a.role == "preempt-latency") return PreemptLatency(a);
     if (a.role == "native-priority") return NativePriority(a);
     if (a.role == "level-sweep") return LevelSweep(a);
@@ -602,7 +793,7 @@ int main(int argc, char **argv) {
         LpWork w = BuildLp(a, q, 0);
         LpResult r = RunLp(a, q, w, nullptr, a.duration_s);
         PrintLp(a, w, r);
-        return r.want == r.got ? 0 : 6;
+        return LpOk(r) ? 0 : 6;
     }
     if (a.role == "hp") {
         Queue q = MakeQueue(a, a.level, a.prio);
@@ -627,7 +818,7 @@ int main(int argc, char **argv) {
         lp.join();
         PrintHp(a, hw, hr, VerifyHp(qh, hw));
         PrintLp(a, lw, lr);
-        return lr.want == lr.got ? 0 : 6;
+        return LpOk(lr) ? 0 : 6;
     }
     std::fprintf(stderr, "unknown --role %s\n", a.role.c_str());
     return 2;

@@ -17,6 +17,8 @@
 #include "xsched/preempt/hal/hw_queue.h"
 #include "xsched/preempt/xqueue/xqueue.h"
 #include "xsched/protocol/names.h"
+#include "xsched/utils/trace.h"
+#include "xsched_b200/pk.h"
 #include "xsched/utils/xassert.h"
 
 namespace xsched::cuda {
@@ -112,13 +114,14 @@ public:
         }
         counter_->Wait(t);
         const int64_t t0 = deactivate_ns_.exchange(0);
-        if (t0) stats_.last_preempt_ns.store((uint64_t)(NowNs() - t0));
+        if (t0) { stats_.last_preempt_ns.store((uint64_t)(NowNs() - t0)); XTRACE(utils::kTraceHwqSynced, GetHandle()); }
     }
 
     void Deactivate() override {
         ContextScope scope(ctx_);
         deactivate_ns_.store(NowNs());
         CUDA_ASSERT(Driver().cuStreamWriteValue32(ctrl_, flag_, 1, CU_STREAM_WRITE_VALUE_DEFAULT));
+        XTRACE(utils::kTraceDeactivateIssued, GetHandle());
         stats_.deactivations.fetch_add(1, std::memory_order_relaxed);
     }
 
@@ -138,6 +141,10 @@ public:
                 replay = true;                            // first unfinished preemptible command
             } else if (x && x->TaskCompleted()) {
                 continue;
+            }
+            if (x && utils::TraceEnabled()) {
+                uint64_t start_ns = 0, exit_ns = 0;         // device stamps of the launch that was flushed
+                if (xpkTaskTimes((xpkTask_t)x->Task(), &start_ns, &exit_ns) == XPK_SUCCESS) XTRACE(utils::kTraceTaskGpuTimes, start_ns, exit_ns);
             }
             LaunchAndNote(c);
             stats_.relaunches.fetch_add(1, std::memory_order_relaxed);

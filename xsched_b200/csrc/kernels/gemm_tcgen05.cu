@@ -135,12 +135,6 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
 // Instruction descriptor for kind::f16: D fp32, A/B bf16, both K-major, N=256, M=128.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kMmaM >> 4) << 24);
 
-__device__ __forceinline__ unsigned long long gemm_time_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
 // Bounded wait.  `quit()` is evaluated between polls; returns false when it fired or on timeout.
 template <class Quit>
 __device__ __forceinline__ bool bounded_wait(void *bar, uint32_t parity, GemmShared *sh, Ctl *ctl,
@@ -150,7 +144,7 @@ __device__ __forceinline__ bool bounded_wait(void *bar, uint32_t parity, GemmSha
     while (!mbar_try_wait(bar, parity)) {
         if (quit()) return false;
         if ((++it & 0xFFu) == 0) {
-            const unsigned long long now = gemm_time_ns();
+            const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
             else if (now - t0 > kWaitLimitNs) {
                 raise_error(ctl, errcode);
@@ -187,6 +181,7 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
     const uint32_t k_blocks = K / kBK;
     const unsigned long long total_tiles = (unsigned long long)m_tiles * n_tiles;
     volatile uint32_t *v_abort = &sh->abort;
+    note_start(ctl);
 
     if constexpr (kPreemptible) {
         // A kernel that starts with the flag already raised (it was queued behind the one being flushed)

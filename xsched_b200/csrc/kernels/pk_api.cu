@@ -407,6 +407,16 @@ xpkResult xpkTaskWait(xpkTask_t t, uint64_t timeout_us, xpkTaskInfo *info) {
     return st == XPK_STATUS_ERROR ? XPK_ERR_DEVICE_TIMEOUT : XPK_SUCCESS;
 }
 
+xpkResult xpkTaskTimes(xpkTask_t t, uint64_t *start_ns, uint64_t *exit_ns) {
+    if (!t || !start_ns || !exit_ns) return XPK_ERR_INVALID_VALUE;
+    volatile Mailbox *m = t->mb_host;
+    if (m->seq == 0) return XPK_ERR_BUSY;
+    std::atomic_thread_fence(std::memory_order_acquire);
+    *start_ns = m->start_ns;
+    *exit_ns = m->exit_ns;
+    return XPK_SUCCESS;
+}
+
 xpkResult xpkTaskReset(xpkTask_t t, void *stream) {
     if (!t) return XPK_ERR_INVALID_VALUE;
     DeviceGuard on_task_device(t->device);

@@ -40,7 +40,9 @@ struct Mailbox {
     uint32_t error;
     unsigned long long preemptions;
     unsigned long long seq;          // == launch number once the fields above are valid
-    unsigned long long pad[3];
+    unsigned long long start_ns;     // %globaltimer when the launch's first CTA started
+    unsigned long long exit_ns;      // %globaltimer when its last CTA left
+    unsigned long long pad[1];
 };
 static_assert(sizeof(Mailbox) == 64, "mailbox is one 64-byte line");
 
@@ -56,7 +58,7 @@ struct __align__(256) Ctl {
     uint32_t ctas_exited;
     uint32_t error;                  // first error code raised by any CTA (0 = none)
     uint32_t status;
-    uint32_t pad0[2];
+    unsigned long long start_ns;     // %globaltimer at the start of this launch's block 0 (for latency break-downs)
     // --- bytes [64,192): kernel-specific persistent words (radix sort phase counters);
     //     cleared by a task reset ---
     unsigned long long user[16];
@@ -69,10 +71,21 @@ struct __align__(256) Ctl {
     unsigned long long returned[2][kMaxReturned];
 };
 constexpr size_t kCtlResetBytes = 192;
-static_assert(offsetof(Ctl, user) == 64 && offsetof(Ctl, total) == 192, "Ctl layout");
+static_assert(offsetof(Ctl, start_ns) == 56 && offsetof(Ctl, user) == 64 && offsetof(Ctl, total) == 192, "Ctl layout");
 static_assert(offsetof(Ctl, returned) == 256, "Ctl layout");
 
 constexpr unsigned long long kNoTile = ~0ull;
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// First statement of every kernel: block 0 notes when the launch began to run.
+__device__ __forceinline__ void note_start(Ctl *ctl) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) ctl->start_ns = global_ns();
+}
 
 __device__ __forceinline__ uint32_t ld_flag(const uint32_t *p) {
     uint32_t v;
@@ -154,6 +167,8 @@ __device__ __forceinline__ void cta_exit(Ctl *ctl, unsigned long long done_by_ct
         m->status = st;
         m->error = err;
         m->preemptions = v->preemptions;
+        m->start_ns = v->start_ns;
+        m->exit_ns = global_ns();
         __threadfence_system();
         m->seq = launch_no;
         __threadfence_system();

@@ -60,11 +60,6 @@ struct SortSmem {
     uint32_t bail;
 };
 
-__device__ __forceinline__ unsigned long long gtime_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ uint32_t ld_relaxed(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -124,13 +119,13 @@ __device__ __forceinline__ uint32_t block_excl_scan256(uint32_t v, SortSmem &sm,
 __device__ __forceinline__ bool wait_counter(Ctl *ctl, const unsigned long long *counter,
                                              unsigned long long target, uint32_t code) {
     if (ld_acquire64(counter) >= target) return true;
-    const unsigned long long t0 = gtime_ns();
+    const unsigned long long t0 = global_ns();
     uint32_t it = 0;
     while (ld_acquire64(counter) < target) {
         __nanosleep(64);
         if ((++it & 255u) == 0) {
             if (ld_relaxed(&ctl->error) != 0) return false;
-            if (gtime_ns() - t0 > kSpinLimitNs) { raise_error(ctl, code); return false; }
+            if (global_ns() - t0 > kSpinLimitNs) { raise_error(ctl, code); return false; }
         }
     }
     return true;
@@ -154,6 +149,7 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     unsigned long long *phase_done = ctl->user;       // [0..4]
     unsigned long long done = 0;
+    note_start(ctl);
 
     while (true) {
         if (tid == 0) {
@@ -250,7 +246,7 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
                 bool ok = true;
                 if (j > 0) {
                     long long k = (long long)j - 1;
-                    const unsigned long long t0 = gtime_ns();
+                    const unsigned long long t0 = global_ns();
                     uint32_t it = 0;
                     while (true) {
                         const uint32_t s = ld_relaxed(state + ((unsigned long long)pass * T + k) * kRadix + tid);
@@ -259,7 +255,7 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
                             __nanosleep(32);
                             if ((++it & 255u) == 0) {
                                 if (ld_relaxed(&ctl->error) != 0) { ok = false; break; }
-                                if (gtime_ns() - t0 > kSpinLimitNs) { raise_error(ctl, kErrSortLookback); ok = false; break; }
+                                if (global_ns() - t0 > kSpinLimitNs) { raise_error(ctl, kErrSortLookback); ok = false; break; }
                             }
                             continue;
                         }

@@ -82,6 +82,7 @@ stream_kernel(Ctl *ctl, float *__restrict__ out, const float *__restrict__ x,
               const float *__restrict__ y, float s, unsigned long long n,
               unsigned long long tile_elems, unsigned long long launch_no) {
     unsigned long long done = 0;
+    note_start(ctl);
     if constexpr (kPreemptible) {
         __shared__ unsigned long long s_tile;
         while (true) {

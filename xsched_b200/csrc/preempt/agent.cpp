@@ -14,6 +14,7 @@
 #include "xsched/preempt/xqueue/xqueue.h"
 #include "xsched/protocol/def.h"
 #include "xsched/protocol/names.h"
+#include "xsched/utils/trace.h"
 #include "xsched/utils/xassert.h"
 
 namespace xsched::preempt {
@@ -122,6 +123,7 @@ XResult SchedAgent::ReplaceScheduler(XSchedulerType scheduler, XPolicyType polic
 void SchedAgent::Execute(const Operation &op) {
     const OperationMeta &m = op.Meta();
     XASSERT(m.pid == (int32_t)GetProcessId(), "operation " FMT_64U " for process %d delivered to process %d", m.id, m.pid, GetProcessId());
+    XTRACE(utils::kTraceOpRecv, m.id, (uint64_t)m.type);
     if (g_executing.load()) {
         if (m.type == kOperationSched) {
             const OpSchedHeader &h = *reinterpret_cast<const OpSchedHeader *>(op.bytes.data());

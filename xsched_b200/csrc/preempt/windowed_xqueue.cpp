@@ -4,6 +4,7 @@
 
 #include "xsched/preempt/sched/agent.h"
 #include "xsched/sched/wire.h"
+#include "xsched/utils/trace.h"
 #include "xsched/utils/xassert.h"
 
 namespace xsched::preempt {
@@ -55,7 +56,7 @@ void WindowedXQueue::Enqueue(std::shared_ptr<XCommand> cmd) {
         pending_.push_back(std::move(cmd));
     }
     q_cv_.notify_all();
-    if (became_ready) SchedAgent::SendEvent(Event::XQueueReady(kHandle, ready_us));
+    if (became_ready) { SchedAgent::SendEvent(Event::XQueueReady(kHandle, ready_us)); XTRACE(utils::kTraceReadySent, kHandle); }
 }
 
 // Next pending command.  With nothing pending: returns nullptr when `block_when_empty` is false;
@@ -74,6 +75,7 @@ std::shared_ptr<XCommand> WindowedXQueue::TakeOrIdle(bool block_when_empty) {
             lk.unlock();
             idle_cv_.notify_all();
             SchedAgent::SendEvent(Event::XQueueIdle(kHandle));
+            XTRACE(utils::kTraceIdleSent, kHandle);
             lk.lock();
         }
         q_cv_.wait(lk, [this] { return !pending_.empty(); });
@@ -330,6 +332,7 @@ void WindowedXQueue::Suspend(int64_t flags) {
     std::lock_guard<std::mutex> serial(suspend_mu_);
     bool expected = false;
     if (!suspended_.compare_exchange_strong(expected, true)) return;     // re-entrant
+    XTRACE(utils::kTraceSuspendBegin, kHandle);
 
     if (flags & kQueueSuspendFlagWaitIdle) WaitForNextIdle();
     else if (flags & kQueueSuspendFlagWaitAll) WaitAll();
@@ -342,16 +345,19 @@ void WindowedXQueue::Suspend(int64_t flags) {
     if (level_ >= kPreemptLevelDeactivate) kHwQueue->Deactivate();
     if (level_ >= kPreemptLevelInterrupt) kHwQueue->Interrupt();
     if (flags & kQueueSuspendFlagSyncHwQueue) kHwQueue->Synchronize();
+    XTRACE(utils::kTraceSuspendEnd, kHandle);
 }
 
 void WindowedXQueue::Resume(int64_t flags) {
     std::lock_guard<std::mutex> serial(suspend_mu_);
     bool expected = true;
     if (!suspended_.compare_exchange_strong(expected, false)) return;
+    XTRACE(utils::kTraceResumeBegin, kHandle);
 
     auto unpause = [this] {
         { std::lock_guard<std::mutex> lk(w_mu_); paused_ = false; }
         w_cv_.notify_all();
+        XTRACE(utils::kTraceResumeEnd, kHandle);
     };
 
     if (level_ == kPreemptLevelBlock) {

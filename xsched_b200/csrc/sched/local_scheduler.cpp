@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <chrono>
 #include "xsched/protocol/names.h"
+#include "xsched/utils/trace.h"
 #include "xsched/utils/xassert.h"
 
 namespace xsched::sched {
@@ -237,6 +238,7 @@ void LocalScheduler::Apply(const Event &e) {
 void LocalScheduler::Decide() {
     decision_.Clear();
     policy_->Sched(status_, Now(), decision_);
+    XTRACE(utils::kTraceDecision, decision_.suspend.size() + decision_.resume.size() + decision_.ordered.size());
 
     auto move = [this](XQueueHandle h, bool to_suspended) {
         auto qit = status_.xqueues.find(h);
@@ -265,6 +267,7 @@ void LocalScheduler::Decide() {
         }
         Execute(Operation::Sched(id, pid, std::vector<uint64_t>(p.running.begin(), p.running.end()),
                                  std::vector<uint64_t>(p.suspended.begin(), p.suspended.end())));
+        XTRACE(utils::kTraceOpSent, (uint64_t)pid, id);
     }
     dirty_.clear();
 

@@ -30,6 +30,7 @@
 #include "xsched/protocol/names.h"
 #include "xsched/sched/ipc.h"
 #include "xsched/sched/scheduler.h"
+#include "xsched/utils/trace.h"
 #include "xsched/utils/xassert.h"
 
 using namespace xsched::sched;
@@ -80,6 +81,7 @@ public:
                     if (n <= 0) { g_stop.store(true); break; }
                     Event e;
                     if (!e.Assign(buf, (size_t)n)) continue;
+                    XTRACE(xsched::utils::kTraceEventRecv, (uint64_t)e.Type(), (uint64_t)e.Pid());
                     if (e.Type() == kEventProcessCreate) Track(e.Pid());
                     if (e.Type() == kEventProcessDestroy) Untrack(e.Pid());
                     batch.push_back(e);
@@ -102,6 +104,7 @@ public:
                 if (n <= 0) break;
                 Event e;
                 if (!e.Assign(buf, (size_t)n)) { XWARN("malformed event of %ld bytes dropped", n); continue; }
+                XTRACE(xsched::utils::kTraceEventRecv, (uint64_t)e.Type(), (uint64_t)e.Pid());
                 if (e.Type() == kEventProcessCreate) Track(e.Pid());
                 if (e.Type() == kEventProcessDestroy) Untrack(e.Pid());
                 if (e.Type() == kEventSchedulerTerminate) continue;      // clients cannot stop the server

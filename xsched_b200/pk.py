@@ -26,7 +26,7 @@ EXPORTS = [
     "xpkDeviceSmCount", "xpkResultString", "xpkFlagCreate", "xpkFlagDestroy", "xpkFlagSet",
     "xpkTaskCreateTriad", "xpkTaskCreateVecAdd", "xpkSortScratchBytes", "xpkTaskCreateSort",
     "xpkTaskCreateGemm", "xpkTaskLaunch", "xpkTaskQuery", "xpkTaskWait", "xpkTaskReset",
-    "xpkTaskFlag", "xpkTaskKind", "xpkTaskDestroy", "xpkLaunchCount", "xpkSortNoAlloc",
+    "xpkTaskFlag", "xpkTaskKind", "xpkTaskDestroy", "xpkLaunchCount", "xpkSortNoAlloc", "xpkTaskTimes",
 ]
 
 
@@ -52,6 +52,7 @@ lib.xpkTaskLaunch.argtypes = [_vp, _vp, C.c_int]
 lib.xpkTaskQuery.argtypes = [_vp, C.POINTER(TaskInfo)]
 lib.xpkTaskWait.argtypes = [_vp, _u64, C.POINTER(TaskInfo)]
 lib.xpkTaskReset.argtypes = [_vp, _vp]
+lib.xpkTaskTimes.argtypes = [_vp, C.POINTER(_u64), C.POINTER(_u64)]
 lib.xpkTaskFlag.argtypes = [_vp, C.POINTER(_vp)]
 lib.xpkTaskKind.argtypes = [_vp, C.POINTER(_u32)]
 lib.xpkTaskDestroy.argtypes = [_vp]
