@@ -4,8 +4,9 @@
 Workload (`config.workload` = "gemm8192_vs_vecadd64M"): a low-priority process runs a persistent,
 preemptible bf16 GEMM (M=N=K=8192, A,B ~ N(0,1), fp32 accumulate) in a loop through a level-2 XQueue;
 a high-priority process issues an fp32 vector add over 64 Mi elements ~ U(-1,1) every 10 ms through
-its own XQueue; one xserver with the HPF policy schedules both.  One "step" is one high-priority
-request.  Reported:
+its own XQueue; one xserver with the HPF policy schedules both.  One "step" is a batch of 100 high-priority
+requests (one second of the 10 ms arrival period), so that the default 20 steps give 2000 co-run samples and
+the P99 is a percentile rather than a maximum.  Reported:
 
   value              P99 latency of the high-priority request while co-running / its P99 standalone
                      (lower is better; inputs resident in HBM)
@@ -40,7 +41,8 @@ REF_DRIVER = ROOT / "oracle" / "_ref" / "lane_driver_ref"
 GEMM = dict(M=8192, N=8192, K=8192)
 HP_N = 1 << 26
 PERIOD_US = 10_000
-E2E_PERIOD_US = 60_000
+E2E_PERIOD_US = 40_000
+REQS_PER_STEP = 100          # high-priority requests per step
 
 
 def peaks() -> dict:
@@ -174,6 +176,17 @@ def pct(values: list[float], p: float) -> float:
     return v[min(len(v) - 1, int(p * (len(v) - 1) + 0.5))] if v else float("nan")
 
 
+def ratio_interval(co: list[float], alone: list[float], p: float = 0.99, rounds: int = 400, seed: int = 12345) -> list[float] | None:
+    """95 % bootstrap interval of pct(co, p) / pct(alone, p): both sample sets resampled with replacement."""
+    if len(co) < 50 or len(alone) < 50:
+        return None
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    a, b = np.asarray(co), np.asarray(alone)
+    r = [np.quantile(rng.choice(a, a.size), p, method="nearest") / np.quantile(rng.choice(b, b.size), p, method="nearest") for _ in range(rounds)]
+    return [round(float(np.quantile(r, 0.025)), 4), round(float(np.quantile(r, 0.975)), 4)]
+
+
 def base_env(ns: str, sched: str | None) -> dict:
     env = dict(os.environ, XLOG_LEVEL="WARN", XSCHED_IPC_NAMESPACE=ns, XSCHED_IPC_SPIN="ON")
     env.pop("XSCHED_POLICY", None)
@@ -184,10 +197,12 @@ def base_env(ns: str, sched: str | None) -> dict:
     return env
 
 
-def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, period_us: int, lp_kw: dict) -> tuple[dict, dict]:
-    """LP process + HP process under the (already running) xserver.  Returns (hp_json, lp_json)."""
+def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, period_us: int, lp_kw: dict,
+          extra_env: dict | None = None) -> tuple[dict, dict]:
+    """LP process + HP process under the (already running) xserver; `steps` timed and `warmup` untimed
+    high-priority requests.  Returns (hp_json, lp_json)."""
     import tempfile
-    env = base_env(ns, "GLB")
+    env = dict(base_env(ns, "GLB"), **(extra_env or {}))
     hp_env = dict(env, XSCHED_IPC_SPIN="OFF")      # operations for the HP process are never urgent: do not burn a core on them
     lp_err = tempfile.TemporaryFile(mode="w+")
     lp = subprocess.Popen(worker_cmd("lp", device, level=level, prio=0, duration_s=3600, warmup_s=0.5, **lp_kw),
@@ -228,6 +243,146 @@ def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, 
     if not lp_json:
         raise RuntimeError("LP worker printed no result: " + lp_stderr_tail())
     return hp, lp_json[-1]
+
+
+# ---- per-stage timeline of one preemption (XSCHED_TRACE_FILE records of all three processes) ----------------
+def load_traces(prefix: str) -> dict[int, list[tuple[int, str, int, int]]]:
+    import glob
+    out: dict[int, list[tuple[int, str, int, int]]] = {}
+    for f in glob.glob(prefix + ".*"):
+        try:
+            pid = int(f.rsplit(".", 1)[1])
+        except ValueError:
+            continue
+        rows = []
+        with open(f) as fh:
+            for line in fh:
+                t = line.split()
+                if len(t) == 4:
+                    rows.append((int(t[0]), t[1], int(t[2]), int(t[3])))
+        rows.sort()
+        out[pid] = rows
+        os.unlink(f)
+    return out
+
+
+def _signed(v: int) -> int:
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def timeline_stages(traces: dict[int, list[tuple[int, str, int, int]]]) -> dict:
+    """Stage durations (us) of every high-priority request that caused a preemption, from the merged records:
+    submit -> ready event sent -> server received -> operation sent -> LP process received -> flag write issued
+    -> last CTA of the LP kernels left (device clock) -> first CTA of the HP kernel started (device clock)
+    -> HP kernel done (device clock) -> request complete on the host."""
+    import bisect
+    role = {}
+    for pid, rows in traces.items():
+        kinds = {r[1] for r in rows}
+        if "app_submit" in kinds:
+            role["hp"] = pid
+        elif "deactivate_issued" in kinds:
+            role["lp"] = pid
+        elif "event_recv" in kinds:
+            role["server"] = pid
+    if {"hp", "lp", "server"} - role.keys():
+        return {"error": f"trace files incomplete: roles found {sorted(role)}"}
+    hp, lp, srv = traces[role["hp"]], traces[role["lp"]], traces[role["server"]]
+
+    def offset(rows):
+        o = [_signed(r[2]) for r in rows if r[1] == "gpu_clock_offset"]
+        return o[0] if o else None
+    off_hp, off_lp = offset(hp), offset(lp)
+    if off_hp is None or off_lp is None:
+        return {"error": "no device clock calibration in the traces"}
+
+    def times(rows, kind, pred=lambda r: True):
+        return [r[0] for r in rows if r[1] == kind and pred(r)]
+
+    def first_after(ts, t):
+        i = bisect.bisect_left(ts, t)
+        return ts[i] if i < len(ts) else None
+    ready_sent = times(hp, "ready_sent")
+    ev_recv = times(srv, "event_recv", lambda r: r[3] == role["hp"])
+    op_sent_lp = times(srv, "op_sent", lambda r: r[2] == role["lp"])
+    op_recv = times(lp, "op_recv")
+    deact = times(lp, "deactivate_issued")
+    lp_exits = sorted(r[3] + off_lp for r in lp if r[1] == "task_gpu_times")      # last-CTA exits of flushed launches, host clock
+    submits = {r[2]: r[0] for r in hp if r[1] == "app_submit"}
+    dones = {r[2]: r[0] for r in hp if r[1] == "app_done"}
+    gpu = {}
+    idx = None
+    for r in hp:
+        if r[1] == "app_done":
+            idx = r[2]
+        elif r[1] == "app_gpu_times" and idx is not None:
+            gpu[idx] = (r[2] + off_hp, r[3] + off_hp)
+            idx = None
+    names = ["submit_to_ready_sent", "ready_sent_to_server_recv", "server_recv_to_op_sent", "op_sent_to_lp_recv", "lp_recv_to_flag_write_issued",
+             "flag_write_to_lp_last_cta_exit", "lp_last_cta_exit_to_hp_first_cta", "hp_kernel", "hp_kernel_end_to_host_done", "total"]
+    cols: dict[str, list[float]] = {n: [] for n in names}
+    used = 0
+    for i, t0 in sorted(submits.items()):
+        if i == 0 or i not in dones or i not in gpu:
+            continue
+        t_done = dones[i]
+        a = first_after(ready_sent, t0)
+        b = first_after(ev_recv, a) if a else None
+        c = first_after(op_sent_lp, b) if b else None
+        d = first_after(op_recv, c) if c else None
+        e = first_after(deact, d) if d else None
+        if None in (a, b, c, d, e) or e > t_done:
+            continue              # this request met an already idle GPU: nothing was preempted for it
+        g0, g1 = gpu[i]
+        lo = bisect.bisect_left(lp_exits, e - 20_000)
+        hi = bisect.bisect_right(lp_exits, t_done)
+        if lo >= hi:
+            continue
+        x = lp_exits[hi - 1]      # the last flushed launch to leave the GPU (a negative next stage = the HP kernel started beside it)
+        used += 1
+        for n, v in zip(names, [a - t0, b - a, c - b, d - c, e - d, x - e, g0 - x, g1 - g0, t_done - g1, t_done - t0]):
+            cols[n].append(v / 1e3)
+    if not used:
+        return {"error": "no request could be matched with a preemption in the traces"}
+    return {"requests_matched": used,
+            "stages_us": {n: {"p50": round(pct(v, 0.5), 1), "p99": round(pct(v, 0.99), 1)} for n, v in cols.items()},
+            "clock_note": "device stamps converted with a per-process offset calibrated to about 1 us"}
+
+
+def timeline_leg(device: int, ns: str, lp_kw: dict, requests: int = 300) -> dict:
+    """The headline co-run once more under its own xserver with stage stamps switched on in all three processes,
+    and two control arms in which nothing is ever preempted: the high-priority process beside a process that
+    only holds a context, and beside one that runs 10 us kernels back to back."""
+    import tempfile
+    prefix = tempfile.mktemp(prefix="xsched_trace_")
+    tns = ns + "tl."
+    tr_env = {"XSCHED_TRACE_FILE": prefix}
+    out: dict = {}
+    srv = subprocess.Popen([str(XSERVER), "HPF", "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=dict(base_env(tns, None), **tr_env))
+    srv.stdout.readline()
+    hp = None
+    try:
+        hp, lp = corun(device, tns, 2, requests, 20, False, PERIOD_US, lp_kw, extra_env=tr_env)
+    finally:
+        srv.send_signal(signal.SIGTERM)          # the server writes its records when it exits
+        try:
+            srv.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            srv.kill()
+        traces = load_traces(prefix)
+    out = timeline_stages(traces)
+    out["hp_p50_us"], out["hp_p99_us"], out["requests"] = hp["p50_us"], hp["p99_us"], requests
+    env_app = base_env(tns, "APP")
+    arms = {"beside_idle_context": worker_cmd("idle", device, level=2, **lp_kw),
+            "beside_10us_kernels": worker_cmd("spin-lp", device, kernel_us=10)}
+    for name, cmd in arms.items():
+        other, _ = start_lp(cmd, env_app, name)
+        try:
+            r = run_json(worker_cmd("hp", device, level=2, prio=1, count=requests, period_us=PERIOD_US, hp_n=HP_N), env_app, 120)[-1]
+            out[name] = {"hp_p50_us": r["p50_us"], "hp_p99_us": r["p99_us"]}
+        finally:
+            stop_lp(other, 60)
+    return out
 
 
 def find_real_driver() -> str | None:
@@ -358,7 +513,7 @@ def impl_reference(args) -> None:
     # Blackwell kernel to run (its CUDA level 2 stops at sm_86), so each GEMM launch becomes an 800 us
     # busy-spin command and each vector add a 160 us one, arriving every 10 ms, under the reference's stock
     # level-1 path (threshold/batch 16/8).  K steps = K high-priority arrivals.
-    steps = max(20, min(args.steps + args.warmup, 1500))
+    steps = max(200, min((args.steps + args.warmup) * REQS_PER_STEP, 3000))
     lp_us, hp_us, period_us = 800, 160, PERIOD_US
     lp_count = int(steps * period_us / lp_us)
     t0 = time.time()
@@ -367,9 +522,10 @@ def impl_reference(args) -> None:
     n = max(1, r["corun"]["n"])
     line = {
         "impl": "reference", "metric": "hp_p99_latency_vs_standalone", "value": round(r["p99_ratio"], 3), "unit": "x",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "hp_samples": n, "ms_per_step": round(wall * 1e3 / n, 3), "higher_is_better": False,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "hp_samples": n, "requests_per_step": REQS_PER_STEP,
+        "ms_per_step": round(wall * 1e3 / max(1, args.steps + args.warmup), 3), "higher_is_better": False,
         "scaling": "weak", "vs_baseline": None, "dtype": "n/a (host busy-spin commands)", "data": "synthetic",
-        "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "preempt_level": 1, "hp_period_us": period_us,
+        "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "preempt_level": 1, "hp_period_us": period_us, "hp_requests": n,
                    "replay": f"host-only lane: {lp_count} LP commands of {lp_us} us back-to-back, HP commands of {hp_us} us every {period_us} us, "
                              "reference core (LCL scheduler), threshold/batch 16/8"},
         "hp_p50_us": r["corun"]["p50_us"], "hp_p99_us": r["corun"]["p99_us"], "hp_standalone_p99_us": r["standalone"]["p99_us"],
@@ -419,14 +575,15 @@ def stop_lp(p, timeout: float = 120) -> dict:
     return js[-1] if js else {}
 
 
-def config4(args) -> None:
+def config4(args, ctx=None) -> dict | None:
     """Workload configuration 4 (8 GPUs, LLF): one xserver under the laxity policy (LLF) with per-device state; every GPU hosts four
     processes — a high-priority Llama-3-8B-shaped decode (unmodified PyTorch under the interposer, 20 ms deadline
     per decode step: laxity = 20 ms - standalone step time, relaxed priority 0, critical priority 1) and three
     low-priority level-2 loops (8192^3 bf16 GEMM, 2^31-element fp32 triad, 16 Mi-key int32 sort).  Weak scaling:
-    the same four processes per GPU at every N; no data-path collective.  Prints one JSON line."""
+    the same four processes per GPU at every N; no data-path collective.  Returns the result line on rank 0
+    (None elsewhere); every rank of the job must call it."""
     import tempfile
-    rank, world, local, pg = dist_ctx()
+    rank, world, local, pg = ctx if ctx is not None else dist_ctx()
     device = local
     ns = f"cfg4{os.environ.get('MASTER_PORT', os.getpid())}."
     policy = args.config4_policy
@@ -491,11 +648,10 @@ def config4(args) -> None:
         allr = [None] * world
         pg.all_gather_object(allr, res)
     if rank != 0:
-        return
+        return None
     bad = [r["error"] for r in allr if "error" in r]
     if bad:
-        print(json.dumps({"metric": "config4_deadline_miss_rate", "n_gpus": world, "error": bad[0], "ranks_failed": len(bad)}))
-        return
+        return {"metric": "config4_deadline_miss_rate", "n_gpus": world, "error": bad[0], "ranks_failed": len(bad)}
     toks = [x for r in allr for x in r["tok_ms"]]
     missed = sum(1 for x in toks if x > deadline_ms)
     def agg(kind: str, key: str) -> float:
@@ -519,14 +675,68 @@ def config4(args) -> None:
         "seconds": round(max(r["elapsed"] for r in allr), 2),
         "gpu_launches": int(sum(r[key][k].get("xpk_launches", 0) for r in allr for key in ("lp_alone", "lp_co") for k in ("gemm", "triad", "sort"))),
     }
-    print(json.dumps(line))
+    return line
+
+
+def profile_case(a) -> None:
+    """A few launches of one preemptible kernel with the CUDA-event time of each: the small, self-contained case the
+    ncu captures under profiles/ run.  Inputs are synthetic (seeded torch generators)."""
+    import torch
+    from xsched_b200 import pk
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    s = torch.cuda.current_stream().cuda_stream
+    restore = None
+    kernel = a.profile_case
+    if kernel == "gemm":
+        x = torch.randn(a.m, a.k, device="cuda", generator=g).to(torch.bfloat16)
+        y = torch.randn(a.n, a.k, device="cuda", generator=g).to(torch.bfloat16)
+        z = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        t = pk.Task.gemm(z, x, y, flags=a.flags)
+        work, unit = 2.0 * a.m * a.n * a.k / 1e12, "TFLOP/s"
+    elif kernel in ("triad", "vecadd"):
+        n = a.elems or ((1 << 28) if kernel == "triad" else (1 << 26))
+        x = torch.rand(n, device="cuda", generator=g) * 2 - 1
+        y = torch.rand(n, device="cuda", generator=g) * 2 - 1
+        z = torch.empty(n, device="cuda")
+        t = pk.Task.triad(z, x, y, 1.5, tile_elems=a.tile, flags=a.flags) if kernel == "triad" else pk.Task.vecadd(z, x, y, tile_elems=a.tile, flags=a.flags)
+        work, unit = 12.0 * n / 1e9, "GB/s"
+    else:
+        n = a.elems or (1 << 24)
+        k0 = torch.randint(0, 2**31 - 1, (n,), dtype=torch.int32, device="cuda", generator=g)
+        keys = k0.clone()
+        tmp = torch.empty_like(keys)
+        scratch = torch.empty(pk.sort_scratch_bytes(n), dtype=torch.uint8, device="cuda")
+        t = pk.Task.sort(keys, tmp, scratch, flags=a.flags)
+        restore = lambda: keys.copy_(k0)
+        work, unit = 36.0 * n / 1e9, "GB/s"
+    times = []
+    for i in range(a.reps):
+        if restore:
+            restore()
+        t.reset(s)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        t.launch(s)
+        e1.record()
+        torch.cuda.synchronize()
+        info = t.wait()
+        ms = e0.elapsed_time(e1)
+        times.append(ms)
+        if a.reps <= 12:
+            print(f"{kernel} flags={a.flags} launch {i}: {ms:.4f} ms  {work / (ms * 1e-3):.1f} {unit}  status={info.status}")
+    ts = sorted(times[min(3, len(times) - 1):])        # the first launches warm the clocks and caches up
+    med = ts[len(ts) // 2]
+    print(json.dumps({"kernel": kernel, "flags": a.flags, "reps": a.reps, "median_ms": round(med, 4), "min_ms": round(ts[0], 4),
+                      "median_rate": round(work / (med * 1e-3), 1), "unit": unit}))
+    t.destroy()
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20, help="timed steps; one step = 100 high-priority requests")
+    ap.add_argument("--warmup", type=int, default=5, help="untimed steps before them")
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--level1", action="store_true", help="also run the co-run phase at preemption level 1")
     ap.add_argument("--no-e2e", action="store_true")
@@ -537,16 +747,35 @@ def main() -> None:
     ap.add_argument("--config", type=int, default=1, help="1 = the headline workload (default); 4 = the LLF decode + three LP loops per GPU run")
     ap.add_argument("--config4-policy", default="LAX", choices=["LAX", "HPF"])
     ap.add_argument("--config4-requests", type=int, default=4)
+    ap.add_argument("--no-config4", action="store_true", help="skip the LLF leg (workload configuration 4) of the default run")
+    ap.add_argument("--no-timeline", action="store_true", help="skip the per-stage timeline of a preemption and its control arms")
+    ap.add_argument("--profile-case", default="", choices=["", "gemm", "triad", "sort", "vecadd"],
+                    help="run a few launches of ONE kernel and print their CUDA-event times (the small case the ncu captures use); "
+                         "with --m/--n/--k, --elems, --reps, --flags (0 preemptible, 1 twin without the flag poll, 2 GEMM with in-flight abort), --tile")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--elems", type=int, default=0)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--flags", type=int, default=0)
+    ap.add_argument("--tile", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
         impl_reference(args)
         return
+    if args.profile_case:
+        profile_case(args)
+        return
     if args.config == 4:
-        config4(args)
+        line = config4(args)
+        if line is not None:
+            print(json.dumps(line))
         return
     if not WORKER.exists() or not (LIB / "libxpk.so").exists():
         raise SystemExit("native libraries missing: run `python -c 'import __graft_entry__ as g; g.build()'` (there is no fallback path)")
     args.warmup = max(3, args.warmup)
+    requests, warm_requests = args.steps * REQS_PER_STEP, args.warmup * REQS_PER_STEP
+    side_requests = min(requests, 500)        # comparison arms that are context, not the headline
 
     rank, world, local, pg = dist_ctx()
     device = local
@@ -567,12 +796,13 @@ def main() -> None:
         mark("standalone phases")
         import tempfile
         alone_path = tempfile.mktemp(prefix="xsched_hp_alone_", suffix=".txt")
-        hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(500, args.steps), period_us=PERIOD_US, hp_n=HP_N,
-                                       samples=alone_path), env_alone, 180)[-1]
+        hp_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=max(2000, requests), period_us=PERIOD_US, hp_n=HP_N,
+                                       samples=alone_path), env_alone, 120 + max(2000, requests) * PERIOD_US * 3 / 1e6)[-1]
         hp_alone["samples_us"] = read_samples(alone_path)
         lp_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **lp_kw), env_alone, 120)[-1]
         launches += hp_alone["xpk_launches"] + lp_alone["xpk_launches"]
-        lat = run_json(worker_cmd("preempt-latency", device, level=2, count=300, **lp_kw), env_alone, 120)[-1]
+        lat = run_json(worker_cmd("preempt-latency", device, level=2, count=1000, **lp_kw), env_alone, 180)[-1]
+        launches += lat.get("xpk_launches", 0)
         roof, roof_launches = gemm_roofline(device)
         print(f"[bench] standalone hp={hp_alone} lp={lp_alone} lat={lat} roof={roof}", file=sys.stderr, flush=True)
         launches += roof_launches
@@ -585,7 +815,7 @@ def main() -> None:
         sampler = ClockSampler(device)
         sampler.start()
         t0 = time.time()
-        hp_co, lp_co = corun(device, ns, 2, args.steps, args.warmup, False, PERIOD_US, lp_kw)
+        hp_co, lp_co = corun(device, ns, 2, requests, warm_requests, False, PERIOD_US, lp_kw)
         elapsed = time.time() - t0
         clocks = sampler.stop()
         print(f"[bench] corun hp={hp_co} lp={lp_co}", file=sys.stderr, flush=True)
@@ -599,10 +829,10 @@ def main() -> None:
             # inter-process context switch on the GPU), and the no-XSched baseline: native CUDA stream
             # priorities with the non-preemptible twin of the GEMM.
             try:       # an extra leg must not take the headline down with it
-                both = run_json(worker_cmd("both", device, level=2, count=args.steps, period_us=PERIOD_US, hp_n=HP_N, duration_s=3600, **lp_kw),
+                both = run_json(worker_cmd("both", device, level=2, count=side_requests, period_us=PERIOD_US, hp_n=HP_N, duration_s=3600, **lp_kw),
                                 base_env(ns, None), 600)
                 hp_b, lp_b = both[0], both[1]
-                nat = run_json(worker_cmd("native-priority", device, count=args.steps, period_us=PERIOD_US, hp_n=HP_N, kernel="gemm", **GEMM),
+                nat = run_json(worker_cmd("native-priority", device, count=side_requests, period_us=PERIOD_US, hp_n=HP_N, kernel="gemm", **GEMM),
                                base_env(ns, None), 600)[-1]
                 launches += hp_b["xpk_launches"]
                 extra["one_process_two_queues"] = {"hp_p99_us": hp_b["p99_us"], "hp_p50_us": hp_b["p50_us"], "ratio": round(hp_b["p99_us"] / hp_alone["p99_us"], 3),
@@ -629,7 +859,7 @@ def main() -> None:
                             continue
                         for th, bs in ((16, 8), (2, 1)):
                             mark(f"transparent level 1: {name} window {th}/{bs}")
-                            r = transparent_corun(device, lib_path, min(args.steps, 200), th, bs)
+                            r = transparent_corun(device, lib_path, side_requests, th, bs)
                             if "hp_p99_us" in r:
                                 r["ratio_p99"] = round(r["hp_p99_us"] / plain_hp["p99_us"], 3)
                                 r["lp_kept_pct"] = round(100 * r["lp_tflops"] / plain_lp["rate"], 2) if r.get("lp_tflops") else None
@@ -713,22 +943,28 @@ def main() -> None:
             except Exception as e:
                 extra["config2_llama_decode_vs_gemm"] = {"error": str(e)[:400]}
         if args.level1:
-            hp_l1, lp_l1 = corun(device, ns, 1, args.steps, args.warmup, False, PERIOD_US, lp_kw)
+            hp_l1, lp_l1 = corun(device, ns, 1, side_requests, 20, False, PERIOD_US, lp_kw)
             extra["level1"] = {"hp_p99_us": hp_l1["p99_us"], "ratio": round(hp_l1["p99_us"] / hp_alone["p99_us"], 3),
                                "bg_kept_pct": round(100 * lp_l1["rate"] / lp_alone["rate"], 2)}
         e2e = None
         if not args.no_e2e:
             try:
-                n_e2e = max(30, args.steps // 6)
+                n_e2e = max(100, requests // 4)
                 hp_e_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=n_e2e, period_us=E2E_PERIOD_US, hp_n=HP_N, e2e=1), env_alone, 600)[-1]
-                hp_e, lp_e = corun(device, ns, 2, n_e2e, 5, True, E2E_PERIOD_US, lp_kw)
+                hp_e, lp_e = corun(device, ns, 2, n_e2e, 10, True, E2E_PERIOD_US, lp_kw)
                 launches += hp_e_alone["xpk_launches"] + hp_e["xpk_launches"] + lp_e["xpk_launches"]
                 e2e = {"value": round(hp_e["p99_us"] / hp_e_alone["p99_us"], 4), "unit": "x", "h2d_bytes_per_step": int(hp_e["h2d_bytes"]),
                        "d2h_bytes_per_step": int(hp_e["d2h_bytes"]), "hp_p99_us": hp_e["p99_us"], "hp_standalone_p99_us": hp_e_alone["p99_us"],
-                       "period_us": E2E_PERIOD_US, "bg_throughput_kept_pct": round(100 * lp_e["rate"] / lp_alone["rate"], 2),
+                       "period_us": E2E_PERIOD_US, "hp_samples": n_e2e, "bg_throughput_kept_pct": round(100 * lp_e["rate"] / lp_alone["rate"], 2),
                        "note": "request = H2D of both inputs from pinned memory + vector add + D2H of the result, as XQueue callback commands"}
             except Exception as e:       # reported, not fatal: the device-resident figure stands on its own
                 e2e = {"error": str(e)[:300]}
+        if not args.no_timeline and world == 1:
+            try:
+                mark("timeline of a preemption + control arms")
+                extra["preempt_timeline"] = timeline_leg(device, ns, lp_kw)
+            except Exception as e:
+                extra["preempt_timeline"] = {"error": str(e)[:300]}
     finally:
         if pg:
             pg.barrier()
@@ -738,6 +974,11 @@ def main() -> None:
                 server.wait(timeout=10)
             except subprocess.TimeoutExpired:
                 server.kill()
+
+    cfg4 = None
+    if not args.no_config4:
+        mark("config 4 leg (LLF, four processes per GPU)")
+        cfg4 = config4(args, (rank, world, local, pg))
 
     ratio = hp_co["p99_us"] / hp_alone["p99_us"]
     kept = 100.0 * lp_co["rate"] / lp_alone["rate"]
@@ -789,19 +1030,24 @@ def main() -> None:
         "data": "synthetic", "impl": "ours",
         "config": {"workload": "gemm8192_vs_vecadd64M", "policy": "HPF", "processes_per_gpu": 2, "preempt_level": 2, "lp_window": "threshold 2 / batch 1", "ipc": "polling receivers (XSCHED_IPC_SPIN=ON)", "hp_period_us": PERIOD_US,
                    "lp": "persistent preemptible bf16 GEMM 8192^3 in a loop", "hp": "fp32 vector add, 64 Mi elements",
-                   "l2": "LP operands+output 384 MiB and HP arrays 768 MiB both exceed the 126 MB L2 (no flush needed)", "xserver": 1},
+                   "l2": "LP operands+outputs 640 MiB and HP arrays 768 MiB both exceed the 126 MB L2 (no flush needed)", "xserver": 1,
+                   "hp_requests": requests, "hp_warmup_requests": warm_requests},
         "hp_p99_us": round(worst["hp_p99"], 2), "hp_standalone_p99_us": round(worst["alone_p99"], 2),
         "hp_p50_us": round(pooled["hp_p50"], 2), "hp_standalone_p50_us": round(pooled["alone_p50"], 2),
         "hp_p50_ratio": round(pooled["hp_p50"] / pooled["alone_p50"], 4), "hp_samples": len(co_all), "hp_standalone_samples": len(alone_all),
+        "value_interval_95": ratio_interval(co_all, alone_all),
         "preempt_latency_us": round(max(r["preempt_p99"] for r in allr), 2),
         "preempt_latency": {"p50_us": lat["preempt_p50_us"], "p95_us": lat["preempt_p95_us"], "p99_us": lat["preempt_p99_us"],
-                            "definition": "wall time of XQueueSuspend(xq, kQueueSuspendFlagSyncHwQueue), 300 samples at random moments"},
+                            "samples": lat["n"], "outputs_checked_after_preemption": lat.get("preempted_outputs_checked"),
+                            "definition": "wall time of XQueueSuspend(xq, kQueueSuspendFlagSyncHwQueue) at random moments"},
         "bg_throughput_kept_pct": round(min(r["kept"] for r in allr), 2),
         "bg_tflops_aggregate": round(sum(r["lp_rate"] for r in allr), 1), "bg_tflops_standalone": lp_alone["rate"],
         "bit_exact": all(r["bit_exact"] for r in allr),
         "per_gpu": [{"ratio": round(r["ratio"], 4), "kept_pct": round(r["kept"], 2), "preempt_p99_us": r["preempt_p99"]} for r in allr],
         "roofline": roof, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         "deactivations": lp_co["deactivations"], "relaunches": lp_co["relaunches"],
+        "lp_iterations_verified": lp_co.get("verified_iters"), "lp_preempted_iterations_verified": lp_co.get("verified_preempted_iters"),
+        "config4_llf": cfg4,
     }
     line.update(extra)
     print(json.dumps(line))

@@ -58,8 +58,9 @@ typedef enum {
 /* Launch-time flags for xpkTaskCreate*. */
 enum {
     XPK_FLAG_NONE           = 0,
-    XPK_FLAG_NON_PREEMPTIBLE = 1, /* build the twin: same tile loop, no flag poll, no
-                                     ticket atomics.  Used to measure the check's cost. */
+    XPK_FLAG_NON_PREEMPTIBLE = 1, /* the twin: same tile loop and the same ticket claim, the
+                                     preempt flag never read.  For kernels nothing needs to
+                                     stop, and to measure what the check costs.            */
     XPK_FLAG_ABORT_INFLIGHT = 2, /* GEMM only: on preemption abandon tiles whose main
                                      loop is still running and recompute them on resume
                                      (keeps the preemption latency below one tile).     */
@@ -162,7 +163,7 @@ xpkResult xpkTaskDestroy(xpkTask_t task);
  * nothing else, a latency-critical section where cudaMalloc's implicit device synchronisation is not
  * acceptable.  xpkTaskCreateSort needs a control block, a mailbox and caller-provided scratch; this
  * entry point needs none of them: its control block, digit histograms and look-back words live in a
- * fixed array inside the library's device image (about 2.1 MB, held by every GPU that loads the
+ * fixed array inside the library's device image (about 4.2 MB, held by every GPU that loads the
  * library until the process exits).
  *
  * Sorts `n` int32 keys ascending, in place in `keys`, using `tmp` (n keys) as the second buffer, on

@@ -121,8 +121,14 @@ int TypeOf(const void *p) {
 // Legacy-default-stream rule, simplified to the strict side: work for the legacy stream is accepted only after
 // everything already given to blocking streams (created without CU_STREAM_NON_BLOCKING) has finished, and work
 // for a blocking stream only after the legacy stream has drained.
+// Set while a `_ptsz` entry point runs: there NULL names the calling thread's default stream.
+thread_local bool t_null_is_per_thread = false;
+std::atomic<uint64_t> g_per_thread_stream_ops{0};          // operations the fake itself resolved to a per-thread default stream
+Stream *PerThreadStream();
+
 Stream *Of(CUstream s) {
-    if (s == nullptr || s == CU_STREAM_LEGACY || s == CU_STREAM_PER_THREAD) {
+    if (s == CU_STREAM_PER_THREAD || (s == nullptr && t_null_is_per_thread)) { g_per_thread_stream_ops++; return PerThreadStream(); }
+    if (s == nullptr || s == CU_STREAM_LEGACY) {
         std::vector<Stream *> blocking;
         { std::lock_guard<std::mutex> lk(S().mu); for (Stream *x : S().streams) if (!(x->flags & CU_STREAM_NON_BLOCKING)) blocking.push_back(x); }
         for (Stream *x : blocking) x->Drain();
@@ -224,6 +230,16 @@ static CUresult NewStream(CUstream *out, unsigned flags, int prio) {
     *out = (CUstream)s;
     return CUDA_SUCCESS;
 }
+} // extern "C"
+namespace {
+// The per-thread default stream of the real driver behaves like a non-blocking stream owned by the thread.
+Stream *PerThreadStream() {
+    thread_local Stream *mine = nullptr;
+    if (!mine) { CUstream h = nullptr; NewStream(&h, CU_STREAM_NON_BLOCKING, 0); mine = (Stream *)h; }
+    return mine;
+}
+} // namespace
+extern "C" {
 API cuStreamCreateWithPriority(CUstream *out, unsigned flags, int prio) { return NewStream(out, flags, prio); }
 API cuStreamCreate(CUstream *out, unsigned flags) { return NewStream(out, flags, 0); }
 API cuStreamDestroy(CUstream s) {
@@ -401,14 +417,32 @@ API cuGraphExecDestroy(CUgraphExec exec) { delete (std::shared_ptr<Recorded> *)e
 API cuGraphDestroy(CUgraph g) { delete (std::shared_ptr<Recorded> *)g; return CUDA_SUCCESS; }
 
 // ---- symbol lookup ----
-API cuGetProcAddress(const char *symbol, void **pfn, int, cuuint64_t, CUdriverProcAddressQueryResult *status) {
+// A few per-thread-default-stream twins, enough for the interposer tests (launch, copies, memset, event, sync).
+struct NullIsPerThread { bool prev; NullIsPerThread() : prev(t_null_is_per_thread) { t_null_is_per_thread = true; } ~NullIsPerThread() { t_null_is_per_thread = prev; } };
+API cuLaunchKernel_ptsz(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz, unsigned sh, CUstream s, void **p, void **e) {
+    NullIsPerThread scope; return cuLaunchKernel(f, gx, gy, gz, bx, by, bz, sh, s, p, e);
+}
+API cuMemcpyHtoDAsync_v2_ptsz(CUdeviceptr d, const void *h, size_t n, CUstream s) { NullIsPerThread scope; return cuMemcpyHtoDAsync(d, h, n, s); }
+API cuMemcpyDtoHAsync_v2_ptsz(void *h, CUdeviceptr d, size_t n, CUstream s) { NullIsPerThread scope; return cuMemcpyDtoHAsync(h, d, n, s); }
+API cuMemsetD32Async_ptsz(CUdeviceptr d, unsigned v, size_t n, CUstream s) { NullIsPerThread scope; return cuMemsetD32Async(d, v, n, s); }
+API cuEventRecord_ptsz(CUevent e, CUstream s) { NullIsPerThread scope; return cuEventRecord(e, s); }
+API cuStreamSynchronize_ptsz(CUstream s) { NullIsPerThread scope; return cuStreamSynchronize(s); }
+API cuStreamQuery_ptsz(CUstream s) { NullIsPerThread scope; return cuStreamQuery(s); }
+__attribute__((visibility("default"))) uint64_t fakePerThreadStreamOps() { return g_per_thread_stream_ops.load(); }
+
+API cuGetProcAddress(const char *symbol, void **pfn, int, cuuint64_t lookup_flags, CUdriverProcAddressQueryResult *status) {
     Dl_info info;
     void *self = dladdr((void *)&cuInit, &info) ? dlopen(info.dli_fname, RTLD_NOW | RTLD_NOLOAD) : nullptr;
     void *p = nullptr;
     if (self) {
         char name[128];
+        if (lookup_flags & CU_GET_PROC_ADDRESS_PER_THREAD_DEFAULT_STREAM) {
+            std::snprintf(name, sizeof(name), "%s_v2_ptsz", symbol);
+            p = dlsym(self, name);
+            if (!p) { std::snprintf(name, sizeof(name), "%s_ptsz", symbol); p = dlsym(self, name); }
+        }
         std::snprintf(name, sizeof(name), "%s_v2", symbol);
-        p = dlsym(self, name);
+        if (!p) p = dlsym(self, name);
         if (!p) p = dlsym(self, symbol);
     }
     *pfn = p;

@@ -26,7 +26,7 @@ SCENARIOS = [
 def build(tmp: Path, flag: str):
     """Objects are compiled once, in parallel, and linked into the scenario runner and the server."""
     from concurrent.futures import ThreadPoolExecutor
-    units = {p: tmp / (p.parent.name + "_" + p.stem + ".o") for d in ("preempt", "sched", "hal_host") for p in sorted((CSRC / d).glob("*.cpp"))}
+    units = {p: tmp / (p.parent.name + "_" + p.stem + ".o") for d in ("utils", "preempt", "sched", "hal_host") for p in sorted((CSRC / d).glob("*.cpp"))}
     units[ROOT / "oracle" / "lane_driver.cpp"] = tmp / "lane_driver.o"
     units[CSRC / "server" / "xserver.cpp"] = tmp / "xserver.o"
     common = [CXX, "-std=c++20", "-O1", "-g", f"-fsanitize={flag}", "-pthread", f"-I{ROOT / 'include'}", f"-I{CSRC}"]
@@ -38,7 +38,7 @@ def build(tmp: Path, flag: str):
         for r in pool.map(compile_one, units.items()):
             assert r.returncode == 0, r.stderr[-2000:]
     lane, srv = tmp / "lane_san", tmp / "xserver_san"
-    core = [str(o) for s_, o in units.items() if s_.parent.name in ("preempt", "sched")]
+    core = [str(o) for s_, o in units.items() if s_.parent.name in ("utils", "preempt", "sched")]
     host = [str(o) for s_, o in units.items() if s_.parent.name == "hal_host"]
     for out, objs in ((lane, [str(tmp / "lane_driver.o")] + core + host), (srv, [str(tmp / "xserver.o")] + core)):
         r = subprocess.run(common + ["-o", str(out)] + objs + ["-ldl", "-lrt"], capture_output=True, text=True)

@@ -139,7 +139,7 @@ def test_interposer_and_hal_are_clean_under_sanitizers(tmp_path, sanitizer):
     """Everything between the program and the fake driver — interposer, CUDA HAL, XQueue runtime, scheduler —
     compiled with ThreadSanitizer, then with AddressSanitizer + UBSan (the driver is opened without RTLD_DEEPBIND
     in such builds; leak checking is off: the process-lifetime singletons are never freed by design)."""
-    srcs = [CSRC / "shim" / "shim.cpp"] + [p for d in ("hal_cuda", "preempt", "sched") for p in sorted((CSRC / d).glob("*.cpp"))]
+    srcs = [CSRC / "shim" / "shim.cpp"] + [p for d in ("hal_cuda", "preempt", "sched", "utils") for p in sorted((CSRC / d).glob("*.cpp"))]
     common = [CXX, "-O1", "-g", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer", "-fPIC", "-pthread", f"-I{ROOT / 'include'}", f"-I{CSRC}", f"-I{CUDA_INC}"]
     san_env = dict(TSAN_OPTIONS="halt_on_error=0", ASAN_OPTIONS="detect_leaks=0")
     markers = ("WARNING: ThreadSanitizer", "ERROR: AddressSanitizer", "runtime error:")
@@ -249,3 +249,44 @@ def test_transparent_two_process_scheduling_without_a_gpu(tmp_path, spin, level)
     # and it does run between the requests
     gaps = [(requests[i][1], requests[i + 1][0]) for i in range(len(requests) - 1)]
     assert all(sum(1 for t in starts if a + 3000 < t < b) > 3 for a, b in gaps)
+
+
+PTDS_APP = FAKE_DIR / "ptds_app"
+
+
+def run_ptds(libdir: Path, *args, **extra):
+    env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+    env.update(FAKE_CUDA_LIB=str(FAKE), LD_LIBRARY_PATH=f"{libdir}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""), XLOG_LEVEL="WARN")
+    env.update({k: str(v) for k, v in extra.items()})
+    return subprocess.run([str(PTDS_APP), *map(str, args)], capture_output=True, text=True, env=env, timeout=300)
+
+
+def test_per_thread_default_stream_is_scheduled(tmp_path):
+    """CU_STREAM_PER_THREAD and the `_ptsz` entry points (looked up with the per-thread flag): every thread's default
+    stream becomes a private stream with an XQueue; nothing bypasses the queues; same results as without the interposer."""
+    plain = run_ptds(as_libcuda(tmp_path, FAKE), 3, 20)
+    assert plain.returncode == 0 and plain.stdout.startswith("OK "), plain.stdout + plain.stderr
+    stats = tmp_path / "stats.json"
+    r = run_ptds(as_libcuda(tmp_path, LIB / "libshimcuda.so"), 3, 20, XSCHED_CUDA_LIB=FAKE, XSCHED_AUTO_XQUEUE="ON", XSCHED_POLICY="HPF",
+                 XSCHED_AUTO_XQUEUE_LEVEL=1, XSCHED_AUTO_XQUEUE_THRESHOLD=4, XSCHED_AUTO_XQUEUE_BATCH_SIZE=2, XSCHED_SHIM_STATS_FILE=stats)
+    assert r.returncode == 0, r.stdout + r.stderr[-3000:]
+    assert r.stdout == plain.stdout
+    st = json.loads(stats.read_text())
+    assert st["thread_streams"] == 3 and st["streams_with_xqueue"] == 3
+    assert st["launches_queued"] == 3 * 20 * 2 and st["launches_direct"] == 0
+    assert st["copies_queued"] == 3 * 20 * 2 and st["copies_direct"] == 0
+    assert st["syncs_via_xqueue"] == 3 * 20
+    assert st["getproc_hooked_ptsz"] == 3 * 5            # five per-thread lookups per thread, all answered with the twins
+
+
+def test_single_stream_per_process(tmp_path):
+    """XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS=ON: four stream creations hand out one reference-counted stream; work
+    given to any handle is ordered (the program's kernels on four handles read and write the same buffer, which is
+    only correct when the handles are one stream); the stream lives until its last handle is destroyed."""
+    stats = tmp_path / "stats.json"
+    r = run_ptds(as_libcuda(tmp_path, LIB / "libshimcuda.so"), 1, 9, "single", XSCHED_CUDA_LIB=FAKE, XSCHED_AUTO_XQUEUE="ON", XSCHED_POLICY="HPF",
+                 XSCHED_AUTO_XQUEUE_LEVEL=1, XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS="ON", XSCHED_SHIM_STATS_FILE=stats)
+    assert r.returncode == 0, r.stdout + r.stderr[-3000:]
+    assert r.stdout.startswith("OK 136 same_handles=1")
+    st = json.loads(stats.read_text())
+    assert st["single_stream_refs"] == 4 and st["streams_with_xqueue"] == 1 and st["launches_queued"] == 9

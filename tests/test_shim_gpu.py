@@ -49,6 +49,41 @@ def test_plain_cuda_program_under_the_shim(shim_dir, tmp_path, level):
     assert st["getproc_hooked"] > 0                     # the runtime resolved its entry points through the override
 
 
+def test_per_thread_default_stream_program_under_the_shim(shim_dir, tmp_path):
+    """A program built with --default-stream per-thread: its two threads' default streams become two private
+    streams with an XQueue each, and every launch and copy goes through them."""
+    app = ROOT / "tests" / "apps" / "plain_ptds"
+    assert app.exists(), "tests/apps/plain_ptds not built (python -m xsched_b200.build)"
+    plain = subprocess.run([str(app), "25"], capture_output=True, text=True, timeout=120)
+    assert plain.returncode == 0 and plain.stdout.startswith("OK"), plain.stdout + plain.stderr
+    stats = tmp_path / "stats.json"
+    r = subprocess.run([str(app), "25"], capture_output=True, text=True, timeout=180,
+                       env=shim_env(shim_dir, stats, XSCHED_AUTO_XQUEUE_LEVEL=1, XSCHED_AUTO_XQUEUE_THRESHOLD=4, XSCHED_AUTO_XQUEUE_BATCH_SIZE=2))
+    assert r.returncode == 0, r.stdout + r.stderr[-2000:]
+    assert r.stdout == plain.stdout
+    st = json.loads(stats.read_text())
+    assert st["thread_streams"] >= 2 and st["streams_with_xqueue"] >= 2
+    assert st["launches_queued"] == 2 * 25 * 2          # two threads x rounds x two kernels
+    assert st["copies_queued"] == 2 * 25 * 2
+    assert st["getproc_hooked_ptsz"] > 0                 # the runtime asked for the per-thread variants and got the twins
+    assert st["launches_direct"] == 0
+
+
+def test_single_stream_per_process_mode(shim_dir, tmp_path):
+    """XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS=ON: the program's two streams are one stream with one XQueue; the
+    cross-stream event dependency of the test program still holds and the results are the same."""
+    plain = subprocess.run([str(APP), "20"], capture_output=True, text=True, timeout=120)
+    assert plain.returncode == 0
+    stats = tmp_path / "stats.json"
+    r = subprocess.run([str(APP), "20"], capture_output=True, text=True, timeout=180,
+                       env=shim_env(shim_dir, stats, XSCHED_AUTO_XQUEUE_LEVEL=1, XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS="ON"))
+    assert r.returncode == 0, r.stdout + r.stderr[-2000:]
+    assert r.stdout == plain.stdout
+    st = json.loads(stats.read_text())
+    assert st["streams_with_xqueue"] == 1 and st["single_stream_refs"] == 2
+    assert st["launches_queued"] == 20 * 3
+
+
 TORCH_SCRIPT = r"""
 import torch
 torch.manual_seed(0)

@@ -85,6 +85,8 @@ SHIM_HANDLED = {
     "cuMemcpyPeerAsync", "cuMemsetD16Async", "cuGraphLaunch", "cuStreamAddCallback", "cuMemcpy", "cuMemcpyDtoH_v2", "cuMemcpyHtoD_v2",
     "cuMemcpyDtoD_v2", "cuMemcpy3DAsync_v2", "cuMemsetD2D8Async", "cuMemsetD2D16Async", "cuMemsetD2D32Async", "cuGraphUpload",
     "cuEventRecordWithFlags", "cuStreamBeginCaptureToGraph",
+    # per-thread-default-stream twins of the above
+    "cuEventRecordWithFlags_ptsz", "cuEventRecord_ptsz", "cuGraphLaunch_ptsz", "cuGraphUpload_ptsz", "cuLaunchCooperativeKernel_ptsz", "cuLaunchHostFunc_ptsz", "cuLaunchKernelEx_ptsz", "cuLaunchKernel_ptsz", "cuMemAllocAsync_ptsz", "cuMemFreeAsync_ptsz", "cuMemcpy2DAsync_v2_ptsz", "cuMemcpy3DAsync_v2_ptsz", "cuMemcpyAsync_ptsz", "cuMemcpyDtoDAsync_v2_ptsz", "cuMemcpyDtoD_v2_ptds", "cuMemcpyDtoHAsync_v2_ptsz", "cuMemcpyDtoH_v2_ptds", "cuMemcpyHtoDAsync_v2_ptsz", "cuMemcpyHtoD_v2_ptds", "cuMemcpyPeerAsync_ptsz", "cuMemcpy_ptds", "cuMemsetD16Async_ptsz", "cuMemsetD2D16Async_ptsz", "cuMemsetD2D32Async_ptsz", "cuMemsetD2D8Async_ptsz", "cuMemsetD32Async_ptsz", "cuMemsetD8Async_ptsz", "cuStreamAddCallback_ptsz", "cuStreamBeginCaptureToGraph_ptsz", "cuStreamBeginCapture_v2_ptsz", "cuStreamEndCapture_ptsz", "cuStreamQuery_ptsz", "cuStreamSynchronize_ptsz", "cuStreamWaitEvent_ptsz",
 }
 
 
@@ -201,6 +203,10 @@ def build_test_apps(force: bool = False, verbose: bool = False) -> Path | None:
             continue
         if force or _stale(out, [src]):
             _run([NVCC, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, src], verbose)
+    # the same kind of program built for per-thread default streams
+    src, ptds = ROOT / "tests" / "apps" / "plain_ptds.cu", ROOT / "tests" / "apps" / "plain_ptds"
+    if src.exists() and (force or _stale(ptds, [src])):
+        _run([NVCC, "-std=c++17", "-O2", "--default-stream", "per-thread", "-gencode", "arch=compute_100a,code=sm_100a", "-o", ptds, src], verbose)
     build_fake_driver(force, verbose)
     return out
 
@@ -225,6 +231,9 @@ def build_fake_driver(force: bool = False, verbose: bool = False) -> Path | None
     loop_src, loop_app = d / "loop_app.cpp", d / "loop_app"
     if loop_src.exists() and (force or _stale(loop_app, [loop_src, lib])):
         _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", "-o", loop_app, loop_src, f"-L{link}", "-lcuda", "-ldl", "-pthread"], verbose)
+    ptds_src, ptds_app = d / "ptds_app.cpp", d / "ptds_app"
+    if ptds_src.exists() and (force or _stale(ptds_app, [ptds_src, lib])):
+        _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", "-o", ptds_app, ptds_src, f"-L{link}", "-lcuda", "-ldl", "-pthread"], verbose)
     hal_src, hal_app = d / "hal_app.cpp", d / "hal_app"
     if hal_src.exists() and (LIB / "libhalcuda.so").exists() and (force or _stale(hal_app, [hal_src, lib, LIB / "libhalcuda.so", LIB / "libpreempt.so"])):
         _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", f"-I{INC}", "-o", hal_app, hal_src, f"-L{link}", f"-L{LIB}",

@@ -179,7 +179,6 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (M + kBM - 1) / kBM, n_tiles = N / kBN;   // M is a multiple of 128: the last row-block may be half full
     const uint32_t k_blocks = K / kBK;
-    const unsigned long long total_tiles = (unsigned long long)m_tiles * n_tiles;
     volatile uint32_t *v_abort = &sh->abort;
     note_start(ctl);
 
@@ -223,12 +222,9 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
         // ======================= producer: claim + TMA =======================
         if (lane == 0) {
             unsigned long long kseq = 0, tseq = 0;
-            unsigned long long static_tile = blockIdx.x;
             bool live = true;
             while (live) {
-                unsigned long long tile;
-                if constexpr (kPreemptible) tile = claim_tile(ctl);
-                else { tile = static_tile < total_tiles ? static_tile : kNoTile; static_tile += gridDim.x; }
+                const unsigned long long tile = claim_tile<kPreemptible>(ctl);     // the twin takes the same tickets without reading the flag
                 const int slot = (int)(tseq % kSchedSlots);
                 const uint32_t sph = (uint32_t)((tseq / kSchedSlots) & 1);
                 if (!bounded_wait(&sh->sched_empty[slot], sph ^ 1u, sh, ctl, kErrGemmProducer,

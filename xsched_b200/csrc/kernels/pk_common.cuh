@@ -93,17 +93,38 @@ __device__ __forceinline__ uint32_t ld_flag(const uint32_t *p) {
     return v;
 }
 
+// The claim in its parts, for kernels that overlap it with work: the cursor fields are frozen while a launch
+// runs, so they may be read once; a ticket is one atomic; a ticket number maps to a tile.
+struct ClaimCtx {
+    unsigned long long nret;     // tickets below this are tiles handed back by an earlier launch
+    unsigned long long fresh;    // tiles never claimed so far
+    unsigned long long base;     // first of them
+    uint32_t cur;                // which returned[] list this launch consumes
+};
+__device__ __forceinline__ ClaimCtx load_claim_ctx(const Ctl *ctl) {
+    ClaimCtx c;
+    c.nret = ctl->n_returned;
+    c.base = ctl->base;
+    c.fresh = ctl->total - c.base;
+    c.cur = ctl->cur;
+    return c;
+}
+__device__ __forceinline__ unsigned long long take_ticket(Ctl *ctl) { return atomicAdd(&ctl->claim_seq, 1ull); }
+__device__ __forceinline__ unsigned long long resolve_ticket(const Ctl *ctl, const ClaimCtx &c, unsigned long long t) {
+    if (t < c.nret) return ctl->returned[c.cur][t];
+    t -= c.nret;
+    return t < c.fresh ? c.base + t : kNoTile;
+}
+
 // One thread per CTA calls this.  Returns a tile index or kNoTile (flag raised or work
 // exhausted).  Tickets < n_returned map to tiles handed back by an earlier launch.
+// kPoll = false is the twin used to measure what the check costs: the same ticket sequence, the same
+// atomics, the flag never read.
+template <bool kPoll = true>
 __device__ __forceinline__ unsigned long long claim_tile(Ctl *ctl) {
-    if (ld_flag(ctl->flag) != 0) return kNoTile;
-    const unsigned long long nret = ctl->n_returned;
-    const unsigned long long fresh = ctl->total - ctl->base;
-    unsigned long long t = atomicAdd(&ctl->claim_seq, 1ull);
-    if (t < nret) return ctl->returned[ctl->cur][t];
-    t -= nret;
-    if (t >= fresh) return kNoTile;
-    return ctl->base + t;
+    if constexpr (kPoll) { if (ld_flag(ctl->flag) != 0) return kNoTile; }
+    const ClaimCtx c = load_claim_ctx(ctl);
+    return resolve_ticket(ctl, c, take_ticket(ctl));
 }
 
 // Hand a claimed tile back (its output has not been written, or may be rewritten whole).

@@ -1,6 +1,6 @@
 // Preemptible persistent int32 LSD radix sort (8-bit digits, 4 passes, ascending).
 //
-// One persistent kernel walks a single ticket sequence of 5*T tiles (T = ceil(n / 8192)):
+// One persistent kernel walks a single ticket sequence of 5*T tiles (T = ceil(n / 4096)):
 //   phase 0, tickets [0,T):       digit histograms of all four bytes of every key, summed
 //                                 into hist[4][256] with integer atomics (order-free, exact);
 //   phase p=1..4, tickets [pT,(p+1)T): scatter pass p-1 over tile j = ticket - pT.
@@ -9,11 +9,13 @@
 // a claimed tile only ever waits on smaller tickets, so the waits cannot deadlock; they are
 // bounded all the same and raise an error instead of spinning forever.
 //
-// Inside a scatter tile (512 threads x 16 keys, keys held warp-striped so that load order is
-// preserved):
-//   * each warp ranks its keys digit by digit with __ballot_sync / __popc — eight ballots give the
-//     mask of lanes that share a digit, those lanes learn their order from the mask, the lowest lane bumps the warp's
-//     counter in shared memory and __shfl_sync hands the base back (stable within the warp);
+// Inside a scatter tile (256 threads x 16 keys, keys held warp-striped so that load order is
+// preserved; four CTAs per SM, so that one CTA's barriers and look-back waits are covered by the others):
+//   * each warp ranks its keys item by item: every lane ORs its lane bit into a shared-memory word
+//     selected by (warp, digit), reads the word back — the mask of lanes holding the same digit — and the
+//     warp's running counter of that digit; its rank is counter + number of lower lanes in the mask; the
+//     lowest lane of the mask advances the counter and clears the word (stable within the warp; two
+//     alternating mask tables make two warp barriers per item enough);
 //   * warp counters are prefix-summed across warps, giving stable ranks within the tile;
 //   * the tile's per-digit counts are published and the exclusive prefix over earlier tiles
 //     is obtained by decoupled look-back (one thread per digit);
@@ -37,10 +39,12 @@ namespace xpk {
 
 void note_launches(unsigned n);      // pk_api.cu: the library-wide launch counter
 
-constexpr int kSortThreads = 512;
+constexpr int kSortThreads = 256;
 constexpr int kSortWarps   = kSortThreads / 32;
 constexpr int kSortItems   = 16;
-constexpr int kSortTile    = kSortThreads * kSortItems;   // 8192 keys
+constexpr int kSortTile    = kSortThreads * kSortItems;   // 4096 keys
+constexpr int kSortCtasPerSm = 4;
+static_assert(kSortThreads == 256, "one thread per digit: the scans and the look-back assume 256 threads");
 constexpr int kRadix       = 256;
 constexpr uint32_t kFlagAgg  = 1u << 30;
 constexpr uint32_t kFlagInc  = 2u << 30;
@@ -52,13 +56,16 @@ constexpr uint32_t kErrSortLookback  = 0x50000002u;
 
 struct SortSmem {
     uint32_t warp_hist[kSortWarps][kRadix];   // per-warp digit counters -> exclusive prefix over warps
+    uint32_t match[2][kSortWarps][kRadix];    // lane masks per (item parity, warp, digit); all zero between uses
     uint32_t keys[kSortTile];                 // ranked staging / phase-0 histograms
     uint32_t tile_off[kRadix];                // exclusive digit offsets inside the tile
     uint32_t gbase[kRadix];                   // dst index = gbase[digit] + rank in tile (mod 2^32)
     uint32_t scan_tmp[kSortWarps];
-    unsigned long long tile;
+    ClaimCtx claim;                           // thread 0's copy of the frozen cursor fields
+    uint32_t tile;                            // tile handed from thread 0 to the CTA (kNoTile32 = none)
     uint32_t bail;
 };
+constexpr uint32_t kNoTile32 = 0xFFFFFFFFu;   // 5 * T tickets always fit 32 bits (n <= 2^30)
 
 __device__ __forceinline__ uint32_t ld_relaxed(const uint32_t *p) {
     uint32_t v;
@@ -77,21 +84,7 @@ __device__ __forceinline__ unsigned long long ld_acquire64(const unsigned long l
 // Signed ascending order == unsigned order of the key with its sign bit flipped.
 __device__ __forceinline__ uint32_t twiddle(uint32_t k) { return k ^ 0x80000000u; }
 
-// Lanes of the warp holding the same 8-bit digit as this lane: eight ballots, one per digit bit, each
-// keeping the lanes that agree with this lane on that bit.  (The single match.any instruction gives the
-// same mask but issues at a small fraction of the ballot rate.)
-__device__ __forceinline__ uint32_t match_digit(uint32_t d) {
-    uint32_t mask = 0xffffffffu;
-#pragma unroll
-    for (int b = 0; b < 8; ++b) {
-        const bool bit = (d >> b) & 1u;
-        const uint32_t vote = __ballot_sync(0xffffffffu, bit);
-        mask &= bit ? vote : ~vote;
-    }
-    return mask;
-}
-
-// Exclusive scan of 256 values held by threads 0..255 (one each); all 512 threads call.
+// Exclusive scan of 256 values, one per thread; all threads call.
 __device__ __forceinline__ uint32_t block_excl_scan256(uint32_t v, SortSmem &sm, uint32_t *total) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint32_t inc = v;
@@ -104,7 +97,7 @@ __device__ __forceinline__ uint32_t block_excl_scan256(uint32_t v, SortSmem &sm,
     __syncthreads();
     uint32_t add = 0, tot = 0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
+    for (int w = 0; w < kSortWarps; ++w) {
         uint32_t t = sm.scan_tmp[w];
         if (w < warp) add += t;
         tot += t;
@@ -131,45 +124,58 @@ __device__ __forceinline__ bool wait_counter(Ctl *ctl, const unsigned long long 
     return true;
 }
 
-template <bool kPoll>
-__device__ __forceinline__ unsigned long long sort_claim(Ctl *ctl) {
-    if constexpr (kPoll) return claim_tile(ctl);
-    // Twin: same ticket order (the look-back needs it) but the flag is never read.
-    unsigned long long t = atomicAdd(&ctl->claim_seq, 1ull);
-    const unsigned long long fresh = ctl->total - ctl->base;
-    return t < fresh ? ctl->base + t : kNoTile;
-}
+constexpr int kLookbackWindow = 8;      // predecessor tiles read per round of the look-back
 
+// The ticket claim is two dependent round trips to L2 (flag, then the ticket atomic) that one thread makes while
+// 255 wait; measured at a fifth of a tile's time when done at the top of the loop.  It is therefore spread over
+// the tile: thread 0 reads the preempt flag at the top of tile i (used much later), takes the ticket of tile
+// i+1 just before it starts writing tile i out, and hands the tile id to the CTA at the closing barrier.  The
+// ticket is taken late on purpose: tickets must be taken in the order in which CTAs become free, or the
+// look-back of ticket t+1 waits for a CTA that still has most of another tile to do before it ranks ticket t.
+// So the flag a CTA acts on is at most one tile old: after the flag is raised a CTA finishes the tile it is in
+// and possibly one more (about 10 us each).  A claimed ticket is always processed by the CTA that took it, which
+// the look-back of later tickets relies on.
 template <bool kPoll>
-__global__ void __launch_bounds__(kSortThreads, 2)
+__global__ void __launch_bounds__(kSortThreads, kSortCtasPerSm)
 radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint32_t *state,
-                  unsigned long long n, unsigned long long T, unsigned long long launch_no) {
+                  unsigned long long n64, unsigned long long T64, unsigned long long launch_no) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     SortSmem &sm = *reinterpret_cast<SortSmem *>(smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t n = (uint32_t)n64, T = (uint32_t)T64;     // n <= 2^30
     unsigned long long *phase_done = ctl->user;       // [0..4]
-    unsigned long long done = 0;
+    uint32_t done = 0;
+    uint32_t goff = 0;            // exclusive global offset of digit `tid` in pass `goff_pass`
+    int goff_pass = -1;
     note_start(ctl);
+    // The mask tables are all zero whenever no warp is between its two barriers of an item.
+    for (int i = tid; i < 2 * kSortWarps * kRadix; i += kSortThreads) (&sm.match[0][0][0])[i] = 0;
+    if (tid == 0) {
+        sm.claim = load_claim_ctx(ctl);               // frozen while a launch runs
+        const unsigned long long first = claim_tile<kPoll>(ctl);
+        sm.tile = first == kNoTile ? kNoTile32 : (uint32_t)first;
+        sm.bail = 0;
+    }
+    __syncthreads();
+    uint32_t ticket = sm.tile;
+    uint32_t cur_phase = kNoTile32;                   // phase whose predecessor is known to be complete
 
-    while (true) {
-        if (tid == 0) {
-            unsigned long long t = sort_claim<kPoll>(ctl);
-            uint32_t bail = 0;
-            if (t != kNoTile) {
-                const unsigned long long phase = t / T;
-                if (phase > 0 && !wait_counter(ctl, &phase_done[phase - 1], T, kErrSortPhaseWait))
-                    bail = 1;
-            }
-            sm.tile = t;
-            sm.bail = bail;
+    while (ticket != kNoTile32) {
+        const uint32_t phase = ticket / T;
+        if (phase != cur_phase) {
+            // First tile of a phase for this CTA: every tile of the phase before must have finished.  (Uniform.)
+            if (tid == 0 && phase > 0 && !wait_counter(ctl, &phase_done[phase - 1], T, kErrSortPhaseWait)) sm.bail = 1;
+            __syncthreads();
+            if (sm.bail) break;
+            cur_phase = phase;
         }
-        __syncthreads();
-        const unsigned long long ticket = sm.tile;
-        if (ticket == kNoTile || sm.bail) break;
-        const unsigned long long phase = ticket / T;
-        const unsigned long long j = ticket - phase * T;
-        const unsigned long long lo = j * (unsigned long long)kSortTile;
-        const uint32_t count = (uint32_t)((n - lo) < (unsigned long long)kSortTile ? (n - lo) : kSortTile);
+        const uint32_t j = ticket - phase * T;
+        const uint32_t lo = j * (uint32_t)kSortTile;
+        const uint32_t count = min(n - lo, (uint32_t)kSortTile);
+        uint32_t flag_now = 0;
+        if constexpr (kPoll) { if (tid == 0) flag_now = ld_flag(ctl->flag); }       // consumed a barrier later
+        unsigned long long next_seq = kNoTile;        // thread 0: ticket number taken for the next tile
+        uint32_t next = kNoTile32;
 
         if (phase == 0) {
             // ---- histograms of all four digits of this tile's keys ----
@@ -184,6 +190,7 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
                 atomicAdd(&h[3 * kRadix + (k >> 24)], 1u);
             }
             __syncthreads();
+            if (tid == 0 && flag_now == 0) next_seq = take_ticket(ctl);
             for (int i = tid; i < 4 * kRadix; i += kSortThreads) {
                 const uint32_t c = h[i];
                 if (c) atomicAdd(&hist[i], c);
@@ -193,7 +200,7 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
             const int shift = pass * 8;
             const uint32_t *src = (pass & 1) ? tmp : keys;
             uint32_t *dst = (pass & 1) ? keys : tmp;
-            uint32_t *st = state + ((unsigned long long)pass * T + j) * kRadix;
+            uint32_t *st = state + ((unsigned long long)pass * T + j) * kRadix;      // 4 * T * 256 words can pass 2^32 bytes
 
             // ---- load (warp-striped) ----
             uint32_t key[kSortItems];
@@ -204,71 +211,99 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
                 const uint32_t idx = wbase + i * 32 + lane;
                 key[i] = idx < count ? twiddle(__ldcg(src + lo + idx)) : 0xFFFFFFFFu;
             }
-            for (int i = tid; i < kSortWarps * kRadix; i += kSortThreads) (&sm.warp_hist[0][0])[i] = 0;
-            __syncthreads();
+            // Each warp clears its own counter row (no other warp touches it before the block barrier below).
+            volatile uint32_t *wh = sm.warp_hist[warp];
+#pragma unroll
+            for (int i = 0; i < kRadix / 32; ++i) wh[i * 32 + lane] = 0;
+            __syncwarp();
 
             // ---- stable rank inside the warp ----
-            uint32_t *wh = sm.warp_hist[warp];
+            const uint32_t lane_bit = 1u << lane, lower = lane_bit - 1u;
 #pragma unroll
             for (int i = 0; i < kSortItems; ++i) {
                 const uint32_t d = (key[i] >> shift) & 255u;
-                const uint32_t mask = match_digit(d);
-                const int leader = __ffs(mask) - 1;
-                const uint32_t before = __popc(mask & ((1u << lane) - 1u));
-                uint32_t base = 0;
-                if (lane == leader) { base = wh[d]; wh[d] = base + __popc(mask); }
-                base = __shfl_sync(0xffffffffu, base, leader);
-                rank[i] = base + before;
+                uint32_t *mw = &sm.match[i & 1][warp][d];
+                atomicOr(mw, lane_bit);
                 __syncwarp();
+                const uint32_t mask = *(volatile uint32_t *)mw;      // lanes of this item with the same digit
+                const uint32_t base = wh[d];                         // keys of earlier items with that digit
+                __syncwarp();
+                if ((mask & lower) == 0) {                           // lowest lane of the group
+                    wh[d] = base + __popc(mask);
+                    *(volatile uint32_t *)mw = 0;
+                }
+                rank[i] = base + __popc(mask & lower);
+                // No barrier here: the next item uses the other mask table, and its first barrier orders this
+                // counter update before the next read of the counters.
             }
             __syncthreads();
 
-            // ---- per-digit totals, exclusive prefix over warps ----
+            // ---- per-digit totals, exclusive prefix over warps (thread t owns digit t) ----
             uint32_t cnt = 0;
-            if (tid < kRadix) {
 #pragma unroll
-                for (int w = 0; w < kSortWarps; ++w) {
-                    const uint32_t c = sm.warp_hist[w][tid];
-                    sm.warp_hist[w][tid] = cnt;
-                    cnt += c;
-                }
-                // Publish early so later tiles can look back through this one.
-                st_relaxed(st + tid, (j == 0 ? kFlagInc : kFlagAgg) | cnt);
+            for (int w = 0; w < kSortWarps; ++w) {
+                const uint32_t c = sm.warp_hist[w][tid];
+                sm.warp_hist[w][tid] = cnt;
+                cnt += c;
             }
-            const uint32_t toff = block_excl_scan256(tid < kRadix ? cnt : 0u, sm, nullptr);
-            // Global start of each digit in this pass.
-            const uint32_t hval = tid < kRadix ? __ldcg(hist + pass * kRadix + tid) : 0u;
-            const uint32_t goff = block_excl_scan256(hval, sm, nullptr);
+            // Publish early so later tiles can look back through this one.
+            st_relaxed(st + tid, (j == 0 ? kFlagInc : kFlagAgg) | cnt);
+            const uint32_t toff = block_excl_scan256(cnt, sm, nullptr);
+            // Global start of each digit in this pass: the same for every tile of a pass, so it is computed when
+            // this CTA meets the pass for the first time and kept in a register (the condition is uniform).
+            if (goff_pass != pass) {
+                goff = block_excl_scan256(__ldcg(hist + pass * kRadix + tid), sm, nullptr);
+                goff_pass = pass;
+            }
 
-            if (tid < kRadix) {
-                // ---- decoupled look-back over earlier tiles of this pass ----
-                uint32_t excl = 0;
-                bool ok = true;
-                if (j > 0) {
-                    long long k = (long long)j - 1;
-                    const unsigned long long t0 = global_ns();
-                    uint32_t it = 0;
-                    while (true) {
-                        const uint32_t s = ld_relaxed(state + ((unsigned long long)pass * T + k) * kRadix + tid);
-                        const uint32_t f = s & ~kValMask;
-                        if (f == 0) {
-                            __nanosleep(32);
-                            if ((++it & 255u) == 0) {
-                                if (ld_relaxed(&ctl->error) != 0) { ok = false; break; }
-                                if (global_ns() - t0 > kSpinLimitNs) { raise_error(ctl, kErrSortLookback); ok = false; break; }
-                            }
-                            continue;
+            // ---- decoupled look-back over earlier tiles of this pass, kLookbackWindow tiles per round ----
+            uint32_t excl = 0;
+            bool ok = true;
+            if (j > 0) {
+                long long k = (long long)j - 1;                  // nearest tile not yet accounted for
+                const uint32_t *row0 = state + (unsigned long long)pass * T * kRadix + tid;
+                unsigned long long t0 = 0;
+                uint32_t it = 0;
+                bool found = false;
+                while (!found) {
+                    // The nearest unaccounted tile first, alone: while it is unpublished nothing else is worth reading.
+                    uint32_t s0 = ld_relaxed(row0 + (unsigned long long)k * kRadix);
+                    while ((s0 & ~kValMask) == 0) {
+                        __nanosleep(32);
+                        if ((++it & 127u) == 0) {
+                            if (ld_relaxed(&ctl->error) != 0) { ok = false; break; }
+                            const unsigned long long now = global_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > kSpinLimitNs) { raise_error(ctl, kErrSortLookback); ok = false; break; }
                         }
-                        excl += s & kValMask;
-                        if (f == kFlagInc) break;
-                        --k;
+                        s0 = ld_relaxed(row0 + (unsigned long long)k * kRadix);
                     }
-                    if (ok) st_relaxed(st + tid, kFlagInc | ((excl + cnt) & kValMask));
+                    if (!ok) break;
+                    excl += s0 & kValMask;
+                    if ((s0 & ~kValMask) == kFlagInc) break;
+                    --k;
+                    // Then a window of older tiles in one round trip; they are accounted for in order up to the
+                    // first inclusive word, or up to the first word that is not published yet.
+                    uint32_t sv[kLookbackWindow];
+#pragma unroll
+                    for (int w = 0; w < kLookbackWindow; ++w)
+                        sv[w] = (k - w) >= 0 ? ld_relaxed(row0 + (unsigned long long)(k - w) * kRadix) : kFlagInc;   // before tile 0: nothing
+                    int used = 0;
+#pragma unroll
+                    for (int w = 0; w < kLookbackWindow; ++w) {
+                        const uint32_t f = sv[w] & ~kValMask;
+                        if (found || used != w || f == 0) continue;
+                        excl += sv[w] & kValMask;
+                        used = w + 1;
+                        if (f == kFlagInc) found = true;
+                    }
+                    k -= used;
                 }
-                sm.tile_off[tid] = toff;
-                sm.gbase[tid] = goff + excl - toff;
-                if (!ok) sm.bail = 1;
+                if (ok) st_relaxed(st + tid, kFlagInc | ((excl + cnt) & kValMask));
             }
+            sm.tile_off[tid] = toff;
+            sm.gbase[tid] = goff + excl - toff;
+            if (!ok) sm.bail = 1;
             __syncthreads();
             if (sm.bail) break;
 
@@ -280,19 +315,28 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
             }
             __syncthreads();
 
+            if (tid == 0 && flag_now == 0) next_seq = take_ticket(ctl);      // result needed after the write-out
+
             // ---- write out: consecutive threads -> consecutive addresses per digit run ----
+#pragma unroll 4
             for (uint32_t idx = tid; idx < count; idx += kSortThreads) {
                 const uint32_t k = sm.keys[idx];
                 const uint32_t d = (k >> shift) & 255u;
                 dst[sm.gbase[d] + idx] = twiddle(k);
             }
         }
+        if (tid == 0) {
+            const unsigned long long nt = next_seq == kNoTile ? kNoTile : resolve_ticket(ctl, sm.claim, next_seq);
+            sm.tile = nt == kNoTile ? kNoTile32 : (uint32_t)nt;
+        }
         __syncthreads();
+        next = sm.tile;
         if (tid == 0) {
             __threadfence();
             atomicAdd(&phase_done[phase], 1ull);
         }
         ++done;
+        ticket = next;
     }
     __syncthreads();
     if (tid == 0) cta_exit(ctl, done, launch_no);

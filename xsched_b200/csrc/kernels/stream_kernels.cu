@@ -6,9 +6,10 @@
 // over latency x bandwidth bytes in flight.  Indexing is 64-bit throughout (2^31 elements
 // per array overflows 32-bit byte offsets).
 //
-// The preemptible form claims one tile (tile_elems elements) at a time through
-// xpk::claim_tile, which reads the preempt flag first.  The twin walks the same tiles
-// with a static stride and touches neither the flag nor the ticket counter.
+// Both forms claim one tile (tile_elems elements) at a time through xpk::claim_tile; the
+// preemptible one reads the preempt flag before each claim, the twin (kPreemptible = false:
+// the high-priority kernels, and the measurement of what the check costs) never does.  Tiles
+// handed out dynamically also balance the HBM channels better than a static stride does.
 #include "pk_common.cuh"
 
 namespace xpk {
@@ -83,29 +84,18 @@ stream_kernel(Ctl *ctl, float *__restrict__ out, const float *__restrict__ x,
               unsigned long long tile_elems, unsigned long long launch_no) {
     unsigned long long done = 0;
     note_start(ctl);
-    if constexpr (kPreemptible) {
-        __shared__ unsigned long long s_tile;
-        while (true) {
-            if (threadIdx.x == 0) s_tile = claim_tile(ctl);
-            __syncthreads();
-            const unsigned long long tile = s_tile;
-            if (tile == kNoTile) break;
-            const unsigned long long lo = tile * tile_elems;
-            unsigned long long hi = lo + tile_elems;
-            if (hi > n) hi = n;
-            stream_tile<OP>(out, x, y, s, lo, hi);
-            ++done;
-            __syncthreads();          // s_tile is rewritten next iteration
-        }
-    } else {
-        const unsigned long long total = (n + tile_elems - 1) / tile_elems;
-        for (unsigned long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
-            const unsigned long long lo = tile * tile_elems;
-            unsigned long long hi = lo + tile_elems;
-            if (hi > n) hi = n;
-            stream_tile<OP>(out, x, y, s, lo, hi);
-            ++done;
-        }
+    __shared__ unsigned long long s_tile;
+    while (true) {
+        if (threadIdx.x == 0) s_tile = claim_tile<kPreemptible>(ctl);
+        __syncthreads();
+        const unsigned long long tile = s_tile;
+        if (tile == kNoTile) break;
+        const unsigned long long lo = tile * tile_elems;
+        unsigned long long hi = lo + tile_elems;
+        if (hi > n) hi = n;
+        stream_tile<OP>(out, x, y, s, lo, hi);
+        ++done;
+        __syncthreads();          // s_tile is rewritten next iteration
     }
     __syncthreads();
     if (threadIdx.x == 0) cta_exit(ctl, done, launch_no);

@@ -12,6 +12,13 @@
 // cuGetProcAddress override intercept.cpp:1108-1166): legacy-stream calls first drain XQueues of blocking
 // streams and then go straight to the driver; while a stream capture is open everything goes straight to
 // the driver.  Unlike the reference, the generic cuMemcpyAsync is routed too.  x86-64 only (trampolines).
+//
+// Per-thread default stream (programs built with --default-stream per-thread, or that pass CU_STREAM_PER_THREAD):
+// every routed entry point has a `_ptsz` twin, and lookups with CU_GET_PROC_ADDRESS_PER_THREAD_DEFAULT_STREAM get
+// the twin.  CU_STREAM_PER_THREAD — and, in a twin, the NULL stream — is replaced by a private non-blocking stream
+// of the calling thread (one per context), which gets its own XQueue like any created stream (reference:
+// platforms/cuda/shim/src/shim.cpp:25-41, shim.h:20-62).  XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS=ON makes every
+// cuStreamCreate* hand out one shared, reference-counted stream (reference: shim.cpp:472-567).
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -19,6 +26,7 @@
 #include <memory>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 #include <cuda.h>
 
 #include "hal_cuda/cuda_command.h"
@@ -42,7 +50,8 @@ namespace {
 // ---- statistics (dumped as JSON to $XSCHED_SHIM_STATS_FILE at exit) ----
 struct Stats {
     std::atomic<uint64_t> launches_queued{0}, launches_direct{0}, copies_queued{0}, copies_direct{0}, events_queued{0},
-        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0}, copies_waited{0}, launches_blocking{0}, calls_queued{0}, graphs_queued{0};
+        syncs_via_xqueue{0}, streams_with_xqueue{0}, getproc_hooked{0}, copies_waited{0}, launches_blocking{0}, calls_queued{0}, graphs_queued{0},
+        thread_streams{0}, getproc_hooked_ptsz{0}, single_stream_refs{0};
 } g_stats;
 
 void DumpStats() {
@@ -50,13 +59,16 @@ void DumpStats() {
     if (path.empty()) return;
     if (FILE *f = std::fopen(path.c_str(), "w")) {
         std::fprintf(f, "{\"launches_queued\": %llu, \"launches_direct\": %llu, \"copies_queued\": %llu, \"copies_direct\": %llu, "
-                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu, \"copies_waited\": %llu, \"launches_blocking\": %llu, \"calls_queued\": %llu, \"graphs_queued\": %llu}\n",
+                        "\"events_queued\": %llu, \"syncs_via_xqueue\": %llu, \"streams_with_xqueue\": %llu, \"getproc_hooked\": %llu, \"copies_waited\": %llu, \"launches_blocking\": %llu, \"calls_queued\": %llu, \"graphs_queued\": %llu, "
+                        "\"thread_streams\": %llu, \"getproc_hooked_ptsz\": %llu, \"single_stream_refs\": %llu}\n",
                      (unsigned long long)g_stats.launches_queued, (unsigned long long)g_stats.launches_direct,
                      (unsigned long long)g_stats.copies_queued, (unsigned long long)g_stats.copies_direct,
                      (unsigned long long)g_stats.events_queued, (unsigned long long)g_stats.syncs_via_xqueue,
                      (unsigned long long)g_stats.streams_with_xqueue, (unsigned long long)g_stats.getproc_hooked,
                      (unsigned long long)g_stats.copies_waited, (unsigned long long)g_stats.launches_blocking,
-                     (unsigned long long)g_stats.calls_queued, (unsigned long long)g_stats.graphs_queued);
+                     (unsigned long long)g_stats.calls_queued, (unsigned long long)g_stats.graphs_queued,
+                     (unsigned long long)g_stats.thread_streams, (unsigned long long)g_stats.getproc_hooked_ptsz,
+                     (unsigned long long)g_stats.single_stream_refs);
         std::fclose(f);
     }
 }
@@ -72,6 +84,40 @@ template <class F> F Real(const char *name) {
 std::atomic<int64_t> g_capturing{0};
 
 bool IsLegacy(CUstream s) { return s == nullptr || s == CU_STREAM_LEGACY; }
+
+void AutoCreate(CUstream s);
+
+// Set while a `_ptsz` twin runs on this thread: there the NULL stream means the per-thread default stream.
+thread_local bool t_ptsz = false;
+struct PtszScope {
+    bool prev;
+    PtszScope() : prev(t_ptsz) { t_ptsz = true; }
+    ~PtszScope() { t_ptsz = prev; }
+};
+
+// The calling thread's private stand-in for the per-thread default stream in the current context.  Created on
+// first use, non-blocking, with an XQueue when XSCHED_AUTO_XQUEUE is on.  Like the reference it lives until the
+// process ends (a stream cannot be destroyed safely from a thread-exit hook once its context may be gone).
+CUstream ThreadStream() {
+    struct Entry { CUcontext ctx; CUstream stream; };
+    thread_local std::vector<Entry> mine;
+    CUcontext ctx = nullptr;
+    if (Driver().cuCtxGetCurrent(&ctx) != CUDA_SUCCESS || ctx == nullptr) return CU_STREAM_PER_THREAD;    // let the driver report it
+    for (const Entry &e : mine) if (e.ctx == ctx) return e.stream;
+    CUstream st = nullptr;
+    if (Driver().cuStreamCreateWithPriority(&st, CU_STREAM_NON_BLOCKING, 0) != CUDA_SUCCESS) return CU_STREAM_PER_THREAD;
+    AutoCreate(st);
+    mine.push_back(Entry{ctx, st});
+    g_stats.thread_streams++;
+    return st;
+}
+
+// Stream handle as the rest of a handler sees it: CU_STREAM_PER_THREAD (and NULL inside a _ptsz twin) becomes
+// the thread's private stream; NULL elsewhere stays the legacy default stream.
+CUstream Normalize(CUstream s) {
+    if (s == CU_STREAM_PER_THREAD || (s == nullptr && t_ptsz)) return ThreadStream();
+    return s;
+}
 
 // Work on the legacy default stream is ordered after everything on blocking streams: drain their XQueues.
 void DrainBlockingStreams() {
@@ -90,7 +136,7 @@ void DrainBlockingStreams() {
 std::shared_ptr<XQueue> Route(CUstream s) {
     if (g_capturing.load(std::memory_order_relaxed) > 0) return nullptr;
     if (IsLegacy(s)) { DrainBlockingStreams(); return nullptr; }
-    if (s == CU_STREAM_PER_THREAD) return nullptr;
+    if (s == CU_STREAM_PER_THREAD) return nullptr;        // only when no private stream could be made
     return HwQueueManager::GetXQueue((HwQueueHandle)(uintptr_t)s);
 }
 
@@ -118,6 +164,7 @@ extern "C" {
 
 SHIM_API CUresult CUDAAPI cuLaunchKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                                          unsigned shmem, CUstream s, void **params, void **extra) {
+    s = Normalize(s);
     REAL(cuLaunchKernel, "cuLaunchKernel");
     auto xq = Route(s);
     if (xq) {
@@ -132,6 +179,9 @@ SHIM_API CUresult CUDAAPI cuLaunchKernel(CUfunction f, unsigned gx, unsigned gy,
 
 SHIM_API CUresult CUDAAPI cuLaunchKernelEx(const CUlaunchConfig *config, CUfunction f, void **params, void **extra) {
     if (config == nullptr) return CUDA_ERROR_INVALID_VALUE;
+    CUlaunchConfig normalized = *config;
+    normalized.hStream = Normalize(config->hStream);
+    config = &normalized;
     auto xq = Route(config->hStream);
     if (xq) {
         auto cmd = std::make_shared<CudaKernelLaunchCommand>(config, f, params, extra);
@@ -159,12 +209,14 @@ static bool SubmitCall(CUstream s, const char *what, F &&call, bool blocking = f
 
 SHIM_API CUresult CUDAAPI cuLaunchCooperativeKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                                                     unsigned shmem, CUstream s, void **params) {
+    s = Normalize(s);
     REAL(cuLaunchCooperativeKernel, "cuLaunchCooperativeKernel");
     if (SubmitCall(s, "cooperative launch", [=](CUstream st) { return real(f, gx, gy, gz, bx, by, bz, shmem, st, params); }, /*blocking=*/true))
         return CUDA_SUCCESS;
     return real(f, gx, gy, gz, bx, by, bz, shmem, s, params);
 }
 SHIM_API CUresult CUDAAPI cuMemAllocAsync(CUdeviceptr *p, size_t n, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemAllocAsync, "cuMemAllocAsync");
     // Blocking: the address is read by the caller as soon as the call returns.
     auto res = std::make_shared<CUresult>(CUDA_SUCCESS);
@@ -172,6 +224,7 @@ SHIM_API CUresult CUDAAPI cuMemAllocAsync(CUdeviceptr *p, size_t n, CUstream s) 
     return real(p, n, s);
 }
 SHIM_API CUresult CUDAAPI cuMemFreeAsync(CUdeviceptr p, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemFreeAsync, "cuMemFreeAsync");
     if (SubmitCall(s, "cuMemFreeAsync", [=](CUstream st) { return real(p, st); })) return CUDA_SUCCESS;
     return real(p, s);
@@ -180,6 +233,7 @@ static bool PageableSide(CUmemorytype type, const void *host) {
     return type == CU_MEMORYTYPE_HOST && host != nullptr && IsPageableHost(host);
 }
 SHIM_API CUresult CUDAAPI cuMemcpy2DAsync(const CUDA_MEMCPY2D *c, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemcpy2DAsync, "cuMemcpy2DAsync_v2");
     if (c == nullptr) return CUDA_ERROR_INVALID_VALUE;
     auto xq = Route(s);
@@ -194,6 +248,7 @@ SHIM_API CUresult CUDAAPI cuMemcpy2DAsync(const CUDA_MEMCPY2D *c, CUstream s) {
     return CUDA_SUCCESS;
 }
 SHIM_API CUresult CUDAAPI cuMemcpy3DAsync(const CUDA_MEMCPY3D *c, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemcpy3DAsync, "cuMemcpy3DAsync_v2");
     if (c == nullptr) return CUDA_ERROR_INVALID_VALUE;
     auto xq = Route(s);
@@ -208,26 +263,31 @@ SHIM_API CUresult CUDAAPI cuMemcpy3DAsync(const CUDA_MEMCPY3D *c, CUstream s) {
     return CUDA_SUCCESS;
 }
 SHIM_API CUresult CUDAAPI cuMemcpyPeerAsync(CUdeviceptr d, CUcontext dc, CUdeviceptr sp, CUcontext sc, size_t n, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemcpyPeerAsync, "cuMemcpyPeerAsync");
     if (SubmitCall(s, "cuMemcpyPeerAsync", [=](CUstream st) { return real(d, dc, sp, sc, n, st); })) return CUDA_SUCCESS;
     return real(d, dc, sp, sc, n, s);
 }
 SHIM_API CUresult CUDAAPI cuMemsetD16Async(CUdeviceptr d, unsigned short v, size_t n, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemsetD16Async, "cuMemsetD16Async");
     if (SubmitCall(s, "cuMemsetD16Async", [=](CUstream st) { return real(d, v, n, st); })) return CUDA_SUCCESS;
     return real(d, v, n, s);
 }
 SHIM_API CUresult CUDAAPI cuMemsetD2D8Async(CUdeviceptr d, size_t pitch, unsigned char v, size_t w, size_t h, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemsetD2D8Async, "cuMemsetD2D8Async");
     if (SubmitCall(s, "cuMemsetD2D8Async", [=](CUstream st) { return real(d, pitch, v, w, h, st); })) return CUDA_SUCCESS;
     return real(d, pitch, v, w, h, s);
 }
 SHIM_API CUresult CUDAAPI cuMemsetD2D16Async(CUdeviceptr d, size_t pitch, unsigned short v, size_t w, size_t h, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemsetD2D16Async, "cuMemsetD2D16Async");
     if (SubmitCall(s, "cuMemsetD2D16Async", [=](CUstream st) { return real(d, pitch, v, w, h, st); })) return CUDA_SUCCESS;
     return real(d, pitch, v, w, h, s);
 }
 SHIM_API CUresult CUDAAPI cuMemsetD2D32Async(CUdeviceptr d, size_t pitch, unsigned v, size_t w, size_t h, CUstream s) {
+    s = Normalize(s);
     REAL(cuMemsetD2D32Async, "cuMemsetD2D32Async");
     if (SubmitCall(s, "cuMemsetD2D32Async", [=](CUstream st) { return real(d, pitch, v, w, h, st); })) return CUDA_SUCCESS;
     return real(d, pitch, v, w, h, s);
@@ -235,16 +295,19 @@ SHIM_API CUresult CUDAAPI cuMemsetD2D32Async(CUdeviceptr d, size_t pitch, unsign
 // A graph launch is one command of the stream's XQueue: it takes part in the window, and the scheduler
 // sees the queue as busy while the graph runs.
 SHIM_API CUresult CUDAAPI cuGraphLaunch(CUgraphExec g, CUstream s) {
+    s = Normalize(s);
     REAL(cuGraphLaunch, "cuGraphLaunch");
     if (SubmitCall(s, "cuGraphLaunch", [=](CUstream st) { return real(g, st); })) { g_stats.graphs_queued++; return CUDA_SUCCESS; }
     return real(g, s);
 }
 SHIM_API CUresult CUDAAPI cuGraphUpload(CUgraphExec g, CUstream s) {
+    s = Normalize(s);
     REAL(cuGraphUpload, "cuGraphUpload");
     if (SubmitCall(s, "cuGraphUpload", [=](CUstream st) { return real(g, st); })) return CUDA_SUCCESS;
     return real(g, s);
 }
 SHIM_API CUresult CUDAAPI cuStreamAddCallback(CUstream s, CUstreamCallback cb, void *data, unsigned flags) {
+    s = Normalize(s);
     REAL(cuStreamAddCallback, "cuStreamAddCallback");
     if (SubmitCall(s, "cuStreamAddCallback", [=](CUstream st) { return real(st, cb, data, flags); })) return CUDA_SUCCESS;
     return real(s, cb, data, flags);
@@ -272,6 +335,7 @@ SHIM_API CUresult CUDAAPI cuMemcpyDtoD(CUdeviceptr d, CUdeviceptr sp, size_t n) 
 }
 
 static CUresult CopyCommon(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t n, CUstream s) {
+    s = Normalize(s);
     auto xq = Route(s);
     if (xq) {
         // Pageable host memory makes the copy synchronous for its caller (the source may be reused, the
@@ -306,20 +370,24 @@ SHIM_API CUresult CUDAAPI cuMemcpyDtoHAsync(void *dst, CUdeviceptr src, size_t n
 SHIM_API CUresult CUDAAPI cuMemcpyDtoDAsync(CUdeviceptr dst, CUdeviceptr src, size_t n, CUstream s) { return CopyCommon(CopyKind::kDtoD, dst, src, n, s); }
 
 SHIM_API CUresult CUDAAPI cuMemsetD8Async(CUdeviceptr dst, unsigned char v, size_t n, CUstream s) {
+    s = Normalize(s);
     if (auto xq = Route(s)) { xq->Submit(std::make_shared<CudaMemsetCommand>(dst, v, n, 1)); return CUDA_SUCCESS; }
     return Driver().cuMemsetD8Async(dst, v, n, s);
 }
 SHIM_API CUresult CUDAAPI cuMemsetD32Async(CUdeviceptr dst, unsigned v, size_t n, CUstream s) {
+    s = Normalize(s);
     if (auto xq = Route(s)) { xq->Submit(std::make_shared<CudaMemsetCommand>(dst, v, n, 4)); return CUDA_SUCCESS; }
     return Driver().cuMemsetD32Async(dst, v, n, s);
 }
 
 SHIM_API CUresult CUDAAPI cuLaunchHostFunc(CUstream s, CUhostFn fn, void *data) {
+    s = Normalize(s);
     if (auto xq = Route(s)) { xq->Submit(std::make_shared<CudaHostFuncCommand>(fn, data)); return CUDA_SUCCESS; }
     return Driver().cuLaunchHostFunc(s, fn, data);
 }
 
 SHIM_API CUresult CUDAAPI cuEventRecord(CUevent ev, CUstream s) {
+    s = Normalize(s);
     auto xq = Route(s);
     if (!xq) {
         { std::lock_guard<std::mutex> lk(g_ev_mu); g_events.erase(ev); }
@@ -333,6 +401,7 @@ SHIM_API CUresult CUDAAPI cuEventRecord(CUevent ev, CUstream s) {
 }
 
 SHIM_API CUresult CUDAAPI cuEventRecordWithFlags(CUevent ev, CUstream s, unsigned flags) {
+    s = Normalize(s);
     REAL(cuEventRecordWithFlags, "cuEventRecordWithFlags");
     auto xq = Route(s);
     if (!xq) {
@@ -368,6 +437,7 @@ SHIM_API CUresult CUDAAPI cuEventDestroy(CUevent ev) {
 }
 
 SHIM_API CUresult CUDAAPI cuStreamWaitEvent(CUstream s, CUevent ev, unsigned flags) {
+    s = Normalize(s);
     auto rec = FindRecord(ev);
     auto xq = Route(s);
     if (xq) {
@@ -382,6 +452,7 @@ SHIM_API CUresult CUDAAPI cuStreamWaitEvent(CUstream s, CUevent ev, unsigned fla
 // stream-ordered calls that are not turned into commands (the generated trampolines) are only known to the
 // driver.  (The reference stops after the XQueue, platforms/cuda/shim/src/shim.cpp:413-419.)
 SHIM_API CUresult CUDAAPI cuStreamSynchronize(CUstream s) {
+    s = Normalize(s);
     if (auto xq = Route(s)) {
         xq->WaitAll();
         g_stats.syncs_via_xqueue++;
@@ -390,6 +461,7 @@ SHIM_API CUresult CUDAAPI cuStreamSynchronize(CUstream s) {
 }
 
 SHIM_API CUresult CUDAAPI cuStreamQuery(CUstream s) {
+    s = Normalize(s);
     if (auto xq = Route(s)) {
         if (xq->Query() != kQueueStateIdle) return CUDA_ERROR_NOT_READY;
     }
@@ -406,20 +478,54 @@ SHIM_API CUresult CUDAAPI cuMemFree(CUdeviceptr p) {
     return Driver().cuMemFree(p);
 }
 
+// XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS=ON: every stream the program creates is the same stream (the first
+// creation makes it, with that call's flags and priority; later ones add a reference), so the whole process is
+// one XQueue and its work is serialised; the stream is destroyed with its last reference.
+static std::mutex g_single_mu;
+static CUstream g_single_stream = nullptr;
+static int64_t g_single_refs = 0;
+static bool SingleStreamMode() {
+    static const bool on = GetEnvOption(XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS_ENV_NAME, false);
+    return on;
+}
+extern "C++" {
+template <class Create> static CUresult CreateStream(CUstream *s, Create &&create) {
+    if (s == nullptr) return CUDA_ERROR_INVALID_VALUE;
+    if (!SingleStreamMode()) {
+        const CUresult r = create(s);
+        if (r == CUDA_SUCCESS) AutoCreate(*s);
+        return r;
+    }
+    std::lock_guard<std::mutex> lk(g_single_mu);
+    if (g_single_refs == 0) {
+        const CUresult r = create(&g_single_stream);
+        if (r != CUDA_SUCCESS) return r;
+        AutoCreate(g_single_stream);
+    }
+    ++g_single_refs;
+    g_stats.single_stream_refs++;
+    *s = g_single_stream;
+    return CUDA_SUCCESS;
+}
+} // extern "C++"
+
 SHIM_API CUresult CUDAAPI cuStreamCreate(CUstream *s, unsigned flags) {
     REAL(cuStreamCreate, "cuStreamCreate");
-    const CUresult r = real(s, flags);
-    if (r == CUDA_SUCCESS) AutoCreate(*s);
-    return r;
+    return CreateStream(s, [&](CUstream *out) { return real(out, flags); });
 }
 
 SHIM_API CUresult CUDAAPI cuStreamCreateWithPriority(CUstream *s, unsigned flags, int prio) {
-    const CUresult r = Driver().cuStreamCreateWithPriority(s, flags, prio);
-    if (r == CUDA_SUCCESS) AutoCreate(*s);
-    return r;
+    return CreateStream(s, [&](CUstream *out) { return Driver().cuStreamCreateWithPriority(out, flags, prio); });
 }
 
 SHIM_API CUresult CUDAAPI cuStreamDestroy(CUstream s) {
+    if (SingleStreamMode()) {
+        std::lock_guard<std::mutex> lk(g_single_mu);
+        if (s == g_single_stream && g_single_refs > 0) {
+            if (--g_single_refs > 0) return CUDA_SUCCESS;
+            g_single_stream = nullptr;
+        }
+    }
     if (HwQueueManager::GetXQueue((HwQueueHandle)(uintptr_t)s)) XQueueManager::AutoDestroy((HwQueueHandle)(uintptr_t)s);
     return Driver().cuStreamDestroy(s);
 }
@@ -441,6 +547,7 @@ static void CaptureEnded() {
 }
 
 SHIM_API CUresult CUDAAPI cuStreamBeginCapture(CUstream s, CUstreamCaptureMode mode) {
+    s = Normalize(s);
     REAL(cuStreamBeginCapture, "cuStreamBeginCapture_v2");
     CaptureBegins();
     const CUresult r = real(s, mode);
@@ -450,6 +557,7 @@ SHIM_API CUresult CUDAAPI cuStreamBeginCapture(CUstream s, CUstreamCaptureMode m
 
 SHIM_API CUresult CUDAAPI cuStreamBeginCaptureToGraph(CUstream s, CUgraph g, const CUgraphNode *deps, const CUgraphEdgeData *dep_data, size_t n_deps,
                                                       CUstreamCaptureMode mode) {
+    s = Normalize(s);
     REAL(cuStreamBeginCaptureToGraph, "cuStreamBeginCaptureToGraph");
     CaptureBegins();
     const CUresult r = real(s, g, deps, dep_data, n_deps, mode);
@@ -460,6 +568,7 @@ SHIM_API CUresult CUDAAPI cuStreamBeginCaptureToGraph(CUstream s, CUgraph g, con
 // The counter goes down only when this call really ended a capture: ending on the wrong stream, or on one that
 // was not capturing, leaves the capture (and the bypass) in place.
 SHIM_API CUresult CUDAAPI cuStreamEndCapture(CUstream s, CUgraph *g) {
+    s = Normalize(s);
     REAL(cuStreamEndCapture, "cuStreamEndCapture");
     using IsCapturingFn = CUresult (*)(CUstream, CUstreamCaptureStatus *);
     static const IsCapturingFn is_capturing = (IsCapturingFn)Driver().Sym("cuStreamIsCapturing");
@@ -473,51 +582,104 @@ SHIM_API CUresult CUDAAPI cuStreamEndCapture(CUstream s, CUgraph *g) {
     return r;
 }
 
+
+// ---- per-thread-default-stream twins --------------------------------------------------------------------
+// Same handlers; while one runs, the NULL stream means "this thread's default stream" (Normalize()).  The
+// synchronous copies (`_ptds`) are ordered after everything this process has queued, then go to the driver.
+#define XSHIM_TWIN(call) { PtszScope in_twin; return call; }
+SHIM_API CUresult CUDAAPI cuLaunchKernel_ptsz(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz, unsigned shmem,
+                                              CUstream s, void **params, void **extra) XSHIM_TWIN(cuLaunchKernel(f, gx, gy, gz, bx, by, bz, shmem, s, params, extra))
+SHIM_API CUresult CUDAAPI cuLaunchKernelEx_ptsz(const CUlaunchConfig *c, CUfunction f, void **params, void **extra) XSHIM_TWIN(cuLaunchKernelEx(c, f, params, extra))
+SHIM_API CUresult CUDAAPI cuLaunchCooperativeKernel_ptsz(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz, unsigned shmem,
+                                                         CUstream s, void **params) XSHIM_TWIN(cuLaunchCooperativeKernel(f, gx, gy, gz, bx, by, bz, shmem, s, params))
+SHIM_API CUresult CUDAAPI cuLaunchHostFunc_ptsz(CUstream s, CUhostFn fn, void *data) XSHIM_TWIN(cuLaunchHostFunc(s, fn, data))
+SHIM_API CUresult CUDAAPI cuMemAllocAsync_ptsz(CUdeviceptr *p, size_t n, CUstream s) XSHIM_TWIN(cuMemAllocAsync(p, n, s))
+SHIM_API CUresult CUDAAPI cuMemFreeAsync_ptsz(CUdeviceptr p, CUstream s) XSHIM_TWIN(cuMemFreeAsync(p, s))
+SHIM_API CUresult CUDAAPI cuMemcpyAsync_ptsz(CUdeviceptr d, CUdeviceptr sp, size_t n, CUstream s) XSHIM_TWIN(cuMemcpyAsync(d, sp, n, s))
+SHIM_API CUresult CUDAAPI cuMemcpyHtoDAsync_v2_ptsz(CUdeviceptr d, const void *sp, size_t n, CUstream s) XSHIM_TWIN(cuMemcpyHtoDAsync(d, sp, n, s))
+SHIM_API CUresult CUDAAPI cuMemcpyDtoHAsync_v2_ptsz(void *d, CUdeviceptr sp, size_t n, CUstream s) XSHIM_TWIN(cuMemcpyDtoHAsync(d, sp, n, s))
+SHIM_API CUresult CUDAAPI cuMemcpyDtoDAsync_v2_ptsz(CUdeviceptr d, CUdeviceptr sp, size_t n, CUstream s) XSHIM_TWIN(cuMemcpyDtoDAsync(d, sp, n, s))
+SHIM_API CUresult CUDAAPI cuMemcpy2DAsync_v2_ptsz(const CUDA_MEMCPY2D *c, CUstream s) XSHIM_TWIN(cuMemcpy2DAsync(c, s))
+SHIM_API CUresult CUDAAPI cuMemcpy3DAsync_v2_ptsz(const CUDA_MEMCPY3D *c, CUstream s) XSHIM_TWIN(cuMemcpy3DAsync(c, s))
+SHIM_API CUresult CUDAAPI cuMemcpyPeerAsync_ptsz(CUdeviceptr d, CUcontext dc, CUdeviceptr sp, CUcontext sc, size_t n, CUstream s) XSHIM_TWIN(cuMemcpyPeerAsync(d, dc, sp, sc, n, s))
+SHIM_API CUresult CUDAAPI cuMemsetD8Async_ptsz(CUdeviceptr d, unsigned char v, size_t n, CUstream s) XSHIM_TWIN(cuMemsetD8Async(d, v, n, s))
+SHIM_API CUresult CUDAAPI cuMemsetD16Async_ptsz(CUdeviceptr d, unsigned short v, size_t n, CUstream s) XSHIM_TWIN(cuMemsetD16Async(d, v, n, s))
+SHIM_API CUresult CUDAAPI cuMemsetD32Async_ptsz(CUdeviceptr d, unsigned v, size_t n, CUstream s) XSHIM_TWIN(cuMemsetD32Async(d, v, n, s))
+SHIM_API CUresult CUDAAPI cuMemsetD2D8Async_ptsz(CUdeviceptr d, size_t pitch, unsigned char v, size_t w, size_t h, CUstream s) XSHIM_TWIN(cuMemsetD2D8Async(d, pitch, v, w, h, s))
+SHIM_API CUresult CUDAAPI cuMemsetD2D16Async_ptsz(CUdeviceptr d, size_t pitch, unsigned short v, size_t w, size_t h, CUstream s) XSHIM_TWIN(cuMemsetD2D16Async(d, pitch, v, w, h, s))
+SHIM_API CUresult CUDAAPI cuMemsetD2D32Async_ptsz(CUdeviceptr d, size_t pitch, unsigned v, size_t w, size_t h, CUstream s) XSHIM_TWIN(cuMemsetD2D32Async(d, pitch, v, w, h, s))
+SHIM_API CUresult CUDAAPI cuGraphLaunch_ptsz(CUgraphExec g, CUstream s) XSHIM_TWIN(cuGraphLaunch(g, s))
+SHIM_API CUresult CUDAAPI cuGraphUpload_ptsz(CUgraphExec g, CUstream s) XSHIM_TWIN(cuGraphUpload(g, s))
+SHIM_API CUresult CUDAAPI cuStreamAddCallback_ptsz(CUstream s, CUstreamCallback cb, void *data, unsigned flags) XSHIM_TWIN(cuStreamAddCallback(s, cb, data, flags))
+SHIM_API CUresult CUDAAPI cuEventRecord_ptsz(CUevent ev, CUstream s) XSHIM_TWIN(cuEventRecord(ev, s))
+SHIM_API CUresult CUDAAPI cuEventRecordWithFlags_ptsz(CUevent ev, CUstream s, unsigned flags) XSHIM_TWIN(cuEventRecordWithFlags(ev, s, flags))
+SHIM_API CUresult CUDAAPI cuStreamWaitEvent_ptsz(CUstream s, CUevent ev, unsigned flags) XSHIM_TWIN(cuStreamWaitEvent(s, ev, flags))
+SHIM_API CUresult CUDAAPI cuStreamSynchronize_ptsz(CUstream s) XSHIM_TWIN(cuStreamSynchronize(s))
+SHIM_API CUresult CUDAAPI cuStreamQuery_ptsz(CUstream s) XSHIM_TWIN(cuStreamQuery(s))
+SHIM_API CUresult CUDAAPI cuStreamBeginCapture_v2_ptsz(CUstream s, CUstreamCaptureMode mode) XSHIM_TWIN(cuStreamBeginCapture(s, mode))
+SHIM_API CUresult CUDAAPI cuStreamBeginCaptureToGraph_ptsz(CUstream s, CUgraph g, const CUgraphNode *deps, const CUgraphEdgeData *dep_data, size_t n_deps,
+                                                           CUstreamCaptureMode mode) XSHIM_TWIN(cuStreamBeginCaptureToGraph(s, g, deps, dep_data, n_deps, mode))
+SHIM_API CUresult CUDAAPI cuStreamEndCapture_ptsz(CUstream s, CUgraph *g) XSHIM_TWIN(cuStreamEndCapture(s, g))
+#undef XSHIM_TWIN
+#define XSHIM_SYNC_COPY_PTDS(name, sym, params, args)                                              \
+    SHIM_API CUresult CUDAAPI name params {                                                        \
+        typedef CUresult(CUDAAPI * Fn) params;                                                     \
+        static const Fn real = Real<Fn>(sym);                                                      \
+        if (g_capturing.load() == 0) XQueueManager::ForEachWaitAll();                              \
+        return real args;                                                                          \
+    }
+XSHIM_SYNC_COPY_PTDS(cuMemcpy_ptds, "cuMemcpy_ptds", (CUdeviceptr d, CUdeviceptr sp, size_t n), (d, sp, n))
+XSHIM_SYNC_COPY_PTDS(cuMemcpyDtoH_v2_ptds, "cuMemcpyDtoH_v2_ptds", (void *d, CUdeviceptr sp, size_t n), (d, sp, n))
+XSHIM_SYNC_COPY_PTDS(cuMemcpyHtoD_v2_ptds, "cuMemcpyHtoD_v2_ptds", (CUdeviceptr d, const void *sp, size_t n), (d, sp, n))
+XSHIM_SYNC_COPY_PTDS(cuMemcpyDtoD_v2_ptds, "cuMemcpyDtoD_v2_ptds", (CUdeviceptr d, CUdeviceptr sp, size_t n), (d, sp, n))
+#undef XSHIM_SYNC_COPY_PTDS
+
 // ---- cuGetProcAddress: the CUDA runtime resolves everything through it ----
-struct Hook { const char *name; void *fn; int min_version; };
+// `twin` answers lookups made with CU_GET_PROC_ADDRESS_PER_THREAD_DEFAULT_STREAM (nullptr: the plain handler has no stream).
+struct Hook { const char *name; void *fn; int min_version; void *twin; };
 static const Hook kHooks[] = {
-    {"cuLaunchKernel", (void *)&cuLaunchKernel, 4000},
-    {"cuLaunchKernelEx", (void *)&cuLaunchKernelEx, 11060},
-    {"cuLaunchCooperativeKernel", (void *)&cuLaunchCooperativeKernel, 9000},
-    {"cuMemAllocAsync", (void *)&cuMemAllocAsync, 11020},
-    {"cuMemFreeAsync", (void *)&cuMemFreeAsync, 11020},
-    {"cuMemcpy2DAsync", (void *)&cuMemcpy2DAsync, 3020},
-    {"cuMemcpy3DAsync", (void *)&cuMemcpy3DAsync, 3020},
-    {"cuMemsetD2D8Async", (void *)&cuMemsetD2D8Async, 3020},
-    {"cuMemsetD2D16Async", (void *)&cuMemsetD2D16Async, 3020},
-    {"cuMemsetD2D32Async", (void *)&cuMemsetD2D32Async, 3020},
-    {"cuGraphUpload", (void *)&cuGraphUpload, 11010},
-    {"cuEventRecordWithFlags", (void *)&cuEventRecordWithFlags, 11010},
-    {"cuMemcpyPeerAsync", (void *)&cuMemcpyPeerAsync, 4000},
-    {"cuMemsetD16Async", (void *)&cuMemsetD16Async, 3020},
-    {"cuGraphLaunch", (void *)&cuGraphLaunch, 10000},
-    {"cuStreamAddCallback", (void *)&cuStreamAddCallback, 5000},
-    {"cuMemcpy", (void *)&cuMemcpy, 4000},
-    {"cuMemcpyDtoH", (void *)&cuMemcpyDtoH, 3020},
-    {"cuMemcpyHtoD", (void *)&cuMemcpyHtoD, 3020},
-    {"cuMemcpyDtoD", (void *)&cuMemcpyDtoD, 3020},
-    {"cuMemcpyAsync", (void *)&cuMemcpyAsync, 4000},
-    {"cuMemcpyHtoDAsync", (void *)&cuMemcpyHtoDAsync, 3020},
-    {"cuMemcpyDtoHAsync", (void *)&cuMemcpyDtoHAsync, 3020},
-    {"cuMemcpyDtoDAsync", (void *)&cuMemcpyDtoDAsync, 3020},
-    {"cuMemsetD8Async", (void *)&cuMemsetD8Async, 3020},
-    {"cuMemsetD32Async", (void *)&cuMemsetD32Async, 3020},
-    {"cuLaunchHostFunc", (void *)&cuLaunchHostFunc, 10000},
-    {"cuEventRecord", (void *)&cuEventRecord, 2000},
-    {"cuEventSynchronize", (void *)&cuEventSynchronize, 2000},
-    {"cuEventQuery", (void *)&cuEventQuery, 2000},
-    {"cuEventDestroy", (void *)&cuEventDestroy, 4000},
-    {"cuStreamWaitEvent", (void *)&cuStreamWaitEvent, 3020},
-    {"cuStreamSynchronize", (void *)&cuStreamSynchronize, 2000},
-    {"cuStreamQuery", (void *)&cuStreamQuery, 2000},
-    {"cuCtxSynchronize", (void *)&cuCtxSynchronize, 2000},
-    {"cuMemFree", (void *)&cuMemFree, 3020},
-    {"cuStreamCreate", (void *)&cuStreamCreate, 2000},
-    {"cuStreamCreateWithPriority", (void *)&cuStreamCreateWithPriority, 5050},
-    {"cuStreamDestroy", (void *)&cuStreamDestroy, 4000},
-    {"cuStreamBeginCapture", (void *)&cuStreamBeginCapture, 10010},
-    {"cuStreamBeginCaptureToGraph", (void *)&cuStreamBeginCaptureToGraph, 12030},
-    {"cuStreamEndCapture", (void *)&cuStreamEndCapture, 10000},
+    {"cuLaunchKernel", (void *)&cuLaunchKernel, 4000, (void *)&cuLaunchKernel_ptsz},
+    {"cuLaunchKernelEx", (void *)&cuLaunchKernelEx, 11060, (void *)&cuLaunchKernelEx_ptsz},
+    {"cuLaunchCooperativeKernel", (void *)&cuLaunchCooperativeKernel, 9000, (void *)&cuLaunchCooperativeKernel_ptsz},
+    {"cuMemAllocAsync", (void *)&cuMemAllocAsync, 11020, (void *)&cuMemAllocAsync_ptsz},
+    {"cuMemFreeAsync", (void *)&cuMemFreeAsync, 11020, (void *)&cuMemFreeAsync_ptsz},
+    {"cuMemcpy2DAsync", (void *)&cuMemcpy2DAsync, 3020, (void *)&cuMemcpy2DAsync_v2_ptsz},
+    {"cuMemcpy3DAsync", (void *)&cuMemcpy3DAsync, 3020, (void *)&cuMemcpy3DAsync_v2_ptsz},
+    {"cuMemsetD2D8Async", (void *)&cuMemsetD2D8Async, 3020, (void *)&cuMemsetD2D8Async_ptsz},
+    {"cuMemsetD2D16Async", (void *)&cuMemsetD2D16Async, 3020, (void *)&cuMemsetD2D16Async_ptsz},
+    {"cuMemsetD2D32Async", (void *)&cuMemsetD2D32Async, 3020, (void *)&cuMemsetD2D32Async_ptsz},
+    {"cuGraphUpload", (void *)&cuGraphUpload, 11010, (void *)&cuGraphUpload_ptsz},
+    {"cuEventRecordWithFlags", (void *)&cuEventRecordWithFlags, 11010, (void *)&cuEventRecordWithFlags_ptsz},
+    {"cuMemcpyPeerAsync", (void *)&cuMemcpyPeerAsync, 4000, (void *)&cuMemcpyPeerAsync_ptsz},
+    {"cuMemsetD16Async", (void *)&cuMemsetD16Async, 3020, (void *)&cuMemsetD16Async_ptsz},
+    {"cuGraphLaunch", (void *)&cuGraphLaunch, 10000, (void *)&cuGraphLaunch_ptsz},
+    {"cuStreamAddCallback", (void *)&cuStreamAddCallback, 5000, (void *)&cuStreamAddCallback_ptsz},
+    {"cuMemcpy", (void *)&cuMemcpy, 4000, (void *)&cuMemcpy_ptds},
+    {"cuMemcpyDtoH", (void *)&cuMemcpyDtoH, 3020, (void *)&cuMemcpyDtoH_v2_ptds},
+    {"cuMemcpyHtoD", (void *)&cuMemcpyHtoD, 3020, (void *)&cuMemcpyHtoD_v2_ptds},
+    {"cuMemcpyDtoD", (void *)&cuMemcpyDtoD, 3020, (void *)&cuMemcpyDtoD_v2_ptds},
+    {"cuMemcpyAsync", (void *)&cuMemcpyAsync, 4000, (void *)&cuMemcpyAsync_ptsz},
+    {"cuMemcpyHtoDAsync", (void *)&cuMemcpyHtoDAsync, 3020, (void *)&cuMemcpyHtoDAsync_v2_ptsz},
+    {"cuMemcpyDtoHAsync", (void *)&cuMemcpyDtoHAsync, 3020, (void *)&cuMemcpyDtoHAsync_v2_ptsz},
+    {"cuMemcpyDtoDAsync", (void *)&cuMemcpyDtoDAsync, 3020, (void *)&cuMemcpyDtoDAsync_v2_ptsz},
+    {"cuMemsetD8Async", (void *)&cuMemsetD8Async, 3020, (void *)&cuMemsetD8Async_ptsz},
+    {"cuMemsetD32Async", (void *)&cuMemsetD32Async, 3020, (void *)&cuMemsetD32Async_ptsz},
+    {"cuLaunchHostFunc", (void *)&cuLaunchHostFunc, 10000, (void *)&cuLaunchHostFunc_ptsz},
+    {"cuEventRecord", (void *)&cuEventRecord, 2000, (void *)&cuEventRecord_ptsz},
+    {"cuEventSynchronize", (void *)&cuEventSynchronize, 2000, nullptr},
+    {"cuEventQuery", (void *)&cuEventQuery, 2000, nullptr},
+    {"cuEventDestroy", (void *)&cuEventDestroy, 4000, nullptr},
+    {"cuStreamWaitEvent", (void *)&cuStreamWaitEvent, 3020, (void *)&cuStreamWaitEvent_ptsz},
+    {"cuStreamSynchronize", (void *)&cuStreamSynchronize, 2000, (void *)&cuStreamSynchronize_ptsz},
+    {"cuStreamQuery", (void *)&cuStreamQuery, 2000, (void *)&cuStreamQuery_ptsz},
+    {"cuCtxSynchronize", (void *)&cuCtxSynchronize, 2000, nullptr},
+    {"cuMemFree", (void *)&cuMemFree, 3020, nullptr},
+    {"cuStreamCreate", (void *)&cuStreamCreate, 2000, nullptr},
+    {"cuStreamCreateWithPriority", (void *)&cuStreamCreateWithPriority, 5050, nullptr},
+    {"cuStreamDestroy", (void *)&cuStreamDestroy, 4000, nullptr},
+    {"cuStreamBeginCapture", (void *)&cuStreamBeginCapture, 10010, (void *)&cuStreamBeginCapture_v2_ptsz},
+    {"cuStreamBeginCaptureToGraph", (void *)&cuStreamBeginCaptureToGraph, 12030, (void *)&cuStreamBeginCaptureToGraph_ptsz},
+    {"cuStreamEndCapture", (void *)&cuStreamEndCapture, 10000, (void *)&cuStreamEndCapture_ptsz},
 };
 
 static void *FindHook(const char *symbol, int version, cuuint64_t flags);
@@ -541,14 +703,17 @@ SHIM_API CUresult CUDAAPI cuGetProcAddress(const char *symbol, void **pfn, int v
 }
 
 static void *FindHook(const char *symbol, int version, cuuint64_t flags) {
-    // Per-thread-default-stream entry points are left to the driver (their NULL stream is not the legacy one).
-    if (flags & CU_GET_PROC_ADDRESS_PER_THREAD_DEFAULT_STREAM) return nullptr;
+    const bool per_thread = (flags & CU_GET_PROC_ADDRESS_PER_THREAD_DEFAULT_STREAM) != 0;
     if (std::strcmp(symbol, "cuGetProcAddress") == 0) {
         extern CUresult CUDAAPI cuGetProcAddress_v2(const char *, void **, int, cuuint64_t, CUdriverProcAddressQueryResult *);
         return version >= 12000 ? (void *)&cuGetProcAddress_v2 : (void *)&cuGetProcAddress;
     }
-    for (const Hook &h : kHooks)
-        if (std::strcmp(symbol, h.name) == 0) return version >= h.min_version ? h.fn : nullptr;
+    for (const Hook &h : kHooks) {
+        if (std::strcmp(symbol, h.name) != 0) continue;
+        if (version < h.min_version) return nullptr;
+        if (per_thread && h.twin) { g_stats.getproc_hooked_ptsz++; return h.twin; }
+        return h.fn;       // entry points without a stream argument are the same in both modes
+    }
     return nullptr;
 }
 

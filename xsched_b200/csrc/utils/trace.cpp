@@ -30,7 +30,8 @@ struct State {
         std::atexit([] { TraceFlush(); });
     }
 };
-State &S() { static State s; return s; }
+// Never destroyed: the flush registered with atexit runs after function-local statics would have gone.
+State &S() { static State *s = new State; return *s; }
 
 const char *const kNames[] = {"none", "ready_sent", "idle_sent", "event_recv", "decision", "op_sent", "op_recv", "suspend_begin", "suspend_end",
                               "resume_begin", "resume_end", "deactivate_issued", "hwq_synced", "task_gpu_times", "gpu_clock_offset", "app_submit",
