@@ -262,7 +262,11 @@ def load_traces(prefix: str) -> dict[int, list[tuple[int, str, int, int]]]:
                     rows.append((int(t[0]), t[1], int(t[2]), int(t[3])))
         rows.sort()
         out[pid] = rows
-        os.unlink(f)
+        keep = os.environ.get("XSCHED_BENCH_KEEP_TRACES")       # debugging: a directory that receives the raw files
+        if keep:
+            os.replace(f, os.path.join(keep, os.path.basename(f)))
+        else:
+            os.unlink(f)
     return out
 
 

@@ -65,6 +65,9 @@ public:
     /// Block until every operation issued so far was acknowledged (OperationComplete).
     void WaitAllOperations();
     uint64_t Rounds() const { return rounds_.load(); }
+    /// Id for an operation that is sent to `pid` from outside the policy loop (a configuration change asked for
+    /// over the control interface); 0 when the process is unknown.
+    uint64_t NextOperationId(PID pid);
 
     /// Threadless operation (used by the server's polling loop instead of Run()): apply `n` events and
     /// run one policy round on the calling thread.  With n == 0 only due timers are served.

@@ -26,7 +26,7 @@ enum EventType : int32_t {
 };
 enum HintType : int32_t {
     kHintTypeUnknown = 0, kHintTypePriority = 1, kHintTypeUtilization = 2, kHintTypeTimeslice = 3,
-    kHintTypeDeadline = 4, kHintTypeKDeadline = 5, kHintTypeLaxity = 6, kHintTypeWindowActive = 7,
+    kHintTypeDeadline = 4, kHintTypeKDeadline = 5, kHintTypeLaxity = 6, kHintTypeWindowActive = 7, kHintTypeMax = 8,
 };
 enum OperationType : int32_t { kOperationNone = 0, kOperationTerminate = 1, kOperationSched = 2, kOperationConfig = 4 };
 typedef uint64_t OperationId;

@@ -149,6 +149,13 @@ def build_host(force: bool = False, verbose: bool = False) -> list[Path]:
             _run([CXX, *CXX_FLAGS, "-fPIE", *incs, "-o", out, *server_srcs, f"-L{LIB}", "-Wl,-rpath,$ORIGIN",
                   "-lpreempt", "-ldl", "-lrt"], verbose)
         outs.append(out)
+    cli_srcs = sorted((CSRC / "cli").glob("*.cpp"))
+    if cli_srcs:
+        out = LIB / "xcli"
+        http_src = CSRC / "server" / "http.cpp"
+        if force or _stale(out, cli_srcs + [http_src] + hdrs + [LIB / "libpreempt.so"]):
+            _run([CXX, *CXX_FLAGS, "-fPIE", *incs, "-o", out, *cli_srcs, http_src, f"-L{LIB}", "-Wl,-rpath,$ORIGIN", "-lpreempt", "-ldl", "-lrt"], verbose)
+        outs.append(out)
     # libcuda.so.1 / libcuda.so names the dynamic loader looks for when the shim directory is put on
     # LD_LIBRARY_PATH (same install layout as the reference: platforms/cuda/CMakeLists.txt:2-5).
     shim = LIB / "libshimcuda.so"

@@ -160,6 +160,12 @@ void LocalScheduler::StepInline(const Event *events, size_t n) {
     rounds_.fetch_add(1);
 }
 
+uint64_t LocalScheduler::NextOperationId(PID pid) {
+    std::lock_guard<std::mutex> lk(op_mtx_);
+    auto it = ops_.find(pid);
+    return it == ops_.end() ? 0 : ++it->second.issued;
+}
+
 int64_t LocalScheduler::NextTimerUs() const {
     return timers_.empty() ? INT64_MAX : timers_.front();
 }
