@@ -69,14 +69,24 @@ public:
 
 /// Highest priority first, decided per device: a queue is suspended iff a READY queue with a strictly
 /// higher priority exists on the same device.  Unknown priority = 0; hints are clamped to [-255, 255].
+///
+/// Resume hysteresis (an addition, off unless XSCHED_HPF_RESUME_HYSTERESIS_US > 0 in the scheduler's process): a
+/// queue that has just gone idle still counts as ready for that many microseconds, so that lower priorities are
+/// not resumed into the short gaps of a high-priority task that submits, waits and submits again (a decode loop
+/// reads one token back per step) only to be preempted again at once; a timer re-runs the decision when the
+/// window ends.  With 0 the decisions are exactly the reference's.
 class HighestPriorityFirstPolicy final : public Policy {
 public:
-    HighestPriorityFirstPolicy() : Policy(kPolicyHighestPriorityFirst) {}
+    HighestPriorityFirstPolicy();
+    explicit HighestPriorityFirstPolicy(int64_t resume_hysteresis_us) : Policy(kPolicyHighestPriorityFirst), hysteresis_us_(resume_hysteresis_us) {}
     void Sched(const Status &status, int64_t now_us, Decision &out) override;
     void RecvHint(const void *hint, size_t size) override;
     Priority GetPriority(XQueueHandle h) const;
 private:
     std::unordered_map<XQueueHandle, Priority> prio_;
+    int64_t hysteresis_us_ = 0;
+    std::unordered_map<XQueueHandle, int64_t> idle_since_;      // queues seen ready before and idle now -> when that was noticed
+    std::unordered_map<XQueueHandle, bool> was_ready_;
 };
 
 /// Laxity ("LLF"): a ready queue runs at lax_prio until ready_time + laxity has passed and at crit_prio

@@ -93,6 +93,14 @@ const char *xpkResultString(xpkResult r);
 xpkResult xpkFlagCreate(uint32_t **flag_dev);
 xpkResult xpkFlagDestroy(uint32_t *flag_dev);
 xpkResult xpkFlagSet(uint32_t *flag_dev, uint32_t value, void *ctrl_stream);
+/* A stream write needs 6-14 us to reach device memory.  A flag (256 bytes from xpkFlagCreate, or any zeroed
+ * 16-byte-aligned block whose first word is the flag) can be given an early-warning word in mapped host memory:
+ * the caller stores a non-zero value there (a plain host store, on the GPU within about 2 us) immediately before
+ * xpkFlagSet(flag, 1, ..), and zero before lowering the flag.  Kernels that run a relay (the GEMM) copy the raised
+ * word into the flag; every kernel still honours the flag itself.  The word is freed with the flag's owner
+ * calling xpkFlagDetachRelay.                                                                          */
+xpkResult xpkFlagAttachRelay(uint32_t *flag_dev, volatile uint32_t **relay_host);
+xpkResult xpkFlagDetachRelay(uint32_t *flag_dev, volatile uint32_t *relay_host);
 
 /* ---- task creation ------------------------------------------------------------------
  * `flag_dev` may be NULL: the task then owns a private flag (see xpkTaskFlag).
@@ -130,9 +138,9 @@ xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void 
  * from any thread; `stream` must be a stream of the task's device.                       */
 
 /* Enqueue the task's kernel on `stream`.  A fresh or reset task starts at tile 0; a
- * PREEMPTED task continues from its cursor; a COMPLETED task that is launched again without
- * a reset runs a kernel that finds no tile to claim and publishes COMPLETED again.  Never
- * blocks.  `sm_limit` > 0 caps the persistent grid to that many SMs (0 = all).          */
+ * PREEMPTED task continues from its cursor; a COMPLETED task has re-armed itself and runs
+ * again from tile 0 (callers whose inputs changed in place, like the sort's keys, restore them
+ * first).  Never blocks.  `sm_limit` > 0 caps the persistent grid to that many SMs (0 = all).          */
 xpkResult xpkTaskLaunch(xpkTask_t task, void *stream, int sm_limit);
 
 /* Read the mailbox (mapped host memory; no CUDA call, no synchronisation). */
@@ -147,7 +155,8 @@ xpkResult xpkTaskWait(xpkTask_t task, uint64_t timeout_us, xpkTaskInfo *info);
  * has published.  The GPU clock is not the host's: callers calibrate an offset themselves.            */
 xpkResult xpkTaskTimes(xpkTask_t task, uint64_t *start_ns, uint64_t *exit_ns);
 
-/* Rewind the cursor to tile 0 (enqueued on `stream`, ordered after prior work on it). */
+/* Rewind the cursor to tile 0 (enqueued on `stream`, ordered after prior work on it).  Costs nothing on the
+ * device for a task that was never launched or has completed; the sort's scratch is cleared in any case. */
 xpkResult xpkTaskReset(xpkTask_t task, void *stream);
 
 /* The flag this task polls (its own, or the shared one given at creation). */

@@ -2,8 +2,9 @@
 // sched_probe_ref.cpp, driving this repository's LocalScheduler (csrc/sched/local_scheduler.cpp).
 //   usage: sched_probe_new <policy> [--virtual <t0_us>] < script
 // With --virtual the scheduler runs on the calling thread against a virtual clock that starts at t0_us:
-// a round after every event, `sleep_ms` serves the policy's timers at their exact times, `flush` lets
-// 30 ms pass first (as the real-time mode does).  Outcomes are then exactly reproducible.
+// a round after every event, `sleep_ms` / `sleep_us` serve the policy's timers at their exact times, `flush` lets
+// 30 ms pass first (as the real-time mode does), `peek` reports without letting time pass.  Outcomes are then
+// exactly reproducible.
 #include <chrono>
 #include <cstdio>
 #include <iostream>
@@ -72,8 +73,12 @@ int main(int argc, char **argv) {
             int ms = 0;
             is >> ms;
             if (virt) advance(vnow + (int64_t)ms * 1000); else std::this_thread::sleep_for(std::chrono::milliseconds(ms));
-        } else if (cmd == "flush") {
-            if (virt) advance(vnow + 30000); else std::this_thread::sleep_for(std::chrono::milliseconds(30));
+        } else if (cmd == "sleep_us") {                  // virtual clock only: finer steps than sleep_ms
+            long long us = 0;
+            is >> us;
+            if (virt) advance(vnow + us); else std::this_thread::sleep_for(std::chrono::microseconds(us));
+        } else if (cmd == "flush" || cmd == "peek") {    // peek: the same report without letting time pass first
+            if (cmd == "flush") { if (virt) advance(vnow + 30000); else std::this_thread::sleep_for(std::chrono::milliseconds(30)); }
             std::lock_guard<std::mutex> lk(mu);
             std::printf("flush");
             for (auto &[pid, rs] : last) {

@@ -155,8 +155,10 @@ def script_text(steps, t0_us: int) -> str:
     for st in steps:
         if st[0] == "ev":
             lines.append("event " + build_event(st, t0_us).hex())
-        elif st[0] == "flush":
-            lines.append("flush")
+        elif st[0] in ("flush", "peek"):
+            lines.append(st[0])
+        elif st[0] == "sleep_us":
+            lines.append(f"sleep_us {st[1]}")
         else:
             lines.append(f"sleep_ms {st[1]}")
     return "\n".join(lines) + "\n"

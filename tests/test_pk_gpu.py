@@ -397,6 +397,46 @@ def test_sort_64m_keys_against_numpy(pk):
     t.destroy()
 
 
+def test_gemm_stops_on_the_relayed_host_word_alone(pk, ok):
+    """The flag's early-warning word in mapped host memory: a plain host store to it, with the device flag itself
+    never written, must stop a running GEMM (the relay thread of its first CTA raises the flag), and the resumed
+    task must give the bytes of a straight run."""
+    import time
+    M = N = K = 8192
+    a, b = _gemm_inputs(M, N, K, seed=11)
+    ad, bd = a.cuda(), b.cuda()
+    base = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    t0 = pk.Task.gemm(base, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT)
+    _run_to_completion(t0, pk)
+    t0.destroy()
+    flag = pk.Flag()
+    word = flag.attach_relay()
+    c = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    t = pk.Task.gemm(c, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT, flag=flag)
+    stopped = 0
+    for _ in range(4):
+        # ten launches back to back (7 ms of work), the word raised 200 us into them
+        for _ in range(10):
+            t.launch(_stream())
+        time.sleep(0.0002)
+        word.value = 1
+        info = t.wait()
+        torch.cuda.synchronize()
+        if info.status == pk.STATUS_PREEMPTED:
+            stopped += 1
+            assert info.tiles_done < info.tiles_total
+        word.value = 0
+        flag.set(0)
+        torch.cuda.synchronize()
+        if info.status == pk.STATUS_COMPLETED:
+            t.reset(_stream())
+    assert stopped >= 1, "the relay never stopped the kernel"
+    _run_to_completion(t, pk)
+    assert torch.equal(c, base)
+    t.destroy()
+    flag.destroy()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_task_calls_from_a_thread_on_another_device(pk):
     """Launch / reset / flag writes switch to the task's device for the call: a worker thread that never chose a

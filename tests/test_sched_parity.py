@@ -101,3 +101,21 @@ def test_chpf_follows_linux_priorities():
     finally:
         normal.kill(); nicer.kill()
         normal.wait(); nicer.wait()
+
+
+def test_hpf_resume_hysteresis_keeps_lower_priorities_out_of_short_gaps():
+    """XSCHED_HPF_RESUME_HYSTERESIS_US (an addition; off by default): a high-priority queue that goes idle and comes
+    back within the window never lets the low-priority queue be resumed in between; once the window has passed
+    the low-priority queue runs again.  Without the variable every idle edge resumes at once, as in the reference."""
+    from sched_scenarios import run_virtual, A, B, P1, P2, DEV1
+    steps = [("ev", "proc_create", P1), ("ev", "proc_create", P2), ("ev", "xq_create", P1, A, DEV1), ("ev", "xq_create", P2, B, DEV1),
+             ("ev", "hint_priority", P2, B, 1), ("ev", "xq_ready", P1, A, 0.0), ("ev", "xq_ready", P2, B, 0.0), ("peek",),      # 0: A suspended
+             ("ev", "xq_idle", P2, B), ("peek",),                                                                                  # 1: the gap
+             ("sleep_us", 300), ("ev", "xq_ready", P2, B, 0.0), ("peek",),                                                         # 2: B back within the window
+             ("ev", "xq_idle", P2, B), ("sleep_us", 999), ("peek",),                                                                # 3: window not yet over
+             ("sleep_us", 2), ("peek",)]                                                                                            # 4: over
+    run, susp = ((A,), ()), ((), (A,))
+    with_h = [f[P1] for f in run_virtual(NEW, "HPF", steps, VIRTUAL_T0, env_extra={"XSCHED_HPF_RESUME_HYSTERESIS_US": "1000"})]
+    assert with_h == [susp, susp, susp, susp, run]
+    plain = [f[P1] for f in run_virtual(NEW, "HPF", steps, VIRTUAL_T0)]
+    assert plain == [susp, run, susp, run, run]

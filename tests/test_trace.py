@@ -46,8 +46,14 @@ def test_no_file_without_the_variable(tmp_path):
 def test_timeline_arithmetic_on_synthetic_records():
     bench = load_bench()
     HP, LP, SRV = 100, 200, 300
-    off_hp, off_lp = 5_000_000, 5_000_400          # host - device clock, ns (the two processes calibrate separately)
-    hp, lp, srv = [(10, "gpu_clock_offset", off_hp, 1000)], [(11, "gpu_clock_offset", off_lp, 1000)], []
+    # host - device clock in ns: one device clock, so one true offset, drifting by 40 us per second against the host;
+    # each process records it twice (start and end) and the reader interpolates
+    def off(t):
+        return 5_000_000 + (t * 40) // 1_000_000
+    off_hp = off_lp = None
+    hp = [(10, "gpu_clock_offset", off(10), 1000), (5_000_000, "gpu_clock_offset", off(5_000_000), 1000)]
+    lp = [(11, "gpu_clock_offset", off(11), 1000), (6_000_000, "gpu_clock_offset", off(6_000_000), 1000)]
+    srv = []
     for i in range(1, 4):
         t0 = 1_000_000 * i
         hp += [(t0, "app_submit", i, 0), (t0 + 2_000, "ready_sent", 7, 0)]
@@ -56,11 +62,11 @@ def test_timeline_arithmetic_on_synthetic_records():
         lp_exit_host = t0 + 61_000
         hp_start_host, hp_end_host = t0 + 191_000, t0 + 351_000
         # the LP stamps are written later, at Reactivate, with device-clock values
-        lp += [(t0 + 500_000, "task_gpu_times", lp_exit_host - 700_000 - off_lp, lp_exit_host - off_lp)]
-        hp += [(t0 + 360_000, "app_done", i, 0), (t0 + 360_100, "app_gpu_times", hp_start_host - off_hp, hp_end_host - off_hp)]
+        lp += [(t0 + 500_000, "task_gpu_times", lp_exit_host - 700_000 - off(lp_exit_host), lp_exit_host - off(lp_exit_host))]
+        hp += [(t0 + 360_000, "app_done", i, 0), (t0 + 360_100, "app_gpu_times", hp_start_host - off(hp_start_host), hp_end_host - off(hp_end_host))]
     out = bench.timeline_stages({HP: sorted(hp), LP: sorted(lp), SRV: sorted(srv)})
     assert out["requests_matched"] == 3
-    st = {k: v["p50"] for k, v in out["stages_us"].items()}
+    st = {k: round(v["p50"]) for k, v in out["stages_us"].items()}        # whole microseconds: the interpolation is read at the record's time
     assert st == {"submit_to_ready_sent": 2.0, "ready_sent_to_server_recv": 10.0, "server_recv_to_op_sent": 2.0, "op_sent_to_lp_recv": 10.0,
                   "lp_recv_to_flag_write_issued": 7.0, "flag_write_to_lp_last_cta_exit": 30.0, "lp_last_cta_exit_to_hp_first_cta": 130.0,
                   "hp_kernel": 160.0, "hp_kernel_end_to_host_done": 9.0, "total": 360.0}

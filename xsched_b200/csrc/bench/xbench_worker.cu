@@ -161,7 +161,9 @@ struct Verifier {
 // ---- timeline support: device clock against the host's monotonic clock --------------------------------------
 // A one-thread kernel publishes %globaltimer to a mapped host word for a fraction of a millisecond while the
 // host reads the word and its own clock; the smallest (host - device) difference seen is the offset plus the
-// shortest time a device write takes to become visible to the host (well under a microsecond).
+// shortest time a device write takes to become visible to the host (well under a microsecond).  The two clocks
+// drift against each other (tens of microseconds per second were seen), so a process calibrates when it starts and
+// again when it is done, and readers interpolate.
 __global__ void PublishClock(volatile unsigned long long *out, int rounds) {
     for (int i = 0; i < rounds; ++i) {
         unsigned long long t;
@@ -792,6 +794,7 @@ int main(int argc, char **argv) {
         Queue q = MakeQueue(a, a.level, a.prio);
         LpWork w = BuildLp(a, q, 0);
         LpResult r = RunLp(a, q, w, nullptr, a.duration_s);
+        CalibrateGpuClock();          // a second reading: the two clocks drift by tens of microseconds per second
         PrintLp(a, w, r);
         return LpOk(r) ? 0 : 6;
     }
@@ -801,6 +804,7 @@ int main(int argc, char **argv) {
         std::printf("READY\n"); std::fflush(stdout);
         HpResult r = RunHp(a, q, w, a.count, nullptr);
         std::printf("DONE\n"); std::fflush(stdout);              // requests are over; what follows is verification
+        CalibrateGpuClock();
         PrintHp(a, w, r, VerifyHp(q, w));
         return 0;
     }

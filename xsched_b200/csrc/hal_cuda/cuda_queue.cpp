@@ -69,6 +69,21 @@ public:
 
         CUDA_ASSERT(d.cuMemAlloc(&flag_, 256));
         CUDA_ASSERT(d.cuMemsetD32(flag_, 0, 64));
+        // Early-warning word of the flag in mapped host memory (kernels with a relay see a raise ~2 us after the
+        // store in Deactivate, instead of the 6-14 us the stream write takes): its device address goes into bytes
+        // [8,16) of the flag block (layout: include/xsched_b200/pk.h, xpkFlagAttachRelay).  Driver calls only: the
+        // interposer must not start a CUDA runtime inside a program that has none.
+        void *relay_host = nullptr;
+        CUdeviceptr relay_dev = 0;
+        if (d.cuMemHostAlloc(&relay_host, 64, CU_MEMHOSTALLOC_DEVICEMAP | CU_MEMHOSTALLOC_PORTABLE) == CUDA_SUCCESS) {
+            *(volatile uint32_t *)relay_host = 0;
+            if (d.cuMemHostGetDevicePointer(&relay_dev, relay_host, 0) == CUDA_SUCCESS &&
+                d.cuMemsetD32(flag_ + 8, (unsigned)(relay_dev & 0xFFFFFFFFu), 1) == CUDA_SUCCESS &&
+                d.cuMemsetD32(flag_ + 12, (unsigned)(relay_dev >> 32), 1) == CUDA_SUCCESS)
+                relay_ = (volatile uint32_t *)relay_host;
+            else
+                d.cuMemFreeHost(relay_host);
+        }
         int lo = 0, hi = 0;
         CUDA_ASSERT(d.cuCtxGetStreamPriorityRange(&lo, &hi));
         CUDA_ASSERT(d.cuStreamCreateWithPriority(&ctrl_, CU_STREAM_NON_BLOCKING, hi));
@@ -79,6 +94,7 @@ public:
         const DriverApi &d = Driver();
         d.cuStreamDestroy(ctrl_);
         d.cuMemFree(flag_);
+        if (relay_) d.cuMemFreeHost((void *)relay_);
         d.cuMemFreeHost((void *)counter_->host);
     }
 
@@ -120,6 +136,7 @@ public:
     void Deactivate() override {
         ContextScope scope(ctx_);
         deactivate_ns_.store(NowNs());
+        if (relay_) __atomic_store_n(relay_, 1u, __ATOMIC_SEQ_CST);
         CUDA_ASSERT(Driver().cuStreamWriteValue32(ctrl_, flag_, 1, CU_STREAM_WRITE_VALUE_DEFAULT));
         XTRACE(utils::kTraceDeactivateIssued, GetHandle());
         stats_.deactivations.fetch_add(1, std::memory_order_relaxed);
@@ -128,7 +145,8 @@ public:
     void Reactivate(const CommandLog &log) override {
         ContextScope scope(ctx_);
         const DriverApi &d = Driver();
-        CUDA_ASSERT(d.cuStreamSynchronize(stream_));      // flushed kernels have published their cursors
+        CUDA_ASSERT(d.cuStreamSynchronize(stream_));      // flushed kernels have published their cursors (and no relay is running)
+        if (relay_) __atomic_store_n(relay_, 0u, __ATOMIC_SEQ_CST);
         CUDA_ASSERT(d.cuStreamWriteValue32(ctrl_, flag_, 0, CU_STREAM_WRITE_VALUE_DEFAULT));
         CUDA_ASSERT(d.cuStreamSynchronize(ctrl_));        // the flag is down before anything relaunches
         bool replay = false;
@@ -183,6 +201,7 @@ private:
     XDevice xdevice_ = 0;
     std::shared_ptr<CompletionCounter> counter_;
     CUdeviceptr flag_ = 0;
+    volatile uint32_t *relay_ = nullptr;       // mapped host word announcing a raise of flag_ early
     CUstream ctrl_ = nullptr;
     std::atomic<int64_t> deactivate_ns_{0};
     struct { std::atomic<uint64_t> launched{0}, deactivations{0}, relaunches{0}, last_preempt_ns{0}; } stats_;

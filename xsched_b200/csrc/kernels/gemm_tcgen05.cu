@@ -12,7 +12,9 @@
 //                       accumulators that together fill tensor memory (512 columns);
 //                       tcgen05.commit releases the smem stage / publishes the accumulators;
 //   warps 2-9           two groups of four warps, one per accumulator, read it with tcgen05.ld
-//                       (32 lanes x 32 columns per instruction), round to bf16 and store rows.
+//                       (32 lanes x 32 columns per instruction), round to bf16 and store rows;
+//   warp 10 (one lane,  relays an early copy of the preempt flag from mapped host memory into the device flag
+//   first CTA only)     (see pk_common.cuh); idle in every other CTA.
 //
 // A 256x256 tile moves 64 KB of operands per 64-deep k-block for 2*256*256*64 flop — one third less
 // L2->SM traffic per flop than a 128x256 tile, which measured as the limiter of that shape (tensor pipe
@@ -44,7 +46,8 @@ constexpr int kStages = 3;
 constexpr int kAccBufs = 2;                     // the two row-halves of one tile
 constexpr int kSchedSlots = 4;
 constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
+constexpr int kRelayWarp = 2 + kEpiWarps;                // one more warp: in the grid's first CTA its first lane relays the host's early flag
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps + 32;
 constexpr int kRasterGroup = 16;
 constexpr uint32_t kABytes = kBM * kBK * 2;          // 32 KiB
 constexpr uint32_t kBBytes = kBN * kBK * 2;          // 32 KiB
@@ -70,6 +73,7 @@ struct GemmShared {
     unsigned long long abort_tile_seq;   // sequence number of the abandoned tile
     uint32_t abort;                      // 1: abandon from abort_* on; 2: error, leave now
     uint32_t tmem_base;
+    uint32_t relay_stop;                 // the producer is done: nothing left for an early flag to stop
 };
 constexpr size_t kGemmSmemBytes = 1024 /*align slack*/ + kStages * (kABytes + kBBytes) + sizeof(GemmShared);
 
@@ -201,6 +205,7 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
         for (int i = 0; i < kSchedSlots; ++i) { mbar_init(&sh->sched_full[i], 1); mbar_init(&sh->sched_empty[i], 1 + kEpiWarps); }
         mbar_init(&sh->drain, 1);
         sh->abort = 0;
+        sh->relay_stop = 0;
         sh->abort_kseq = ~0ull;
         sh->abort_tile_seq = ~0ull;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -257,6 +262,7 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
                 }
                 ++tseq;
             }
+            *(volatile uint32_t *)&sh->relay_stop = 1u;
             // Leave only after every load this thread issued has landed in shared memory.
             const unsigned long long first = kseq > (unsigned long long)kStages ? kseq - kStages : 0;
             for (unsigned long long s = first; s < kseq; ++s) {
@@ -319,6 +325,26 @@ gemm_bf16_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __gr
             if (issued_any) {
                 tc_commit(&sh->drain);
                 bounded_wait(&sh->drain, 0u, sh, ctl, kErrGemmDrain, [] { return false; });
+            }
+        }
+        __syncwarp();
+    } else if (warp == kRelayWarp) {
+        // ======================= relay of the host's early flag (first CTA only) =======================
+        // The host raises a word in its own (mapped) memory a few microseconds before its write of the device
+        // flag lands; this thread looks at that word about twice per microsecond and raises the device flag
+        // itself.  Correctness never depends on it: the host's own write of the flag follows in any case.
+        if constexpr (kPreemptible) {
+            if (blockIdx.x == 0 && lane == 0) {
+                const uint32_t *src = flag_relay_source(ctl->flag);
+                if (src != nullptr) {
+                    const unsigned long long t0 = global_ns();
+                    uint32_t it = 0;
+                    while (*(volatile uint32_t *)&sh->relay_stop == 0u) {
+                        if (ld_host_word(src) != 0u) { atomicExch(const_cast<uint32_t *>(ctl->flag), 1u); break; }
+                        __nanosleep(400);
+                        if ((++it & 1023u) == 0 && global_ns() - t0 > kWaitLimitNs) break;      // a very long kernel just loses its relay
+                    }
+                }
             }
         }
         __syncwarp();

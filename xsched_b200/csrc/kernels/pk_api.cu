@@ -224,6 +224,26 @@ xpkResult xpkFlagSet(uint32_t *flag_dev, uint32_t value, void *ctrl_stream) {
     return XPK_ERR_CUDA;
 }
 
+xpkResult xpkFlagAttachRelay(uint32_t *flag_dev, volatile uint32_t **relay_host) {
+    if (!flag_dev || !relay_host || (reinterpret_cast<uintptr_t>(flag_dev) & 15u)) return XPK_ERR_INVALID_VALUE;
+    void *host = nullptr, *alias = nullptr;
+    if (cudaHostAlloc(&host, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return XPK_ERR_CUDA;
+    std::memset(host, 0, 64);
+    if (cudaHostGetDevicePointer(&alias, host, 0) != cudaSuccess) { cudaFreeHost(host); return XPK_ERR_CUDA; }
+    const unsigned long long value = (unsigned long long)(uintptr_t)alias;
+    if (cudaMemcpy((unsigned char *)flag_dev + 8, &value, 8, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFreeHost(host); return XPK_ERR_CUDA; }
+    *relay_host = (volatile uint32_t *)host;
+    return XPK_SUCCESS;
+}
+
+xpkResult xpkFlagDetachRelay(uint32_t *flag_dev, volatile uint32_t *relay_host) {
+    if (!flag_dev || !relay_host) return XPK_ERR_INVALID_VALUE;
+    const unsigned long long none = 0;
+    const bool ok = cudaMemcpy((unsigned char *)flag_dev + 8, &none, 8, cudaMemcpyHostToDevice) == cudaSuccess;
+    cudaFreeHost((void *)relay_host);
+    return ok ? XPK_SUCCESS : XPK_ERR_CUDA;
+}
+
 static xpkResult create_stream_task(xpkTask_t *task, uint32_t kind, float *out, const float *x, const float *y,
                                     float s, uint64_t n, uint32_t tile_elems, uint32_t flags, uint32_t *flag_dev) {
     if (!task || !out || !x || !y || n == 0) return XPK_ERR_INVALID_VALUE;
@@ -421,7 +441,13 @@ xpkResult xpkTaskReset(xpkTask_t t, void *stream) {
     if (!t) return XPK_ERR_INVALID_VALUE;
     DeviceGuard on_task_device(t->device);
     cudaStream_t s = (cudaStream_t)stream;
-    if (cudaMemsetAsync(t->ctl, 0, xpk::kCtlResetBytes, s) != cudaSuccess) return XPK_ERR_CUDA;
+    // A task that was never launched, or whose newest launch has published COMPLETED, already stands at tile 0
+    // (a finishing kernel re-arms its control block): nothing to clear.  Anything else — running, preempted,
+    // failed — is rewound by a stream-ordered memset.
+    volatile Mailbox *m = t->mb_host;
+    const unsigned long long launches = t->launches.load();
+    const bool at_start = launches == t->reset_at.load() || (m->seq == launches && m->status == XPK_STATUS_COMPLETED);
+    if (!at_start && cudaMemsetAsync(t->ctl, 0, xpk::kCtlResetBytes, s) != cudaSuccess) return XPK_ERR_CUDA;
     if (t->kind == XPK_KIND_SORT) {
         if (cudaMemsetAsync(t->sort_hist, 0, t->sort_scratch_bytes, s) != cudaSuccess) return XPK_ERR_CUDA;
     }

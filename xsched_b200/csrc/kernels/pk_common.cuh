@@ -87,6 +87,20 @@ __device__ __forceinline__ void note_start(Ctl *ctl) {
     if (blockIdx.x == 0 && threadIdx.x == 0) ctl->start_ns = global_ns();
 }
 
+// A preempt flag is the first word of a 16-byte block.  Bytes [8,16) of the block may hold the device address of a
+// word in mapped host memory that the host sets (with a plain store, visible to the GPU within a couple of
+// microseconds) just before it enqueues the write of the flag itself (which takes 6-14 us to land): a kernel that
+// runs a relay (the GEMM: one spare thread of its first CTA) copies a raised host word into the flag, so that the
+// tile loops, which only ever poll device memory, see it early.  0 = no such word.
+__device__ __forceinline__ const uint32_t *flag_relay_source(const uint32_t *flag) {
+    return reinterpret_cast<const uint32_t *>(*reinterpret_cast<const unsigned long long *>(flag + 2));
+}
+__device__ __forceinline__ uint32_t ld_host_word(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ uint32_t ld_flag(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -178,6 +192,13 @@ __device__ __forceinline__ void cta_exit(Ctl *ctl, unsigned long long done_by_ct
     uint32_t st = err ? kStatusError : (done >= v->total ? kStatusCompleted : kStatusPreempted);
     if (st == kStatusPreempted) ctl->preemptions = v->preemptions + 1;
     ctl->status = st;
+    const unsigned long long preemptions = v->preemptions, start_ns = v->start_ns;
+    if (st == kStatusCompleted) {
+        // A finished task re-arms itself: the claim state goes back to what a reset leaves, so that the next
+        // submission of the same task needs no memset in front of its kernel (the outcome lives in the mailbox).
+        unsigned long long *w = reinterpret_cast<unsigned long long *>(ctl);
+        for (unsigned i = 0; i < kCtlResetBytes / 8; ++i) w[i] = 0;
+    }
     __threadfence();
 
     Mailbox *mb = v->mailbox;
@@ -187,8 +208,8 @@ __device__ __forceinline__ void cta_exit(Ctl *ctl, unsigned long long done_by_ct
         m->tiles_total = v->total;
         m->status = st;
         m->error = err;
-        m->preemptions = v->preemptions;
-        m->start_ns = v->start_ns;
+        m->preemptions = preemptions;
+        m->start_ns = start_ns;
         m->exit_ns = global_ns();
         __threadfence_system();
         m->seq = launch_no;

@@ -17,11 +17,31 @@ Priority HighestPriorityFirstPolicy::GetPriority(XQueueHandle h) const {
     return it == prio_.end() ? PRIORITY_DEFAULT : it->second;
 }
 
-void HighestPriorityFirstPolicy::Sched(const Status &status, int64_t, Decision &out) {
+HighestPriorityFirstPolicy::HighestPriorityFirstPolicy() : Policy(kPolicyHighestPriorityFirst) {
+    const std::string v = GetEnv("XSCHED_HPF_RESUME_HYSTERESIS_US");
+    if (!v.empty()) hysteresis_us_ = std::max<int64_t>(0, std::atoll(v.c_str()));
+}
+
+void HighestPriorityFirstPolicy::Sched(const Status &status, int64_t now_us, Decision &out) {
+    // With a resume hysteresis, a queue that went idle less than that long ago still counts as ready.
+    std::unordered_map<XQueueHandle, bool> lingering;
+    if (hysteresis_us_ > 0) {
+        for (const auto &[h, q] : status.xqueues) {
+            bool &was = was_ready_[h];
+            if (q.ready) { idle_since_.erase(h); was = true; continue; }
+            if (was) { idle_since_[h] = now_us; was = false; }
+            auto it = idle_since_.find(h);
+            if (it == idle_since_.end()) continue;
+            if (now_us - it->second < hysteresis_us_) { lingering[h] = true; out.timers_us.push_back(it->second + hysteresis_us_); }
+            else idle_since_.erase(it);
+        }
+        for (auto it = was_ready_.begin(); it != was_ready_.end();)        // forget queues that are gone
+            it = status.xqueues.count(it->first) ? std::next(it) : (idle_since_.erase(it->first), was_ready_.erase(it));
+    }
     // Highest priority among the READY queues of each device.
     std::map<XDevice, Priority> top;
     for (const auto &[h, q] : status.xqueues) {
-        if (!q.ready) continue;
+        if (!q.ready && !lingering.count(h)) continue;
         const Priority p = GetPriority(h);
         auto [it, fresh] = top.try_emplace(q.device, p);
         if (!fresh && p > it->second) it->second = p;

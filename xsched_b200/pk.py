@@ -27,6 +27,7 @@ EXPORTS = [
     "xpkTaskCreateTriad", "xpkTaskCreateVecAdd", "xpkSortScratchBytes", "xpkTaskCreateSort",
     "xpkTaskCreateGemm", "xpkTaskLaunch", "xpkTaskQuery", "xpkTaskWait", "xpkTaskReset",
     "xpkTaskFlag", "xpkTaskKind", "xpkTaskDestroy", "xpkLaunchCount", "xpkSortNoAlloc", "xpkTaskTimes",
+    "xpkFlagAttachRelay", "xpkFlagDetachRelay",
 ]
 
 
@@ -42,6 +43,8 @@ lib.xpkDeviceSmCount.argtypes = [C.POINTER(C.c_int)]
 lib.xpkFlagCreate.argtypes = [C.POINTER(_vp)]
 lib.xpkFlagDestroy.argtypes = [_vp]
 lib.xpkFlagSet.argtypes = [_vp, _u32, _vp]
+lib.xpkFlagAttachRelay.argtypes = [_vp, C.POINTER(_vp)]
+lib.xpkFlagDetachRelay.argtypes = [_vp, _vp]
 lib.xpkTaskCreateTriad.argtypes = [C.POINTER(_vp), _vp, _vp, _vp, C.c_float, _u64, _u32, _u32, _vp]
 lib.xpkTaskCreateVecAdd.argtypes = [C.POINTER(_vp), _vp, _vp, _vp, _u64, _u32, _u32, _vp]
 lib.xpkSortScratchBytes.restype = C.c_size_t
@@ -103,8 +106,19 @@ class Flag:
     def set(self, value: int, ctrl_stream: int = 0) -> None:
         _check(lib.xpkFlagSet(self.ptr, value, ctrl_stream), "xpkFlagSet")
 
+    def attach_relay(self):
+        """Give the flag an early-warning word in mapped host memory; returns it as a ctypes c_uint32 the caller
+        stores to (non-zero just before raising the flag, zero before lowering it)."""
+        p = _vp()
+        _check(lib.xpkFlagAttachRelay(self.ptr, C.byref(p)), "xpkFlagAttachRelay")
+        self.relay = p.value
+        return C.c_uint32.from_address(p.value)
+
     def destroy(self) -> None:
         if self.ptr:
+            if getattr(self, "relay", None):
+                lib.xpkFlagDetachRelay(self.ptr, self.relay)
+                self.relay = None
             lib.xpkFlagDestroy(self.ptr)
             self.ptr = None
 
