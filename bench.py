@@ -371,7 +371,7 @@ def timeline_leg(device: int, ns: str, lp_kw: dict, requests: int = 300) -> dict
     tns = ns + "tl."
     tr_env = {"XSCHED_TRACE_FILE": prefix}
     out: dict = {}
-    srv = subprocess.Popen([str(XSERVER), "HPF", "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=dict(base_env(tns, None), **tr_env))
+    srv = subprocess.Popen([str(XSERVER), "HPF", "0"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=dict(base_env(tns, None), **tr_env))
     srv.stdout.readline()
     hp = None
     try:
@@ -424,7 +424,7 @@ def transparent_corun(device: int, shim_lib: Path, steps: int, threshold: int, b
     for k in ("XSCHED_IPC_NAMESPACE", "XSCHED_POLICY", "XSCHED_IPC_SPIN"):      # the reference's clients know no namespace
         base.pop(k, None)
     srv_env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
-    srv = subprocess.Popen([str(XSERVER), "HPF", "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+    srv = subprocess.Popen([str(XSERVER), "HPF", "0"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
                            env=dict(srv_env, XLOG_LEVEL="WARN", XSCHED_IPC_SPIN="ON"))
     srv.stdout.readline()
     pw = str(LIB / "plain_worker")
@@ -603,7 +603,7 @@ def config4(args, ctx=None) -> dict | None:
     deadline_ms = 20.0
     server = None
     if rank == 0:
-        server = subprocess.Popen([str(XSERVER), policy, "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+        server = subprocess.Popen([str(XSERVER), policy, "0"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
                                   env=dict(base_env(ns, None), XSCHED_POLICY_SCOPE="DEVICE"))
         server.stdout.readline()
     if pg:
@@ -798,7 +798,7 @@ def main() -> None:
 
     server = None
     if rank == 0:
-        server = subprocess.Popen([str(XSERVER), "HPF", "50000"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+        server = subprocess.Popen([str(XSERVER), "HPF", "0"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
                                   env=base_env(ns, None))
         server.stdout.readline()
     if pg:
@@ -915,47 +915,71 @@ def main() -> None:
             except Exception as e:       # an extra leg must not take the headline down with it
                 extra["config3_triad_vs_sort"] = {"error": str(e)[:300]}
         if not args.no_config2 and world == 1:
-            # Workload configuration 2 (inference-shaped): HP = batch-1 decode of a random-init Llama-3-8B-shaped model in
-            # PyTorch, run UNCHANGED under the libcuda interposer (its stream becomes a priority-1 XQueue); LP = the
-            # preemptible GEMM stream (16384x4096)*(4096x14336) at level 2.  10 req/s x 128 tokens at batch 1 is ~3x
-            # more than one GPU can serve sequentially, so requests arrive at 1/s here; the primary number is the
-            # per-token step latency against the same script running alone.
+            # Workload configuration 2 (inference-shaped): HP = decode of a random-init Llama-3-8B-shaped model in PyTorch,
+            # run UNCHANGED under the libcuda interposer (its stream becomes a priority-1 XQueue); LP = the preemptible GEMM
+            # stream (16384x4096)*(4096x14336) at level 2.  Three arms:
+            #   sequential_1rps            one request at a time at 1 request/s, plain HPF (the reference's decisions);
+            #   sequential_1rps_hysteresis the same under an xserver with XSCHED_HPF_RESUME_HYSTERESIS_US=500: the LP queue is
+            #                              not resumed into the ~100 us gap between two decode steps;
+            #   batched_10rps              the configured 10 requests/s, requests in flight decoded together (one request
+            #                              at a time needs ~0.7 s of decode per request: 7x more than one GPU has).
+            # The primary number of each arm is the per-token step latency against the same script running alone.
             try:
                 import tempfile
                 real = find_real_driver()
-                d = Path(tempfile.mkdtemp(prefix="xsched_shim_"))
-                for name in ("libcuda.so.1", "libcuda.so"):
-                    os.symlink(LIB / "libshimcuda.so", d / name)
-                env2 = base_env(ns, "GLB")
-                env2.update(XSCHED_CUDA_LIB=real or "", XSCHED_AUTO_XQUEUE="ON", XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_PRIORITY="1",
-                            XSCHED_IPC_SPIN="OFF", LD_LIBRARY_PATH=f"{d}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""))
-                dec = [sys.executable, "-m", "xsched_b200.llama_decode", "--device", str(device), "--requests", "10", "--tokens", "128", "--rate", "1.0"]
-                mark("config 2: decode alone")
-                dec_alone = run_json(dec, env2, 400)[-1]
-                big = dict(kernel="gemm", abort=1, depth=3, threshold=2, batch=1, M=16384, N=14336, K=4096)
+                d = shim_dir(LIB / "libshimcuda.so")
+                big = dict(kernel="gemm", abort=1, depth=3, threshold=2, batch=1, M=16384, N=14336, K=4096, b_std=0.02)
                 big_alone = run_json(worker_cmd("lp", device, level=2, prio=0, duration_s=3, warmup_s=0.5, **big), env_alone, 180)[-1]
-                mark("config 2: co-run")
-                lp2 = subprocess.Popen(worker_cmd("lp", device, level=2, prio=0, duration_s=3600, warmup_s=0.5, **big), stdout=subprocess.PIPE,
-                                       stderr=subprocess.DEVNULL, text=True, env=base_env(ns, "GLB"))
+
+                def decode_env(namespace):
+                    e = base_env(namespace, "GLB")
+                    e.update(XSCHED_CUDA_LIB=real or "", XSCHED_AUTO_XQUEUE="ON", XSCHED_AUTO_XQUEUE_LEVEL="1", XSCHED_AUTO_XQUEUE_PRIORITY="1",
+                             XSCHED_IPC_SPIN="OFF", LD_LIBRARY_PATH=f"{d}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""))
+                    return e
+
+                def arm(namespace, dec, dec_alone):
+                    lp2, _ = start_lp(worker_cmd("lp", device, level=2, prio=0, duration_s=3600, warmup_s=0.5, **big), base_env(namespace, "GLB"), "config 2 LP")
+                    try:
+                        dec_co = run_hp_marking(dec, decode_env(namespace), 600, [lp2])[-1]
+                    finally:
+                        big_co = stop_lp(lp2)
+                    return {"token_p99_ms": dec_co["token_p99_ms"], "token_standalone_p99_ms": dec_alone["token_p99_ms"],
+                            "token_p99_ratio": round(dec_co["token_p99_ms"] / dec_alone["token_p99_ms"], 3),
+                            "token_p50_ratio": round(dec_co["token_p50_ms"] / dec_alone["token_p50_ms"], 3),
+                            "request_p99_ms": dec_co["request_p99_ms"], "request_standalone_p99_ms": dec_alone["request_p99_ms"],
+                            "mean_batch": dec_co.get("mean_batch"), "decode_steps": dec_co.get("decode_steps"),
+                            "lp_tflops_corun": big_co.get("rate"), "lp_kept_pct": round(100 * big_co.get("rate", 0.0) / big_alone["rate"], 2),
+                            "lp_bit_exact": big_co.get("bit_exact"), "lp_preempted_iterations_verified": big_co.get("verified_preempted_iters"),
+                            "deactivations": big_co.get("deactivations"),
+                            "deactivations_per_request": round(big_co.get("deactivations", 0) / max(1, dec_co["requests"]), 1)}
+                dec_base = [sys.executable, "-m", "xsched_b200.llama_decode", "--device", str(device), "--tokens", "128"]
+                seq = dec_base + ["--requests", "8", "--rate", "1.0"]
+                bat = dec_base + ["--requests", "40", "--rate", "10.0", "--batched"]
+                mark("config 2: decode alone (sequential, batched)")
+                seq_alone = run_json(seq, decode_env(ns), 400)[-1]
+                bat_alone = run_json(bat, decode_env(ns), 400)[-1]
+                c2 = {"lp_tflops_standalone": big_alone["rate"],
+                      "hbm_frac_of_decode_step": round(((seq_alone["weights_gb"] + seq_alone["kv_gb"]) / (seq_alone["token_p50_ms"] * 1e-3)) / peaks()["hbm_gbs"], 3),
+                      "note": "HP runs unmodified PyTorch under libshimcuda.so; vocabulary 128256 assumed; LP weights ~ N(0, 0.02)"}
+                mark("config 2: co-run, sequential at 1 request/s")
+                c2["sequential_1rps"] = arm(ns, seq, seq_alone)
+                mark("config 2: co-run, batched at 10 requests/s")
+                c2["batched_10rps"] = arm(ns, bat, bat_alone)
+                c2["batched_10rps"]["token_standalone_p50_ms"] = bat_alone["token_p50_ms"]
+                mark("config 2: co-run, sequential, resume hysteresis 500 us")
+                hns = ns + "h."
+                hsrv = subprocess.Popen([str(XSERVER), "HPF", "0"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+                                        env=dict(base_env(hns, None), XSCHED_HPF_RESUME_HYSTERESIS_US="500"))
+                hsrv.stdout.readline()
                 try:
-                    t_wait = time.time()
-                    while not lp2.stdout.readline().startswith("READY"):
-                        if lp2.poll() is not None or time.time() - t_wait > 90:
-                            raise RuntimeError("config 2 LP worker not ready")
-                    dec_co = run_hp_marking(dec, env2, 600, [lp2])[-1]
+                    c2["sequential_1rps_hysteresis_500us"] = arm(hns, seq, seq_alone)
                 finally:
-                    lp2.send_signal(signal.SIGTERM)
-                    out2, _ = lp2.communicate(timeout=120)
-                big_co = [json.loads(l) for l in out2.splitlines() if l.startswith("{")][-1]
-                extra["config2_llama_decode_vs_gemm"] = {
-                    "token_p99_ms": dec_co["token_p99_ms"], "token_standalone_p99_ms": dec_alone["token_p99_ms"],
-                    "token_p99_ratio": round(dec_co["token_p99_ms"] / dec_alone["token_p99_ms"], 3),
-                    "token_p50_ratio": round(dec_co["token_p50_ms"] / dec_alone["token_p50_ms"], 3),
-                    "request_p99_ms": dec_co["request_p99_ms"], "request_standalone_p99_ms": dec_alone["request_p99_ms"],
-                    "hbm_frac_of_decode_step": round(((dec_alone["weights_gb"] + dec_alone["kv_gb"]) / (dec_alone["token_p50_ms"] * 1e-3)) / peaks()["hbm_gbs"], 3),
-                    "lp_tflops_standalone": big_alone["rate"], "lp_tflops_corun": big_co["rate"], "lp_kept_pct": round(100 * big_co["rate"] / big_alone["rate"], 2),
-                    "lp_bit_exact": big_co["bit_exact"], "deactivations": big_co["deactivations"], "arrival_rate_per_s": 1.0,
-                    "note": "HP runs unmodified PyTorch under libshimcuda.so; vocabulary 128256 assumed"}
+                    hsrv.send_signal(signal.SIGTERM)
+                    try:
+                        hsrv.wait(timeout=10)
+                    except subprocess.TimeoutExpired:
+                        hsrv.kill()
+                extra["config2_llama_decode_vs_gemm"] = c2
             except Exception as e:
                 extra["config2_llama_decode_vs_gemm"] = {"error": str(e)[:400]}
         if args.level1:
@@ -966,13 +990,18 @@ def main() -> None:
         if not args.no_e2e:
             try:
                 n_e2e = max(100, requests // 4)
-                hp_e_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=n_e2e, period_us=E2E_PERIOD_US, hp_n=HP_N, e2e=1), env_alone, 600)[-1]
-                hp_e, lp_e = corun(device, ns, 2, n_e2e, 10, True, E2E_PERIOD_US, lp_kw)
+                # XSCHED_TRANSFER_AWARE_READY=ON in the high-priority process: its queue counts as ready from the moment the
+                # kernel is about to start, not while the request's 512 MiB are still crossing PCIe (and not while the
+                # result goes back), so the low-priority GEMM keeps the SMs during the copies.
+                ta = {"XSCHED_TRANSFER_AWARE_READY": "ON"}
+                hp_e_alone = run_json(worker_cmd("hp", device, level=2, prio=1, count=n_e2e, period_us=E2E_PERIOD_US, hp_n=HP_N, e2e=1), dict(env_alone, **ta), 600)[-1]
+                hp_e, lp_e = corun(device, ns, 2, n_e2e, 10, True, E2E_PERIOD_US, lp_kw, extra_env=ta)
                 launches += hp_e_alone["xpk_launches"] + hp_e["xpk_launches"] + lp_e["xpk_launches"]
                 e2e = {"value": round(hp_e["p99_us"] / hp_e_alone["p99_us"], 4), "unit": "x", "h2d_bytes_per_step": int(hp_e["h2d_bytes"]),
                        "d2h_bytes_per_step": int(hp_e["d2h_bytes"]), "hp_p99_us": hp_e["p99_us"], "hp_standalone_p99_us": hp_e_alone["p99_us"],
                        "period_us": E2E_PERIOD_US, "hp_samples": n_e2e, "bg_throughput_kept_pct": round(100 * lp_e["rate"] / lp_alone["rate"], 2),
-                       "note": "request = H2D of both inputs from pinned memory + vector add + D2H of the result, as XQueue callback commands"}
+                       "hp_p50_us": hp_e["p50_us"], "hp_standalone_p50_us": hp_e_alone["p50_us"], "ready_rule": "XSCHED_TRANSFER_AWARE_READY=ON",
+                       "note": "request = H2D of both inputs from pinned memory + vector add + D2H of the result, as copy and task commands on the high-priority XQueue"}
             except Exception as e:       # reported, not fatal: the device-resident figure stands on its own
                 e2e = {"error": str(e)[:300]}
         if not args.no_timeline and world == 1:

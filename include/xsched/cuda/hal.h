@@ -33,6 +33,13 @@ XResult CudaQueueGetPreemptFlag(HwQueueHandle hwq, uint32_t **flag_dev);
  * command's completion; it is not destroyed by the command. */
 XResult CudaXpkCommandCreate(HwCommandHandle *hw_cmd, void *xpk_task, int rewind);
 
+/* An asynchronous copy as a HwCommand of the CUDA backend (what the interposer makes of cuMemcpy*Async): kind 0 =
+ * host to device, 1 = device to host, 2 = device to device.  Host-to-device and device-to-host copies carry the
+ * transfer-only property (xsched/preempt/xqueue/xcommand.h), which the XQueue uses under
+ * XSCHED_TRANSFER_AWARE_READY=ON; host memory should be pinned.  No counterpart among the reference's C entry
+ * points (its copies exist only inside the shim, platforms/cuda/hal/include/xsched/cuda/hal/common/cuda_command.h:167-199). */
+XResult CudaMemcpyCommandCreate(HwCommandHandle *hw_cmd, void *dst, const void *src, size_t bytes, int kind);
+
 /* Per-queue counters for observability: commands launched, window stalls, deactivations,
  * and the last measured Deactivate-to-idle latency in nanoseconds. */
 typedef struct {

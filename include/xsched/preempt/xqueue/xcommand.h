@@ -29,6 +29,9 @@ enum XCommandProperty {
     kCommandPropertyDeactivatable  = 0x0001,  // HwQueue::Deactivate stops it; Reactivate re-executes it safely
     kCommandPropertyIdempotent     = 0x0002,  // may be re-executed freely (writes no memory)
     kCommandPropertyBlockingSubmit = 0x0004,  // Submit() returns only once it is in flight
+    kCommandPropertyTransferOnly   = 0x0008,  // (addition) moves data over the host link and occupies no compute unit;
+                                              // with XSCHED_TRANSFER_AWARE_READY=ON such commands alone do not make
+                                              // their XQueue "ready" in the scheduler's eyes
     kCommandPropertyMaskAll        = -1,
 };
 

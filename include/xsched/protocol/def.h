@@ -22,6 +22,9 @@
 
 #define XSCHED_CUDA_LIB_ENV_NAME                 "XSCHED_CUDA_LIB"   // path of the real libcuda.so.1
 #define XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS_ENV_NAME "XSCHED_CUDA_SINGLE_STREAM_PER_PROCESS"
+// (addition) ON: an XQueue announces itself ready when its first compute command is about to be launched and idle
+// again once only transfers remain, so that lower priorities keep the compute units while a request copies its data.
+#define XSCHED_TRANSFER_AWARE_READY_ENV_NAME "XSCHED_TRANSFER_AWARE_READY"
 
 // Scheduler selection.  XSCHED_POLICY=<name> implies the in-process (LCL) scheduler.
 #define XSCHED_SCHEDULER_ENV_NAME  "XSCHED_SCHEDULER"

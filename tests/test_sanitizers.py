@@ -29,6 +29,7 @@ def build(tmp: Path, flag: str):
     units = {p: tmp / (p.parent.name + "_" + p.stem + ".o") for d in ("utils", "preempt", "sched", "hal_host") for p in sorted((CSRC / d).glob("*.cpp"))}
     units[ROOT / "oracle" / "lane_driver.cpp"] = tmp / "lane_driver.o"
     units[CSRC / "server" / "xserver.cpp"] = tmp / "xserver.o"
+    units[CSRC / "server" / "http.cpp"] = tmp / "http.o"
     common = [CXX, "-std=c++20", "-O1", "-g", f"-fsanitize={flag}", "-pthread", f"-I{ROOT / 'include'}", f"-I{CSRC}"]
 
     def compile_one(item):
@@ -40,7 +41,7 @@ def build(tmp: Path, flag: str):
     lane, srv = tmp / "lane_san", tmp / "xserver_san"
     core = [str(o) for s_, o in units.items() if s_.parent.name in ("utils", "preempt", "sched")]
     host = [str(o) for s_, o in units.items() if s_.parent.name == "hal_host"]
-    for out, objs in ((lane, [str(tmp / "lane_driver.o")] + core + host), (srv, [str(tmp / "xserver.o")] + core)):
+    for out, objs in ((lane, [str(tmp / "lane_driver.o")] + core + host), (srv, [str(tmp / "xserver.o"), str(tmp / "http.o")] + core)):
         r = subprocess.run(common + ["-o", str(out)] + objs + ["-ldl", "-lrt"], capture_output=True, text=True)
         if r.returncode != 0 and ("cannot find" in r.stderr or "unrecognized" in r.stderr):
             pytest.skip(f"toolchain has no -fsanitize={flag} runtime")

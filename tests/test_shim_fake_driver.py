@@ -290,3 +290,23 @@ def test_single_stream_per_process(tmp_path):
     assert r.stdout.startswith("OK 136 same_handles=1")
     st = json.loads(stats.read_text())
     assert st["single_stream_refs"] == 4 and st["streams_with_xqueue"] == 1 and st["launches_queued"] == 9
+
+
+def test_transfer_aware_readiness_keeps_lower_priorities_running_during_copies(tmp_path):
+    """XSCHED_TRANSFER_AWARE_READY=ON (an addition, off by default): a high-priority request that is copy-in, one
+    kernel, copy-out only takes the "device" away from the low-priority queue for about the kernel's time; with the
+    reference's readiness rule (a queue is ready while anything is queued) the copies count as well."""
+    app = FAKE_DIR / "transfer_app"
+    assert app.exists()
+    out = {}
+    for mode in ("OFF", "ON"):
+        env = {k: v for k, v in os.environ.items() if not k.startswith("XSCHED_")}
+        env.update(FAKE_CUDA_LIB=str(FAKE), XSCHED_CUDA_LIB=str(FAKE), XLOG_LEVEL="WARN", XSCHED_TRANSFER_AWARE_READY=mode,
+                   LD_LIBRARY_PATH=f"{as_libcuda(tmp_path, FAKE)}:{LIB}:" + os.environ.get("LD_LIBRARY_PATH", ""))
+        r = subprocess.run([str(app), "4"], capture_output=True, text=True, env=env, timeout=120)
+        assert r.returncode == 0 and r.stdout.startswith("{"), r.stdout + r.stderr[-2000:]
+        out[mode] = json.loads(r.stdout)
+    on, off = out["ON"], out["OFF"]
+    assert off["lp_held_back_us"] > 3 * off["hp_kernel_us"]            # the copies kept the low-priority queue out
+    assert on["lp_held_back_us"] < 2.5 * on["hp_kernel_us"]            # about the kernels' time only
+    assert on["lp_kernels"] > 2 * off["lp_kernels"]

@@ -245,6 +245,10 @@ def build_fake_driver(force: bool = False, verbose: bool = False) -> Path | None
     if hal_src.exists() and (LIB / "libhalcuda.so").exists() and (force or _stale(hal_app, [hal_src, lib, LIB / "libhalcuda.so", LIB / "libpreempt.so"])):
         _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", f"-I{INC}", "-o", hal_app, hal_src, f"-L{link}", f"-L{LIB}",
               f"-Wl,-rpath,{LIB}", "-lhalcuda", "-lpreempt", "-lcuda", "-ldl", "-pthread"], verbose)
+    tr_src, tr_app = d / "transfer_app.cpp", d / "transfer_app"
+    if tr_src.exists() and (LIB / "libhalcuda.so").exists() and (force or _stale(tr_app, [tr_src, lib, LIB / "libhalcuda.so", LIB / "libpreempt.so"])):
+        _run([CXX, "-std=c++17", "-O1", "-g", f"-I{CUDA_HOME}/include", f"-I{INC}", "-o", tr_app, tr_src, f"-L{link}", f"-L{LIB}",
+              f"-Wl,-rpath,{LIB}", "-lhalcuda", "-lpreempt", "-lcuda", "-ldl", "-pthread"], verbose)
     # the level-2 path of the CUDA HAL with fake preemptible tasks: the HAL's own sources + fake_xpk.cpp in place of libxpk
     l2_src, xpk_src, l2_app = d / "level2_app.cpp", d / "fake_xpk.cpp", d / "level2_app"
     hal_srcs = sorted((CSRC / "hal_cuda").glob("*.cpp"))

@@ -444,16 +444,8 @@ struct HpWork {
 static XResult HpCopyIn(HwQueueHandle hwq, void *data) {
     HpWork *w = (HpWork *)data;
     cudaStream_t s = (cudaStream_t)(uintptr_t)hwq;
-    if (w->keys) return cudaMemcpyAsync(w->keys, w->keys0, w->n * 4, cudaMemcpyDeviceToDevice, s) == cudaSuccess ? kXSchedSuccess : kXSchedErrorHardware;
-    if (cudaMemcpyAsync(w->a, w->ha, w->n * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) return kXSchedErrorHardware;
-    if (cudaMemcpyAsync(w->b, w->hb, w->n * 4, cudaMemcpyHostToDevice, s) != cudaSuccess) return kXSchedErrorHardware;
-    return kXSchedSuccess;
+    return cudaMemcpyAsync(w->keys, w->keys0, w->n * 4, cudaMemcpyDeviceToDevice, s) == cudaSuccess ? kXSchedSuccess : kXSchedErrorHardware;
 }
-static XResult HpCopyOut(HwQueueHandle hwq, void *data) {
-    HpWork *w = (HpWork *)data;
-    return cudaMemcpyAsync(w->hc, w->c, w->n * 4, cudaMemcpyDeviceToHost, (cudaStream_t)(uintptr_t)hwq) == cudaSuccess ? kXSchedSuccess : kXSchedErrorHardware;
-}
-
 static HpWork BuildHp(const Args &a, const Queue &q) {
     HpWork w;
     w.n = a.hp_n; w.e2e = a.e2e != 0; w.stream = q.stream;
@@ -490,10 +482,17 @@ static double HpOnce(const Queue &q, HpWork &w, uint64_t index = 0) {
     if (trace) XTraceStamp(xsched::utils::kTraceAppSubmit, index, 0);
     const int64_t t0 = NowNs();
     HwCommandHandle c;
-    if (w.e2e || w.keys) { XK(HwCommandCreateCallback(&c, HpCopyIn, &w)); XK(XQueueSubmit(q.xq, c)); }
+    if (w.keys) { XK(HwCommandCreateCallback(&c, HpCopyIn, &w)); XK(XQueueSubmit(q.xq, c)); }       // the sort's unsorted input (device to device)
+    else if (w.e2e) {
+        // The request's inputs from pinned host memory, as copy commands of the CUDA backend: they carry the
+        // transfer-only property, which XSCHED_TRANSFER_AWARE_READY=ON uses to leave lower priorities running
+        // until the kernel is about to start.
+        XK(CudaMemcpyCommandCreate(&c, w.a, w.ha, w.n * 4, 0)); XK(XQueueSubmit(q.xq, c));
+        XK(CudaMemcpyCommandCreate(&c, w.b, w.hb, w.n * 4, 0)); XK(XQueueSubmit(q.xq, c));
+    }
     XK(CudaXpkCommandCreate(&c, w.task, 1));
     XK(XQueueSubmit(q.xq, c));
-    if (w.e2e && !w.keys) { XK(HwCommandCreateCallback(&c, HpCopyOut, &w)); XK(XQueueSubmit(q.xq, c)); }
+    if (w.e2e && !w.keys) { XK(CudaMemcpyCommandCreate(&c, w.hc, w.c, w.n * 4, 1)); XK(XQueueSubmit(q.xq, c)); }
     XK(XQueueWaitAll(q.xq));
     const double us = (NowNs() - t0) / 1e3;
     if (trace) {

@@ -213,7 +213,8 @@ bool IsPageableHost(const void *p) {
 }
 
 CudaMemcpyCommand::CudaMemcpyCommand(CopyKind kind, CUdeviceptr dst, CUdeviceptr src, size_t bytes, bool stage_source)
-    : CudaCommand(preempt::kCommandPropertyNone), kind_(kind), dst_(dst), src_(src), bytes_(bytes) {
+    : CudaCommand(kind == CopyKind::kHtoD || kind == CopyKind::kDtoH ? preempt::kCommandPropertyTransferOnly : preempt::kCommandPropertyNone),
+      kind_(kind), dst_(dst), src_(src), bytes_(bytes) {
     if (stage_source && bytes) {
         const unsigned char *p = (const unsigned char *)(uintptr_t)src;
         staged_.assign(p, p + bytes);

@@ -244,6 +244,13 @@ EXPORT_C_FUNC XResult CudaXpkCommandCreate(HwCommandHandle *hw_cmd, void *xpk_ta
     return kXSchedSuccess;
 }
 
+EXPORT_C_FUNC XResult CudaMemcpyCommandCreate(HwCommandHandle *hw_cmd, void *dst, const void *src, size_t bytes, int kind) {
+    if (hw_cmd == nullptr || dst == nullptr || src == nullptr || kind < 0 || kind > 2) return kXSchedErrorInvalidValue;
+    const CopyKind k = kind == 0 ? CopyKind::kHtoD : (kind == 1 ? CopyKind::kDtoH : CopyKind::kDtoD);
+    *hw_cmd = HwCommandManager::Add(std::make_shared<CudaMemcpyCommand>(k, (CUdeviceptr)(uintptr_t)dst, (CUdeviceptr)(uintptr_t)src, bytes));
+    return kXSchedSuccess;
+}
+
 EXPORT_C_FUNC XResult CudaQueueGetStats(HwQueueHandle hwq, CudaQueueStats *stats) {
     if (stats == nullptr) return kXSchedErrorInvalidValue;
     auto q = std::dynamic_pointer_cast<CudaQueue>(HwQueueManager::Get(hwq));

@@ -3,7 +3,9 @@
 #include <sys/prctl.h>
 
 #include "xsched/preempt/sched/agent.h"
+#include "xsched/protocol/def.h"
 #include "xsched/sched/wire.h"
+#include "xsched/utils/env.h"
 #include "xsched/utils/trace.h"
 #include "xsched/utils/xassert.h"
 
@@ -17,7 +19,7 @@ WindowedXQueue::WindowedXQueue(std::shared_ptr<HwQueue> hwq, XPreemptLevel level
                  kQueueFeatureDynamicThreshold | kQueueFeatureDynamicBatchSize | kQueueFeatureSyncSuspend |
                  kQueueFeatureResumeDropCommands,
              hwq),
-      level_(level), threshold_(threshold), batch_size_(batch_size) {
+      level_(level), transfer_aware_(GetEnvOption(XSCHED_TRANSFER_AWARE_READY_ENV_NAME, false)), threshold_(threshold), batch_size_(batch_size) {
     XASSERT(level_ > kPreemptLevelUnknown && level_ < kPreemptLevelMax, "invalid preempt level %d", (int)level_);
     XASSERT(threshold_ >= batch_size_, "the in-flight threshold must not be smaller than the batch size");
     tail_marker_ = std::make_shared<XQueueWaitAllCommand>();
@@ -50,7 +52,10 @@ void WindowedXQueue::Enqueue(std::shared_ptr<XCommand> cmd) {
         std::lock_guard<std::mutex> lk(q_mu_);
         if (cmd->GetType() == kCommandTypeHardware && state_ == kQueueStateIdle) {
             state_ = kQueueStateReady;
-            became_ready = true;
+            // A transfer by itself is not announced (transfer-aware mode): the worker announces the queue when a
+            // compute command is about to be launched.
+            became_ready = !(transfer_aware_ && cmd->GetProps(kCommandPropertyTransferOnly));
+            if (became_ready) announced_ = true;
         }
         tail_is_marker_ = false;
         pending_.push_back(std::move(cmd));
@@ -59,23 +64,37 @@ void WindowedXQueue::Enqueue(std::shared_ptr<XCommand> cmd) {
     if (became_ready) { SchedAgent::SendEvent(Event::XQueueReady(kHandle, ready_us)); XTRACE(utils::kTraceReadySent, kHandle); }
 }
 
+void WindowedXQueue::Announce(bool ready) {
+    {
+        std::lock_guard<std::mutex> lk(q_mu_);
+        if (announced_ == ready) return;
+        announced_ = ready;
+    }
+    if (ready) { SchedAgent::SendEvent(Event::XQueueReady(kHandle, sched::NowEpochUs())); XTRACE(utils::kTraceReadySent, kHandle); }
+    else { SchedAgent::SendEvent(Event::XQueueIdle(kHandle)); XTRACE(utils::kTraceIdleSent, kHandle); }
+}
+
 // Next pending command.  With nothing pending: returns nullptr when `block_when_empty` is false;
 // otherwise declares the queue idle (everything submitted has completed) and sleeps.
 std::shared_ptr<XCommand> WindowedXQueue::TakeOrIdle(bool block_when_empty) {
     std::unique_lock<std::mutex> lk(q_mu_);
     if (pending_.empty()) {
         if (!block_when_empty) return nullptr;
-        bool became_idle = false;
+        bool became_idle = false, tell = false;
         if (state_ == kQueueStateReady) {
             state_ = kQueueStateIdle;
             ++idle_epochs_;
             became_idle = true;
+            tell = announced_;                     // a queue that only ever held transfers was never announced
+            announced_ = false;
         }
         if (became_idle) {
             lk.unlock();
             idle_cv_.notify_all();
-            SchedAgent::SendEvent(Event::XQueueIdle(kHandle));
-            XTRACE(utils::kTraceIdleSent, kHandle);
+            if (tell) {
+                SchedAgent::SendEvent(Event::XQueueIdle(kHandle));
+                XTRACE(utils::kTraceIdleSent, kHandle);
+            }
             lk.lock();
         }
         q_cv_.wait(lk, [this] { return !pending_.empty(); });
@@ -272,6 +291,33 @@ void WindowedXQueue::LaunchOne(std::shared_ptr<HwCommand> cmd) {
 
     cmd->BeforeLaunch();
     std::unique_lock<std::mutex> lk(w_mu_);
+
+    if (transfer_aware_) {
+        const bool transfer = cmd->GetProps(kCommandPropertyTransferOnly) != 0;
+        bool announced, compute_pending = false;
+        {
+            std::lock_guard<std::mutex> ql(q_mu_);
+            announced = announced_;
+            if (transfer && announced)
+                for (const auto &p : pending_)
+                    if (p->GetType() == kCommandTypeHardware && !p->GetProps(kCommandPropertyTransferOnly)) { compute_pending = true; break; }
+        }
+        if (!transfer && !announced) {
+            // First compute command after transfers: it cannot start before they are done, so neither does the
+            // queue need the compute units before then.  Wait for them, then tell the scheduler.
+            SyncAllLocked(lk);
+            lk.unlock();
+            Announce(true);
+            lk.lock();
+        } else if (transfer && announced && !compute_pending) {
+            // A transfer behind the last compute command: once that one has finished the queue holds no compute
+            // work any more; say so before the transfer is handed over.
+            SyncAllLocked(lk);
+            lk.unlock();
+            Announce(false);
+            lk.lock();
+        }
+    }
 
     if (fence_deactivatable) {
         bool found = false;

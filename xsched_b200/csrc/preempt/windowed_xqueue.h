@@ -72,6 +72,13 @@ private:
     bool tail_is_marker_ = true;
     XQueueState state_ = kQueueStateIdle;
     uint64_t idle_epochs_ = 0;
+    // What the scheduler has been told.  Without XSCHED_TRANSFER_AWARE_READY it is the same as state_; with it, a
+    // queue holding only transfer commands stays unannounced, the ready event is sent by the worker when it is about
+    // to launch a compute command (after the transfers before it have finished), and the idle event when a transfer
+    // follows the last compute command (after that one has finished).
+    const bool transfer_aware_;
+    bool announced_ = false;                      // guarded by q_mu_
+    void Announce(bool ready);                    // sends the event if the announced state changes
 
     std::mutex w_mu_;
     std::condition_variable w_cv_;                // pause lifted / terminated

@@ -128,8 +128,8 @@ def main() -> None:
                 logits = torch.nn.functional.rms_norm(x, (H,), norm, 1e-5) @ lm_head.T
                 return logits.argmax(dim=-1).tolist()      # the device->host read of the step's result
 
-            for i in range(3):
-                bstep(min(2, a.max_batch), [i] * min(2, a.max_batch))          # warm-up
+            for n in list(range(1, a.max_batch + 1)) * 2:                      # warm-up: every batch size once picks its kernels
+                bstep(n, [n] * n)
             print("READY", flush=True)
             t0 = time.perf_counter()
             arrivals, t = [], t0
