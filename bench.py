@@ -765,6 +765,9 @@ def main() -> None:
     ap.add_argument("--profile-case", default="", choices=["", "gemm", "triad", "sort", "vecadd"],
                     help="run a few launches of ONE kernel and print their CUDA-event times (the small case the ncu captures use); "
                          "with --m/--n/--k, --elems, --reps, --flags (0 preemptible, 1 twin without the flag poll, 2 GEMM with in-flight abort), --tile")
+    ap.add_argument("--roofline-only", action="store_true",
+                    help="run only the roofline leg (the GEMM timed with CUDA events in this process, no worker processes) and print its "
+                         "JSON: the single-process case an ncu launch list can be taken of")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -778,6 +781,10 @@ def main() -> None:
         return
     if args.profile_case:
         profile_case(args)
+        return
+    if args.roofline_only:
+        roof, n = gemm_roofline(0)
+        print(json.dumps(dict(roof, launches=n)))
         return
     if args.config == 4:
         line = config4(args)

@@ -41,8 +41,9 @@ void note_launches(unsigned n);      // pk_api.cu: the library-wide launch count
 
 constexpr int kSortThreads = 256;
 constexpr int kSortWarps   = kSortThreads / 32;
-constexpr int kSortItems   = 16;
+constexpr int kSortItems   = 16;                  // keys per thread (even: ranks are kept two per register; 20 and 24 measured no faster)
 constexpr int kSortTile    = kSortThreads * kSortItems;   // 4096 keys
+static_assert(kSortItems % 2 == 0 && kSortTile <= 65536, "ranks are packed as 16-bit pairs");
 constexpr int kSortCtasPerSm = 4;
 static_assert(kSortThreads == 256, "one thread per digit: the scans and the look-back assume 256 threads");
 constexpr int kRadix       = 256;
@@ -204,7 +205,7 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
 
             // ---- load (warp-striped) ----
             uint32_t key[kSortItems];
-            uint32_t rank[kSortItems];
+            uint32_t rank2[kSortItems / 2];            // two 16-bit ranks per word (a rank is below the tile size)
             const uint32_t wbase = warp * (32 * kSortItems);
 #pragma unroll
             for (int i = 0; i < kSortItems; ++i) {
@@ -232,7 +233,8 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
                     wh[d] = base + __popc(mask);
                     *(volatile uint32_t *)mw = 0;
                 }
-                rank[i] = base + __popc(mask & lower);
+                const uint32_t r = base + __popc(mask & lower);
+                if (i & 1) rank2[i >> 1] |= r << 16; else rank2[i >> 1] = r;
                 // No barrier here: the next item uses the other mask table, and its first barrier orders this
                 // counter update before the next read of the counters.
             }
@@ -311,7 +313,8 @@ radix_sort_kernel(Ctl *ctl, uint32_t *keys, uint32_t *tmp, uint32_t *hist, uint3
 #pragma unroll
             for (int i = 0; i < kSortItems; ++i) {
                 const uint32_t d = (key[i] >> shift) & 255u;
-                sm.keys[sm.tile_off[d] + sm.warp_hist[warp][d] + rank[i]] = key[i];
+                const uint32_t r = (i & 1) ? rank2[i >> 1] >> 16 : rank2[i >> 1] & 0xFFFFu;
+                sm.keys[sm.tile_off[d] + sm.warp_hist[warp][d] + r] = key[i];
             }
             __syncthreads();
 
