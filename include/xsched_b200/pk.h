@@ -64,6 +64,13 @@ enum {
     XPK_FLAG_ABORT_INFLIGHT = 2, /* GEMM only: on preemption abandon tiles whose main
                                      loop is still running and recompute them on resume
                                      (keeps the preemption latency below one tile).     */
+    XPK_FLAG_GEMM_ONE_CTA   = 4, /* GEMM only: run the form in which one CTA owns a 256x256
+                                     tile (tcgen05 .cta_group::1).                         */
+    XPK_FLAG_GEMM_CTA_PAIR  = 8, /* GEMM only: run the form in which the two SMs of a TPC
+                                     share a 256x256 tile (tcgen05 .cta_group::2).  With
+                                     neither flag the library chooses (XPK_GEMM_FORM=one|pair
+                                     in the environment overrides its choice).  Both forms
+                                     write the same bytes.                                 */
 };
 
 typedef struct xpkTask_st *xpkTask_t;

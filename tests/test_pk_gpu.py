@@ -260,6 +260,14 @@ def test_sort_16m_preempt_resume_bit_exact(pk, ok):
 
 
 # --------------------------------------------------------------------------- GEMM
+# The GEMM exists in two forms (one CTA per 256x256 tile; a pair of CTAs per 512x256 tile) that must write the same bytes.
+FORMS = ["one", "pair"]
+
+
+def _form_flag(pk, form):
+    return {"one": pk.FLAG_GEMM_ONE_CTA, "pair": pk.FLAG_GEMM_CTA_PAIR}[form]
+
+
 def _gemm_inputs(M, N, K, seed, std=1.0):
     g = torch.Generator(device="cpu").manual_seed(seed)
     a = (torch.randn(M, K, generator=g) * std).to(torch.bfloat16)
@@ -280,39 +288,41 @@ def _check_rows(ok, c_gpu, a, b, rows):
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 512), (256, 512, 256), (1024, 1024, 1024),
-                                   (384, 768, 320), (2048, 4096, 192)])
+                                   (384, 768, 320), (2048, 4096, 192), (640, 256, 128), (4608, 5120, 256)])
 def test_gemm_matches_oracle(pk, ok, shape):
     M, N, K = shape
     a, b = _gemm_inputs(M, N, K, seed=M + N + K)
     ad, bd = a.cuda(), b.cuda()
     outs = []
-    for flags in (pk.FLAG_NONE, pk.FLAG_ABORT_INFLIGHT, pk.FLAG_NON_PREEMPTIBLE):
-        c = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
-        t = pk.Task.gemm(c, ad, bd, flags=flags)
-        _run_to_completion(t, pk)
-        outs.append(c)
-        t.destroy()
+    for form in FORMS:
+        for flags in (pk.FLAG_NONE, pk.FLAG_ABORT_INFLIGHT, pk.FLAG_NON_PREEMPTIBLE):
+            c = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+            t = pk.Task.gemm(c, ad, bd, flags=flags | _form_flag(pk, form))
+            _run_to_completion(t, pk)
+            outs.append(c)
+            t.destroy()
     rows = sorted(set([0, 1, 63, 64, 127, M // 2, M - 1] + list(range(128, min(M, 136)))))
     _check_rows(ok, outs[0], a, b, rows)
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
     # library cross-check (different accumulation order, so only approximately equal)
     ref = (ad.float() @ bd.float().T)
     err = (outs[0].float() - ref).abs().max().item()
     assert err <= ref.abs().max().item() * 2.0**-7 + 1e-2
 
 
+@pytest.mark.parametrize("form", FORMS)
 @pytest.mark.parametrize("flags_name", ["tile", "abort"])
-def test_gemm_preempt_resume_bit_exact(pk, ok, flags_name):
+def test_gemm_preempt_resume_bit_exact(pk, ok, flags_name, form):
     M = N = K = 4096
     a, b = _gemm_inputs(M, N, K, seed=1)
     ad, bd = a.cuda(), b.cuda()
     base = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
-    t0 = pk.Task.gemm(base, ad, bd)
+    t0 = pk.Task.gemm(base, ad, bd, flags=pk.FLAG_GEMM_ONE_CTA)
     _run_to_completion(t0, pk)
     t0.destroy()
     _check_rows(ok, base, a, b, [0, 777, 4095])
 
-    flags = pk.FLAG_ABORT_INFLIGHT if flags_name == "abort" else pk.FLAG_NONE
+    flags = (pk.FLAG_ABORT_INFLIGHT if flags_name == "abort" else pk.FLAG_NONE) | _form_flag(pk, form)
     c = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
     t = pk.Task.gemm(c, ad, bd, flags=flags)
     cuts = 0
@@ -345,11 +355,12 @@ def _check_rows_scaled(ok, c_gpu, a, b, rows, scale):
     assert np.abs(ref).max() > 10 * tol.min()           # the rows are not trivially within tolerance
 
 
+@pytest.mark.parametrize("form", FORMS)
 @pytest.mark.parametrize("shape,b_std", [((8192, 8192, 8192), 1.0), ((16384, 14336, 4096), 0.02)],
                          ids=["8192cubed", "16384x4096_by_4096x14336_weights_0.02"])
-def test_gemm_baseline_shapes_against_fp64_rows(pk, ok, shape, b_std):
+def test_gemm_baseline_shapes_against_fp64_rows(pk, ok, shape, b_std, form):
     """The two GEMM shapes of the workload configurations (8192^3 with N(0,1) operands; the inference-shaped
-    (16384x4096)(4096x14336) with weights ~ N(0, 0.02)): eight sampled rows — first and last row of the first and
+    (16384x4096)(4096x14336) with weights ~ N(0, 0.02)): eleven sampled rows — first and last row of the first and
     last row-block, rows either side of the 128-row accumulator boundary — against the fp64 product, for a straight
     run and for a run cut at least three times with in-flight abort; the two runs must also agree bit for bit."""
     M, N, K = shape
@@ -357,16 +368,16 @@ def test_gemm_baseline_shapes_against_fp64_rows(pk, ok, shape, b_std):
     a = torch.randn(M, K, generator=g).to(torch.bfloat16)
     b = (torch.randn(N, K, generator=g) * b_std).to(torch.bfloat16)
     ad, bd = a.cuda(), b.cuda()
-    rows = [0, 127, 128, 255, M // 2 + 1, M - 256, M - 129, M - 1]
+    rows = [0, 127, 128, 255, 256, 383, 511, M // 2 + 1, M - 256, M - 129, M - 1]
     base = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
-    t0 = pk.Task.gemm(base, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT)
+    t0 = pk.Task.gemm(base, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT | _form_flag(pk, form))
     assert _run_to_completion(t0, pk) == 1
     t0.destroy()
     assert not bool(torch.isnan(base).any())
     _check_rows_scaled(ok, base, a, b, rows, b_std)
 
     c = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
-    t = pk.Task.gemm(c, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT)
+    t = pk.Task.gemm(c, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT | _form_flag(pk, form))
     cuts = 0
     for sm_limit in (4, 16, 64, 148, 148):
         info = _preempt_once(t, pk, sm_limit=sm_limit)
@@ -397,7 +408,8 @@ def test_sort_64m_keys_against_numpy(pk):
     t.destroy()
 
 
-def test_gemm_stops_on_the_relayed_host_word_alone(pk, ok):
+@pytest.mark.parametrize("form", FORMS)
+def test_gemm_stops_on_the_relayed_host_word_alone(pk, ok, form):
     """The flag's early-warning word in mapped host memory: a plain host store to it, with the device flag itself
     never written, must stop a running GEMM (the relay thread of its first CTA raises the flag), and the resumed
     task must give the bytes of a straight run."""
@@ -412,7 +424,7 @@ def test_gemm_stops_on_the_relayed_host_word_alone(pk, ok):
     flag = pk.Flag()
     word = flag.attach_relay()
     c = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
-    t = pk.Task.gemm(c, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT, flag=flag)
+    t = pk.Task.gemm(c, ad, bd, flags=pk.FLAG_ABORT_INFLIGHT | _form_flag(pk, form), flag=flag)
     stopped = 0
     for _ in range(4):
         # ten launches back to back (7 ms of work), the word raised 200 us into them

@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -31,6 +32,11 @@ cudaError_t gemm_prepare();
 unsigned long long gemm_tiles(uint32_t M, uint32_t N);
 cudaError_t launch_gemm(bool preemptible, bool abort_inflight, Ctl *ctl, const void *map_a, const void *map_b, void *C,
                         uint32_t M, uint32_t N, uint32_t K, unsigned long long launch_no, int grid, cudaStream_t stream);
+// gemm_pair.cu
+cudaError_t gemm_pair_prepare();
+unsigned long long gemm_pair_tiles(uint32_t M, uint32_t N);
+cudaError_t launch_gemm_pair(bool preemptible, bool abort_inflight, Ctl *ctl, const void *map_a, const void *map_b, void *C,
+                             uint32_t M, uint32_t N, uint32_t K, unsigned long long launch_no, int grid, cudaStream_t stream);
 } // namespace xpk
 
 using xpk::Ctl;
@@ -59,12 +65,14 @@ struct xpkTask_st {
     uint32_t *sort_hist = nullptr, *sort_state = nullptr;
     size_t sort_scratch_bytes = 0;
     uint32_t M = 0, N = 0, K = 0;
+    bool gemm_pair = false;           // the two-CTA form (tensor maps with 128-row boxes)
     alignas(64) unsigned char map_a[128];
     alignas(64) unsigned char map_b[128];
 };
 
 namespace {
 
+constexpr bool kGemmPairByDefault = false;
 std::atomic<uint64_t> g_launches{0};
 } // namespace
 namespace xpk { void note_launches(unsigned n) { g_launches.fetch_add(n); } }
@@ -315,18 +323,30 @@ xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void 
     if (!aligned16(C) || !aligned16(A) || !aligned16(B)) return XPK_ERR_ALIGNMENT;
     xpkTask_st *t = new (std::nothrow) xpkTask_st();
     if (!t) return XPK_ERR_CUDA;
-    xpkResult r = task_common(t, XPK_KIND_GEMM, flags, xpk::gemm_tiles(M, N), flag_dev);
+    // Which form runs the task: a flag decides, else XPK_GEMM_FORM=one|pair, else the library's choice.  A pair needs two SMs.
+    bool use_pair = kGemmPairByDefault;
+    if (const char *form = std::getenv("XPK_GEMM_FORM")) use_pair = std::strcmp(form, "one") != 0;
+    if (flags & XPK_FLAG_GEMM_ONE_CTA) use_pair = false;
+    else if (flags & XPK_FLAG_GEMM_CTA_PAIR) use_pair = true;
+    {
+        int sms = 0, dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { task_free(t); return XPK_ERR_CUDA; }
+        if (sms < 2) use_pair = false;
+    }
+    xpkResult r = task_common(t, XPK_KIND_GEMM, flags, use_pair ? xpk::gemm_pair_tiles(M, N) : xpk::gemm_tiles(M, N), flag_dev);
     if (r != XPK_SUCCESS) { task_free(t); return r; }
     t->p0 = C; t->p1 = A; t->p2 = B; t->M = M; t->N = N; t->K = K;
+    t->gemm_pair = use_pair;
     DeviceState *d = device_state(nullptr);
     {
         std::lock_guard<std::mutex> lk(g_dev_mtx);
         if (!d->gemm_ready) {
-            if (xpk::gemm_prepare() != cudaSuccess) { task_free(t); return XPK_ERR_CUDA; }
+            if (xpk::gemm_prepare() != cudaSuccess || xpk::gemm_pair_prepare() != cudaSuccess) { task_free(t); return XPK_ERR_CUDA; }
             d->gemm_ready = true;
         }
     }
-    if (xpk::gemm_make_map(t->map_a, A, M, K, 256) != 0 || xpk::gemm_make_map(t->map_b, B, N, K, 256) != 0) {
+    const uint32_t box_rows = t->gemm_pair ? 128 : 256;
+    if (xpk::gemm_make_map(t->map_a, A, M, K, box_rows) != 0 || xpk::gemm_make_map(t->map_b, B, N, K, box_rows) != 0) {
         task_free(t);
         return XPK_ERR_CUDA;
     }
@@ -363,6 +383,14 @@ xpkResult xpkTaskLaunch(xpkTask_t t, void *stream, int sm_limit) {
         break;
     case XPK_KIND_GEMM:
         grid = (unsigned long long)sms;
+        if (t->gemm_pair) {
+            // Whole pairs only, one pair per tile at most; an SM limit of one still gets a pair.
+            if (grid > 2 * t->total) grid = 2 * t->total;
+            grid = grid < 2 ? 2 : grid & ~1ull;
+            e = xpk::launch_gemm_pair(preemptible, (t->flags & XPK_FLAG_ABORT_INFLIGHT) != 0, t->ctl, t->map_a, t->map_b, t->p0,
+                                      t->M, t->N, t->K, launch_no, (int)grid, s);
+            break;
+        }
         if (grid > t->total) grid = t->total;
         e = xpk::launch_gemm(preemptible, (t->flags & XPK_FLAG_ABORT_INFLIGHT) != 0, t->ctl, t->map_a, t->map_b, t->p0,
                              t->M, t->N, t->K, launch_no, (int)grid, s);

@@ -19,7 +19,7 @@ lib = C.CDLL(str(_LIB_PATH))
 SUCCESS = 0
 STATUS_IDLE, STATUS_RUNNING, STATUS_COMPLETED, STATUS_PREEMPTED, STATUS_ERROR = range(5)
 KIND_TRIAD, KIND_VECADD, KIND_SORT, KIND_GEMM = 1, 2, 3, 4
-FLAG_NONE, FLAG_NON_PREEMPTIBLE, FLAG_ABORT_INFLIGHT = 0, 1, 2
+FLAG_NONE, FLAG_NON_PREEMPTIBLE, FLAG_ABORT_INFLIGHT, FLAG_GEMM_ONE_CTA, FLAG_GEMM_CTA_PAIR = 0, 1, 2, 4, 8
 
 #: every symbol include/xsched_b200/pk.h declares
 EXPORTS = [
