@@ -482,7 +482,7 @@ def gemm_roofline(device: int) -> tuple[dict, int]:
     pk_ = peaks()
     achieved = 2.0 * M * N * K / (avg * 1e-3) / 1e12
     t.destroy()
-    return ({"bound": "tensor", "kernel": "gemm_bf16_kernel<preemptible, abort>", "achieved": round(achieved, 1),
+    return ({"bound": "tensor", "kernel": "gemm_bf16_pair_kernel<preemptible, abort>", "achieved": round(achieved, 1),
              "peak": pk_["bf16_tflops"], "peak_source": pk_["source"] + " bf16_tflops (burst: kernel timed alone)", "unit": "TFLOP/s",
              "frac": round(achieved / pk_["bf16_tflops"], 4), "avg_launch_ms": round(avg, 4), "median_launch_ms": round(ms[len(ms) // 2], 4),
              # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu

@@ -137,6 +137,9 @@ __global__ void SampleHash(const uint32_t *p, uint64_t words, uint64_t stride_wo
     for (int o = 16; o; o >>= 1) h += __shfl_down_sync(0xffffffffu, h, o);
     if ((threadIdx.x & 31) == 0 && h) atomicAdd(out, h);
 }
+// The checks run on a side stream while the next iterations' kernels occupy the GPU: blocks of 128 threads (5 K
+// registers) still find room on an SM beside a CTA of the two-CTA GEMM, which holds 59 K of its 64 K registers.
+constexpr int kCheckBlocks = 1184, kCheckThreads = 128;
 struct Verifier {
     cudaStream_t side = nullptr;
     unsigned long long *dev = nullptr, *host = nullptr;
@@ -147,13 +150,13 @@ struct Verifier {
     }
     unsigned long long Hash(const void *p, uint64_t words, uint64_t stride_words) {
         CK(cudaMemsetAsync(dev, 0, 8, side));
-        SampleHash<<<592, 256, 0, side>>>((const uint32_t *)p, words, stride_words, dev);
+        SampleHash<<<kCheckBlocks, kCheckThreads, 0, side>>>((const uint32_t *)p, words, stride_words, dev);
         CK(cudaMemcpyAsync(host, dev, 8, cudaMemcpyDeviceToHost, side));
         CK(cudaStreamSynchronize(side));
         return *host;
     }
     void Poison(void *p, uint64_t words, uint64_t stride_words) {
-        SamplePoison<<<592, 256, 0, side>>>((uint32_t *)p, words, stride_words);
+        SamplePoison<<<kCheckBlocks, kCheckThreads, 0, side>>>((uint32_t *)p, words, stride_words);
         CK(cudaStreamSynchronize(side));
     }
 };

@@ -59,6 +59,7 @@ constexpr uint32_t kOperandBytes = kHalf * kBK * 2;     // 16 KiB
 constexpr uint32_t kStageBytes = 3 * kOperandBytes;     // per CTA and stage: two blocks of A, one of B
 constexpr uint32_t kTmemCols = 512;
 constexpr int kAbortPollEvery = 2;
+constexpr uint32_t kParkNs = 1000;                      // longest a waiting thread stays parked before it looks at the abort word again
 constexpr int kPairRasterGroup = 8;                     // row-blocks per raster group (8 x 512 rows)
 
 constexpr unsigned long long kTileMask = (1ull << 40) - 1;     // kNoTile + 1 == 0 under the mask
@@ -88,9 +89,6 @@ struct PairShared {
     uint32_t stop_at_start;              // leader: the flag was already up when the launch began
     uint32_t flag_seen;                  // leader: the watcher has seen the preempt flag raised
     uint32_t watch_off;                  // leader: the watcher has given up (a launch longer than its limit); poll the flag directly
-#ifdef XPK_PAIR_PROFILE
-    long long prof_a, prof_c;
-#endif
 };
 constexpr size_t kSmemBytes = 1024 /*align slack*/ + kStages * kStageBytes + sizeof(PairShared);
 
@@ -157,18 +155,6 @@ __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t adesc
 // Instruction descriptor for kind::f16: D fp32, A/B bf16, both K-major, N=256, M=256 (128 rows per CTA).
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kMmaM >> 4) << 24);
 
-#ifdef XPK_PAIR_PROFILE
-__device__ unsigned long long g_prof[16];
-#define PROF_DECL(name) long long name = 0
-#define PROF_T0() const long long prof_t0 = clock64()
-#define PROF_ADD(name) name += clock64() - prof_t0
-#define PROF_SUM(i, v) atomicAdd(&g_prof[i], (unsigned long long)(v))
-#else
-#define PROF_DECL(name)
-#define PROF_T0()
-#define PROF_ADD(name)
-#define PROF_SUM(i, v)
-#endif
 
 struct Ctx {
     PairShared *sh;
@@ -188,7 +174,7 @@ template <bool kRemote, class Quit>
 __device__ __forceinline__ bool bounded_wait(void *bar, uint32_t parity, const Ctx &cx, uint32_t errcode, Quit quit) {
     uint32_t it = 0;
     unsigned long long t0 = 0;
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_hint(bar, parity, kParkNs)) {
         if (quit()) return false;
         if ((++it & 0xFFu) == 0) {
             const unsigned long long now = global_ns();
@@ -280,7 +266,6 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
             const uint32_t peer_permit = in_cta(&sh->permit, 1);
             const uint32_t peer_abort_kseq = in_cta(&sh->abort_kseq, 1), peer_abort_tile_seq = in_cta(&sh->abort_tile_seq, 1);
             const uint32_t my_full = smem_u32(&sh->full[0]);
-            PROF_DECL(p_claim); PROF_DECL(p_empty);
             // The flag as the watcher (warp kRelayWarp) last saw it: a shared-memory read instead of a round trip
             // to L2 in the middle of the load stream.  The twin never looks.
             auto flag_up = [&]() -> bool {
@@ -299,10 +284,8 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
             unsigned long long ticket = take_ticket(ctl);
             while (live) {
                 unsigned long long tile;
-                { PROF_T0();
                 if (flag_up()) { hand_back(ticket); tile = kNoTile; }
                 else tile = resolve_ticket(ctl, cc, ticket);
-                PROF_ADD(p_claim); }
                 const int slot = (int)(tseq % kSchedSlots);
                 const uint32_t sph = (uint32_t)((tseq / kSchedSlots) & 1);
                 if (!bounded_wait<true>(&sh->sched_empty[slot], sph ^ 1u, cx, kErrProducer, [&] { return aborted() == 2u; })) break;
@@ -336,9 +319,7 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                     }
                     const int stage = (int)(kseq % kStages);
                     const uint32_t ph = (uint32_t)((kseq / kStages) & 1);
-                    { PROF_T0();
                     if (!bounded_wait<false>(&sh->empty[stage], ph ^ 1u, cx, kErrProducer, [&] { return aborted() == 2u; })) { live = false; break; }
-                    PROF_ADD(p_empty); }
                     mbar_arrive_expect_tx(&sh->full[stage], 2 * kStageBytes);
                     tma_load_2d_pair(smem_a0 + stage * kOperandBytes, &map_a, my_full + 8u * stage, (int)(kb * kBK), (int)(m_blk * kTileM));
                     tma_load_2d_pair(smem_a1 + stage * kOperandBytes, &map_a, my_full + 8u * stage, (int)(kb * kBK), (int)(m_blk * kTileM + kMmaM));
@@ -348,7 +329,6 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                 ++tseq;
             }
             *(volatile uint32_t *)&sh->relay_stop = 1u;
-            PROF_SUM(0, p_claim); PROF_SUM(1, p_empty);
             // Leave only after every load of the pair that counts on these barriers has landed.
             const unsigned long long first = kseq > (unsigned long long)kStages ? kseq - kStages : 0;
             for (unsigned long long s = first; s < kseq; ++s) {
@@ -359,13 +339,10 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
         } else if (lane == 0) {
             // ======================= peer's producer: follow the leader =======================
             const uint32_t leader_full = in_cta(&sh->full[0], 0), leader_sched_empty = in_cta(&sh->sched_empty[0], 0);
-            PROF_DECL(p_permit); PROF_DECL(p_empty);
             unsigned long long kseq = 0, tseq = 0;
             bool live = true;
             while (live) {
                 const int slot = (int)(tseq % kSchedSlots);
-                const uint32_t sph = (uint32_t)((tseq / kSchedSlots) & 1);
-                (void)sph;
                 // The leader's word for this use of the slot; then the tile goes on this CTA's own ring for its epilogue warps.
                 unsigned long long word = 0;
                 {
@@ -373,6 +350,7 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                     uint32_t it = 0;
                     unsigned long long t0 = 0;
                     while (((word = ld_relaxed_u64(&sh->tile_word[slot])) >> 40) != want) {
+                        __nanosleep(64);
                         if ((++it & 0xFu) != 0) continue;
                         const uint32_t a = aborted();
                         if (a == 2u || (a == 1u && tseq > *(volatile unsigned long long *)&sh->abort_tile_seq)) { live = false; break; }
@@ -392,13 +370,13 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                 uint32_t m_blk, n_blk;
                 tile_coords<kPairRasterGroup>(tile, m_tiles, n_tiles, m_blk, n_blk);
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-                    // With in-flight aborts the leader says, four k-blocks at a time, how far this tile will be loaded;
+                    // With in-flight aborts the leader says, kAbortPollEvery k-blocks at a time, how far this tile will be loaded;
                     // without them a published tile is always loaded whole.
                     if constexpr (kAbort) {
                         uint32_t it = 0;
                         unsigned long long t0 = 0;
-                        PROF_T0();
                         while (ld_relaxed_u64(&sh->permit) <= kseq) {
+                            __nanosleep(200);                      // a permit comes every kAbortPollEvery k-blocks (about a microsecond and a half)
                             if ((++it & 0xFu) != 0) continue;
                             const uint32_t a = aborted();
                             if (a == 2u || (a == 1u && kseq >= *(volatile unsigned long long *)&sh->abort_kseq)) { live = false; break; }
@@ -409,13 +387,10 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                             }
                         }
                         if (!live) break;
-                        PROF_ADD(p_permit);
                     }
                     const int stage = (int)(kseq % kStages);
                     const uint32_t ph = (uint32_t)((kseq / kStages) & 1);
-                    { PROF_T0();
                     if (!bounded_wait<false>(&sh->empty[stage], ph ^ 1u, cx, kErrProducer, [&] { return aborted() == 2u; })) { live = false; break; }
-                    PROF_ADD(p_empty); }
                     tma_load_2d_pair(smem_a0 + stage * kOperandBytes, &map_a, leader_full + 8u * stage, (int)(kb * kBK), (int)(m_blk * kTileM + kHalf));
                     tma_load_2d_pair(smem_a1 + stage * kOperandBytes, &map_a, leader_full + 8u * stage, (int)(kb * kBK), (int)(m_blk * kTileM + kMmaM + kHalf));
                     tma_load_2d_pair(smem_b + stage * kOperandBytes, &map_b, leader_full + 8u * stage, (int)(kb * kBK), (int)(n_blk * kTileN + kHalf));
@@ -423,7 +398,6 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                 }
                 ++tseq;
             }
-            PROF_SUM(2, p_permit); PROF_SUM(3, p_empty);
             // This CTA's loads are counted in the leader.  Every k-block issued here is issued there too and is consumed
             // by an MMA whose commit arrives on `empty` here: waiting for the last of those proves that the loads
             // have landed and that no arrival is still on its way to this CTA's barriers.  After an error (some wait
@@ -445,50 +419,28 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
         if (lane == 0 && leader) {
             unsigned long long kseq = 0, tseq = 0;
             bool issued_any = false;
-#ifdef XPK_PAIR_PROFILE
-            const long long mma_t0 = clock64();
-            long long w_full = 0, w_tile = 0, w_first = 0, w_steady = 0, t_kb8 = 0, w_sched = 0, w_cd = 0, w_ab = 0;
-#endif
             while (true) {
                 const int slot = (int)(tseq % kSchedSlots);
                 const uint32_t sph = (uint32_t)((tseq / kSchedSlots) & 1);
-#ifdef XPK_PAIR_PROFILE
-                const long long tb0 = clock64();
-#endif
                 if (!bounded_wait<false>(&sh->sched_full[slot], sph, cx, kErrMma,
                                          [&] { const uint32_t a = aborted(); return a == 2u || (a == 1u && tseq > *(volatile unsigned long long *)&sh->abort_tile_seq); })) break;
                 const unsigned long long tile = sh->sched_tile[slot];
                 mbar_arrive(&sh->sched_empty[slot]);
                 if (tile == kNoTile) break;
-#ifdef XPK_PAIR_PROFILE
-                w_sched += clock64() - tb0;
-#endif
                 // Both accumulators must have been drained by both CTAs' epilogues of the previous tile.
                 const uint32_t aph = (uint32_t)(tseq & 1);
                 if (!bounded_wait<true>(&sh->tmem_empty, aph ^ 1u, cx, kErrMma, [&] { return aborted() == 2u; })) break;
                 tc_fence_after();
-#ifdef XPK_PAIR_PROFILE
-                w_tile += clock64() - tb0;
-                if (tseq > 0) w_cd += clock64() - *(volatile long long *)&sh->prof_c;
-#endif
                 const uint32_t d_tmem0 = tmem_base, d_tmem1 = tmem_base + (uint32_t)kTileN;
                 bool abandoned = false;
                 for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                     const int stage = (int)(kseq % kStages);
                     const uint32_t ph = (uint32_t)((kseq / kStages) & 1);
-#ifdef XPK_PAIR_PROFILE
-                    const long long f0 = clock64();
-#endif
                     if (!bounded_wait<false>(&sh->full[stage], ph, cx, kErrMma,
                                              [&] { const uint32_t a = aborted(); return a == 2u || (a == 1u && kseq >= *(volatile unsigned long long *)&sh->abort_kseq); })) {
                         abandoned = true;
                         break;
                     }
-#ifdef XPK_PAIR_PROFILE
-                    if (kb < 8) w_first += clock64() - f0; else w_full += clock64() - f0;
-                    if (kb == 8) t_kb8 = clock64();
-                    if (kb == k_blocks - 1) w_steady += clock64() - t_kb8;
-#endif
                     tc_fence_after();
                     // The descriptors name this CTA's shared memory; the peer's tensor core reads the same offsets of its own.
                     const uint64_t adesc0 = make_kmajor_sw128_desc(smem_u32(smem_a0 + stage * kOperandBytes));
@@ -507,11 +459,6 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                 }
                 if (abandoned) break;
                 tc_commit_both(&sh->tmem_full);
-#ifdef XPK_PAIR_PROFILE
-                { const long long ta = clock64();
-                  while (!mbar_try_wait(&sh->tmem_full, (uint32_t)(tseq & 1))) { }
-                  w_ab += clock64() - ta; }
-#endif
                 ++tseq;
             }
             // All issued MMAs must have retired before tensor memory is freed.
@@ -519,9 +466,6 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                 tc_commit_own(&sh->drain);
                 bounded_wait<false>(&sh->drain, 0u, cx, kErrDrain, [] { return false; });
             }
-#ifdef XPK_PAIR_PROFILE
-            PROF_SUM(4, clock64() - mma_t0); PROF_SUM(5, w_full); PROF_SUM(6, w_tile); PROF_SUM(7, w_first); PROF_SUM(8, kseq); PROF_SUM(9, tseq); PROF_SUM(14, w_steady); PROF_SUM(15, w_sched); PROF_SUM(13, w_cd); PROF_SUM(11, w_ab);
-#endif
         }
         __syncwarp();
     } else if (warp == kRelayWarp) {
@@ -554,32 +498,49 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
         const uint32_t quarter = (uint32_t)(warp & 3);            // TMEM lanes [32q, 32q+32)
         const uint32_t leader_sched_empty = in_cta(&sh->sched_empty[0], 0), leader_tmem_empty = in_cta(&sh->tmem_empty, 0);
         unsigned long long tseq = 0;
-        PROF_DECL(e_sum); PROF_DECL(e_store);
         while (true) {
             const int slot = (int)(tseq % kSchedSlots);
             const uint32_t sph = (uint32_t)((tseq / kSchedSlots) & 1);
-            bool ok = bounded_wait<false>(&sh->sched_full[slot], sph, cx, kErrEpilogue,
+            // One lane per warp waits (a barrier wakes few waiters sooner than many); the warp follows it.
+            bool ok = true;
+            if (lane == 0)
+                ok = bounded_wait<false>(&sh->sched_full[slot], sph, cx, kErrEpilogue,
                                          [&] { const uint32_t a = aborted(); return a == 2u || (a == 1u && tseq > *(volatile unsigned long long *)&sh->abort_tile_seq); });
-            ok = __all_sync(0xffffffffu, ok);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             const unsigned long long tile = *(volatile unsigned long long *)&sh->sched_tile[slot];
             __syncwarp();
-            if (lane == 0) remote_arrive(leader_sched_empty + 8u * slot);
+            if (lane == 0) { if (leader) mbar_arrive(&sh->sched_empty[slot]); else remote_arrive(leader_sched_empty + 8u * slot); }
             if (tile == kNoTile) break;
+            uint32_t m_blk, n_blk;
+            tile_coords<kPairRasterGroup>(tile, m_tiles, n_tiles, m_blk, n_blk);     // before the wait: its divisions are off the critical path
             const uint32_t aph = (uint32_t)(tseq & 1);
-#ifdef XPK_PAIR_PROFILE
-            const long long e0 = clock64();
-#endif
-            ok = bounded_wait<false>(&sh->tmem_full, aph, cx, kErrEpilogue,
-                                     [&] { const uint32_t a = aborted(); return a == 2u || (a == 1u && tseq >= *(volatile unsigned long long *)&sh->abort_tile_seq); });
-            ok = __all_sync(0xffffffffu, ok);
+            if (lane == 0)
+                ok = bounded_wait<false>(&sh->tmem_full, aph, cx, kErrEpilogue,
+                                         [&] { const uint32_t a = aborted(); return a == 2u || (a == 1u && tseq >= *(volatile unsigned long long *)&sh->abort_tile_seq); });
+            ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
-            uint32_t m_blk, n_blk;
-            tile_coords<kPairRasterGroup>(tile, m_tiles, n_tiles, m_blk, n_blk);
-#ifdef XPK_PAIR_PROFILE
-            const long long e1 = clock64();
-#endif
+#ifdef XPK_PAIR_STREAMING_EPILOGUE
+            {
+                const uint32_t row0 = m_blk * kTileM + acc * kMmaM + rank * kHalf;
+                if (row0 < M) {
+                    const uint32_t row = row0 + quarter * 32u + (uint32_t)lane;
+                    __nv_bfloat16 *crow = C + (size_t)row * N + (size_t)n_blk * kTileN;
+                    const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * (uint32_t)kTileN;
+#pragma unroll 1
+                    for (int c = 0; c < kTileN; c += 32) {
+                        uint32_t r[32];
+                        tc_ld32(taddr + (uint32_t)c, r);
+                        tc_wait_ld();
+                        store_row32_bf16(crow + c, r);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { if (leader) mbar_arrive(&sh->tmem_empty); else remote_arrive(leader_tmem_empty); }
+            }
+#else
             // The thread's row of the accumulator (256 fp32) is rounded into 128 registers first; tensor memory is
             // handed back to the MMA thread as soon as every warp has done that, and the row is written out while
             // the next tile's MMAs run.
@@ -588,36 +549,35 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
             uint32_t packed[kTileN / 2];
             if (in_range) {
                 const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * (uint32_t)kTileN;
+                // Two loads in flight per wait: a tensor-memory load takes several hundred cycles to come back.
 #pragma unroll
-                for (int c = 0; c < kTileN / 32; ++c) {
-                    uint32_t r[32];
-                    tc_ld32(taddr + (uint32_t)(32 * c), r);
+                for (int c = 0; c < kTileN / 64; ++c) {
+                    uint32_t r0[32], r1[32];
+                    tc_ld32(taddr + (uint32_t)(64 * c), r0);
+                    tc_ld32(taddr + (uint32_t)(64 * c + 32), r1);
                     tc_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                        packed[16 * c + j] = *reinterpret_cast<uint32_t *>(&v);
+                        __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
+                        __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
+                        packed[32 * c + j] = *reinterpret_cast<uint32_t *>(&v0);
+                        packed[32 * c + 16 + j] = *reinterpret_cast<uint32_t *>(&v1);
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-#ifdef XPK_PAIR_PROFILE
-            if (warp == 2 && lane == 0) { e_sum += clock64() - e0; e_store += clock64() - e1; if (leader) *(volatile long long *)&sh->prof_c = clock64(); }
-#endif
-            if (lane == 0) remote_arrive(leader_tmem_empty);
+            if (lane == 0) { if (leader) mbar_arrive(&sh->tmem_empty); else remote_arrive(leader_tmem_empty); }
             if (in_range) {
                 const uint32_t row = row0 + quarter * 32u + (uint32_t)lane;
                 uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)row * N + (size_t)n_blk * kTileN);
 #pragma unroll
                 for (int v = 0; v < kTileN / 8; ++v) dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
             }
+#endif
             if (leader && warp == 2 && lane == 0) ++tiles_done;
             ++tseq;
         }
-#ifdef XPK_PAIR_PROFILE
-        if (warp == 2 && lane == 0) { if (leader) { PROF_SUM(10, e_sum); PROF_SUM(12, e_store); } }
-#endif
     }
 
     // ---- teardown ----
@@ -633,13 +593,6 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
 
 } // namespace pair
 
-#ifdef XPK_PAIR_PROFILE
-extern "C" int xpkDebugPairProfile(unsigned long long *out16, int reset) {
-    if (cudaMemcpyFromSymbol(out16, pair::g_prof, sizeof(pair::g_prof)) != cudaSuccess) return 1;
-    if (reset) { unsigned long long z[16] = {}; if (cudaMemcpyToSymbol(pair::g_prof, z, sizeof(z)) != cudaSuccess) return 1; }
-    return 0;
-}
-#endif
 
 cudaError_t gemm_pair_prepare() {
     cudaError_t e;

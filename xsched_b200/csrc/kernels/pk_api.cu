@@ -72,7 +72,7 @@ struct xpkTask_st {
 
 namespace {
 
-constexpr bool kGemmPairByDefault = false;
+constexpr bool kGemmPairByDefault = true;
 std::atomic<uint64_t> g_launches{0};
 } // namespace
 namespace xpk { void note_launches(unsigned n) { g_launches.fetch_add(n); } }
