@@ -58,6 +58,9 @@ constexpr int kThreads = 64 + 32 * kEpiWarps + 32;
 constexpr uint32_t kOperandBytes = kHalf * kBK * 2;     // 16 KiB
 constexpr uint32_t kStageBytes = 3 * kOperandBytes;     // per CTA and stage: two blocks of A, one of B
 constexpr uint32_t kTmemCols = 512;
+// 11 warps sit 3+3+3+2 on the SM's four register files of 16 K: at 128 registers per thread every file keeps room
+// for warps of other kernels beside this CTA (four warps of 40 registers, say).
+constexpr int kMaxRegs = 128;
 constexpr int kAbortPollEvery = 2;
 constexpr uint32_t kParkNs = 1000;                      // longest a waiting thread stays parked before it looks at the abort word again
 constexpr int kPairRasterGroup = 8;                     // row-blocks per raster group (8 x 512 rows)
@@ -90,7 +93,9 @@ struct PairShared {
     uint32_t flag_seen;                  // leader: the watcher has seen the preempt flag raised
     uint32_t watch_off;                  // leader: the watcher has given up (a launch longer than its limit); poll the flag directly
 };
-constexpr size_t kSmemBytes = 1024 /*align slack*/ + kStages * kStageBytes + sizeof(PairShared);
+constexpr uint32_t kStagingBytes = 32 * 64 * 2;         // per epilogue warp: 32 rows x 64 bf16, where rows are regrouped for coalesced stores
+constexpr size_t kSharedBlockBytes = (sizeof(PairShared) + 127) & ~(size_t)127;
+constexpr size_t kSmemBytes = 1024 /*align slack*/ + kStages * kStageBytes + kSharedBlockBytes + kEpiWarps * kStagingBytes;
 
 // ---- cluster and .cta_group::2 instructions ---------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -189,7 +194,7 @@ __device__ __forceinline__ bool bounded_wait(void *bar, uint32_t parity, const C
 }
 
 template <bool kPreemptible, bool kAbort>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(kMaxRegs)
 gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       __nv_bfloat16 *__restrict__ C, uint32_t M, uint32_t N, uint32_t K, unsigned long long launch_no) {
     extern __shared__ unsigned char smem_raw[];
@@ -521,60 +526,53 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
-#ifdef XPK_PAIR_STREAMING_EPILOGUE
-            {
-                const uint32_t row0 = m_blk * kTileM + acc * kMmaM + rank * kHalf;
-                if (row0 < M) {
-                    const uint32_t row = row0 + quarter * 32u + (uint32_t)lane;
-                    __nv_bfloat16 *crow = C + (size_t)row * N + (size_t)n_blk * kTileN;
-                    const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * (uint32_t)kTileN;
-#pragma unroll 1
-                    for (int c = 0; c < kTileN; c += 32) {
-                        uint32_t r[32];
-                        tc_ld32(taddr + (uint32_t)c, r);
-                        tc_wait_ld();
-                        store_row32_bf16(crow + c, r);
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) { if (leader) mbar_arrive(&sh->tmem_empty); else remote_arrive(leader_tmem_empty); }
-            }
-#else
-            // The thread's row of the accumulator (256 fp32) is rounded into 128 registers first; tensor memory is
-            // handed back to the MMA thread as soon as every warp has done that, and the row is written out while
-            // the next tile's MMAs run.
+            // 64 columns at a time: two tensor-memory loads in flight (a load takes several hundred cycles to come
+            // back), rounded to bf16, written to this warp's staging block in shared memory with the 16-byte pieces of a
+            // row XOR-swizzled by the row number, read back so that eight lanes hold the 128 contiguous bytes of one
+            // row, and stored: a store instruction then covers 4 rows x 128 bytes instead of 32 rows x 16 bytes.
+            // Tensor memory goes back to the MMA thread as soon as the last loads have landed in registers.
             const uint32_t row0 = m_blk * kTileM + acc * kMmaM + rank * kHalf;
             const bool in_range = row0 < M;                           // the last row-block may be filled in part (M is a multiple of 128)
-            uint32_t packed[kTileN / 2];
-            if (in_range) {
-                const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * (uint32_t)kTileN;
-                // Two loads in flight per wait: a tensor-memory load takes several hundred cycles to come back.
-#pragma unroll
-                for (int c = 0; c < kTileN / 64; ++c) {
-                    uint32_t r0[32], r1[32];
-                    tc_ld32(taddr + (uint32_t)(64 * c), r0);
-                    tc_ld32(taddr + (uint32_t)(64 * c + 32), r1);
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * (uint32_t)kTileN;
+            uint4 *stg = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(sh) + kSharedBlockBytes + (size_t)(warp - 2) * kStagingBytes);
+            __nv_bfloat16 *cbase = C + (size_t)(row0 + quarter * 32u) * N + (size_t)n_blk * kTileN;
+#pragma unroll 1
+            for (int c = 0; c < kTileN / 64; ++c) {
+                uint32_t r[64];
+                if (in_range) {
+                    tc_ld32(taddr + (uint32_t)(64 * c), *reinterpret_cast<uint32_t (*)[32]>(&r[0]));
+                    tc_ld32(taddr + (uint32_t)(64 * c + 32), *reinterpret_cast<uint32_t (*)[32]>(&r[32]));
                     tc_wait_ld();
+                }
+                if (c == kTileN / 64 - 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) { if (leader) mbar_arrive(&sh->tmem_empty); else remote_arrive(leader_tmem_empty); }
+                }
+                if (in_range) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(r0[2 * j]), __uint_as_float(r0[2 * j + 1]));
-                        __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(r1[2 * j]), __uint_as_float(r1[2 * j + 1]));
-                        packed[32 * c + j] = *reinterpret_cast<uint32_t *>(&v0);
-                        packed[32 * c + 16 + j] = *reinterpret_cast<uint32_t *>(&v1);
+                    for (int j = 0; j < 8; ++j) {
+                        uint4 o;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                        __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                        o.x = *reinterpret_cast<uint32_t *>(&p0);
+                        o.y = *reinterpret_cast<uint32_t *>(&p1);
+                        o.z = *reinterpret_cast<uint32_t *>(&p2);
+                        o.w = *reinterpret_cast<uint32_t *>(&p3);
+                        stg[lane * 8 + (j ^ (lane & 7))] = o;
                     }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + (lane >> 3), ch = lane & 7;
+                        const uint4 o = stg[rr * 8 + (ch ^ (rr & 7))];
+                        *reinterpret_cast<uint4 *>(cbase + (size_t)rr * N + 64 * c + 8 * ch) = o;
+                    }
+                    __syncwarp();
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) { if (leader) mbar_arrive(&sh->tmem_empty); else remote_arrive(leader_tmem_empty); }
-            if (in_range) {
-                const uint32_t row = row0 + quarter * 32u + (uint32_t)lane;
-                uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)row * N + (size_t)n_blk * kTileN);
-#pragma unroll
-                for (int v = 0; v < kTileN / 8; ++v) dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-            }
-#endif
             if (leader && warp == 2 && lane == 0) ++tiles_done;
             ++tseq;
         }
