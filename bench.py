@@ -487,7 +487,7 @@ def gemm_roofline(device: int) -> tuple[dict, int]:
              "frac": round(achieved / pk_["bf16_tflops"], 4), "avg_launch_ms": round(avg, 4), "median_launch_ms": round(ms[len(ms) // 2], 4),
              # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
              # capture summarised in profiles/gemm_bf16_8192_ncu.md (algorithmic minimum: 402.7 MB)
-             "traffic": 941.2e6, "traffic_source": "ncu, profiles/gemm_bf16_8192_ncu.md"}, reps + 5)
+             "traffic": 945.4e6, "traffic_source": "ncu, profiles/gemm_bf16_8192_ncu.md"}, reps + 5)
 
 
 def reference_config0(level: int, lp_count: int, threshold: int = 16, batch: int = 8, lp_us: int = 1000, hp_us: int = 2000,
