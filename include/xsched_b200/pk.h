@@ -133,7 +133,9 @@ xpkResult xpkTaskCreateSort(xpkTask_t *task, int32_t *keys, int32_t *tmp, void *
 
 /* bf16 GEMM, C[M,N] (row-major, bf16) = A[M,K] (row-major) * B[N,K]^T (row-major, i.e.
  * both operands K-major), fp32 accumulation in tensor memory.  M % 128 == 0,
- * N % 256 == 0, K % 64 == 0.                                                            */
+ * N % 256 == 0, K % 64 == 0.  A tile (the unit of xpkTaskInfo.tiles_*) is 512x256 in the
+ * pair form and 256x256 in the one-CTA form (XPK_FLAG_GEMM_*); the pair form launches whole
+ * pairs of CTAs (an `sm_limit` is rounded down to an even number, at least 2).           */
 xpkResult xpkTaskCreateGemm(xpkTask_t *task, void *C, const void *A, const void *B,
                             uint32_t M, uint32_t N, uint32_t K, uint32_t flags,
                             uint32_t *flag_dev);
