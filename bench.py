@@ -476,7 +476,7 @@ def gemm_roofline(device: int) -> tuple[dict, int]:
     for e0, e1 in evs:                 # inputs (256 MiB) + output exceed L2, so every launch streams from HBM
         t.reset(s)
         e0.record(); t.launch(s); e1.record()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()       # each launch timed alone, as the burst peak it is compared with was measured
     ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
     avg = sum(ms) / len(ms)
     pk_ = peaks()
@@ -487,7 +487,8 @@ def gemm_roofline(device: int) -> tuple[dict, int]:
              "frac": round(achieved / pk_["bf16_tflops"], 4), "avg_launch_ms": round(avg, 4), "median_launch_ms": round(ms[len(ms) // 2], 4),
              # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this size, from the ncu
              # capture summarised in profiles/gemm_bf16_8192_ncu.md (algorithmic minimum: 402.7 MB)
-             "traffic": 945.4e6, "traffic_source": "ncu, profiles/gemm_bf16_8192_ncu.md"}, reps + 5)
+             "traffic": 945.4e6, "traffic_source": "ncu, profiles/gemm_bf16_8192_ncu.md",
+             "timing": "CUDA events around each of 30 launches, a synchronize between launches"}, reps + 5)
 
 
 def reference_config0(level: int, lp_count: int, threshold: int = 16, batch: int = 8, lp_us: int = 1000, hp_us: int = 2000,
