@@ -456,6 +456,50 @@ def transparent_corun(device: int, shim_lib: Path, steps: int, threshold: int, b
             "window": f"threshold {threshold} / batch {batch}"}
 
 
+def mps_leg(device: int, ns: str, lp_kw: dict, requests: int) -> dict:
+    """The headline configuration once more with the two processes sharing the GPU through CUDA MPS (one GPU context
+    for both, so the GPU has no context to switch between them).  A control daemon is started with a private pipe
+    directory, visible to this leg's processes only and restricted to this GPU, and stopped again before the leg
+    returns; nothing about the GPU itself is changed.  The standalone figure is taken under the same daemon."""
+    import shutil, tempfile
+    ctl = shutil.which("nvidia-cuda-mps-control")
+    if ctl is None:
+        return {"unavailable": "nvidia-cuda-mps-control not found"}
+    d = Path(tempfile.mkdtemp(prefix="xsched_mps_"))
+    (d / "pipe").mkdir(); (d / "log").mkdir()
+    mps_env = {"CUDA_MPS_PIPE_DIRECTORY": str(d / "pipe"), "CUDA_MPS_LOG_DIRECTORY": str(d / "log"), "CUDA_VISIBLE_DEVICES": str(device)}
+    ctl_env = dict(os.environ, **mps_env)
+    r = subprocess.run([ctl, "-d"], env=ctl_env, capture_output=True, text=True, timeout=30)
+    if r.returncode != 0:
+        shutil.rmtree(d, ignore_errors=True)
+        return {"unavailable": f"MPS control daemon did not start (rc {r.returncode}): {(r.stderr or r.stdout)[-200:]}"}
+    mns = ns + "mps."
+    srv = None
+    try:
+        env_alone = dict(base_env(mns, "APP"), **mps_env)        # CUDA_VISIBLE_DEVICES names the GPU: the workers see it as device 0
+        hp_alone = run_json(worker_cmd("hp", 0, level=2, prio=1, count=requests, period_us=PERIOD_US, hp_n=HP_N), env_alone, 180)[-1]
+        lp_alone = run_json(worker_cmd("lp", 0, level=2, prio=0, duration_s=3, warmup_s=0.5, **lp_kw), env_alone, 120)[-1]
+        srv = subprocess.Popen([str(XSERVER), "HPF", "0"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=base_env(mns, None))
+        srv.stdout.readline()
+        hp, lp = corun(0, mns, 2, requests, 50, False, PERIOD_US, lp_kw, extra_env=mps_env)
+        return {"hp_p50_us": hp["p50_us"], "hp_p99_us": hp["p99_us"], "hp_standalone_p50_us": hp_alone["p50_us"], "hp_standalone_p99_us": hp_alone["p99_us"],
+                "ratio": round(hp["p99_us"] / hp_alone["p99_us"], 3), "p50_ratio": round(hp["p50_us"] / hp_alone["p50_us"], 3),
+                "bg_kept_pct": round(100 * lp["rate"] / lp_alone["rate"], 2), "bg_tflops_standalone": lp_alone["rate"], "bit_exact": lp["bit_exact"],
+                "lp_iterations_verified": lp.get("verified_iters"), "requests": requests,
+                "note": "same two processes and xserver as the headline; both are clients of one MPS server (started and stopped by this leg)"}
+    finally:
+        if srv is not None:
+            srv.send_signal(signal.SIGTERM)
+            try:
+                srv.wait(timeout=10)
+            except subprocess.TimeoutExpired:
+                srv.kill()
+        try:
+            subprocess.run([ctl], input="quit\n", env=ctl_env, capture_output=True, text=True, timeout=60)
+        finally:
+            shutil.rmtree(d, ignore_errors=True)
+
+
 def gemm_roofline(device: int) -> tuple[dict, int]:
     """Average launch duration of the preemptible GEMM, CUDA events on the launching stream."""
     import torch
@@ -862,6 +906,12 @@ def main() -> None:
                                                    "ratio": nat["ratio_p99"]}
             except Exception as e:
                 extra["one_process_two_queues"] = {"error": str(e)[:300]}
+            if world == 1:
+                try:
+                    mark("two processes under MPS")
+                    extra["two_processes_under_mps"] = mps_leg(device, ns, lp_kw, max(300, side_requests))
+                except Exception as e:
+                    extra["two_processes_under_mps"] = {"error": str(e)[:300]}
             if world == 1 and (LIB / "plain_worker").exists():
                 # Transparent mode, level 1: XSched-unaware processes under a libcuda interposer.  Once with this
                 # repository's shim and once with the REFERENCE's own level-1 CUDA HAL + shim (compiled from its sources
@@ -873,6 +923,19 @@ def main() -> None:
                                         plain_env, 120)[-1]
                     plain_lp = run_json([pw, "--role", "lp", "--device", str(device), "--in-flight", "3", "--duration-s", "3"], plain_env, 120)[-1]
                     tr = {"plain_hp_p99_us": plain_hp["p99_us"], "plain_hp_p50_us": plain_hp["p50_us"], "plain_lp_tflops": plain_lp["rate"]}
+                    # The same two processes with no XSched at all: what the GPU's own time slicing between two
+                    # contexts gives the high-priority process (it switches contexts between kernels only).
+                    for inflight in (3, 1):
+                        mark(f"native sharing of the GPU by two processes, LP with {inflight} kernels in flight")
+                        lp_nat, _ = start_lp([pw, "--role", "lp", "--device", str(device), "--in-flight", str(inflight)], plain_env, "plain LP worker")
+                        try:
+                            r = run_hp_marking([pw, "--role", "hp", "--device", str(device), "--count", "300", "--period-us", str(PERIOD_US), "--hp-n", str(HP_N)],
+                                               plain_env, 120, [lp_nat])[-1]
+                        finally:
+                            lpr = stop_lp(lp_nat, 60)
+                        tr.setdefault("no_scheduler", {})[f"lp_in_flight_{inflight}"] = {
+                            "hp_p50_us": r["p50_us"], "hp_p99_us": r["p99_us"], "ratio_p99": round(r["p99_us"] / plain_hp["p99_us"], 3),
+                            "lp_kept_pct": round(100 * lpr["rate"] / plain_lp["rate"], 2) if lpr.get("rate") else None}
                     shims = {"this_shim": LIB / "libshimcuda.so", "reference_shim": ROOT / "oracle" / "_ref" / "libshimcuda_ref.so"}
                     for name, lib_path in shims.items():
                         if not lib_path.exists():
