@@ -198,7 +198,7 @@ def base_env(ns: str, sched: str | None) -> dict:
 
 
 def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, period_us: int, lp_kw: dict,
-          extra_env: dict | None = None) -> tuple[dict, dict]:
+          extra_env: dict | None = None, hp_kw: dict | None = None) -> tuple[dict, dict]:
     """LP process + HP process under the (already running) xserver; `steps` timed and `warmup` untimed
     high-priority requests.  Returns (hp_json, lp_json)."""
     import tempfile
@@ -228,8 +228,8 @@ def corun(device: int, ns: str, level: int, steps: int, warmup: int, e2e: bool, 
         # budget: every request takes at most a few periods even when things go badly
         hp_timeout = 60 + (steps + warmup) * period_us * 20 / 1e6
         samples_path = tempfile.mktemp(prefix="xsched_hp_", suffix=".txt")
-        hp = run_hp_marking(worker_cmd("hp", device, level=level, prio=1, count=steps + warmup, period_us=period_us, hp_n=HP_N,
-                                       e2e=int(e2e), samples=samples_path), hp_env, hp_timeout, [lp])[-1]
+        hp = run_hp_marking(worker_cmd("hp", device, level=level, prio=1, count=steps + warmup, period_us=period_us,
+                                       **dict(dict(hp_n=HP_N, e2e=int(e2e)), **(hp_kw or {})), samples=samples_path), hp_env, hp_timeout, [lp])[-1]
         hp["samples_us"] = read_samples(samples_path)[warmup:]
         mark(f"corun level {level}: HP done")
     finally:
@@ -482,11 +482,24 @@ def mps_leg(device: int, ns: str, lp_kw: dict, requests: int) -> dict:
         srv = subprocess.Popen([str(XSERVER), "HPF", "0"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, env=base_env(mns, None))
         srv.stdout.readline()
         hp, lp = corun(0, mns, 2, requests, 50, False, PERIOD_US, lp_kw, extra_env=mps_env)
-        return {"hp_p50_us": hp["p50_us"], "hp_p99_us": hp["p99_us"], "hp_standalone_p50_us": hp_alone["p50_us"], "hp_standalone_p99_us": hp_alone["p99_us"],
-                "ratio": round(hp["p99_us"] / hp_alone["p99_us"], 3), "p50_ratio": round(hp["p50_us"] / hp_alone["p50_us"], 3),
-                "bg_kept_pct": round(100 * lp["rate"] / lp_alone["rate"], 2), "bg_tflops_standalone": lp_alone["rate"], "bit_exact": lp["bit_exact"],
-                "lp_iterations_verified": lp.get("verified_iters"), "requests": requests,
-                "note": "same two processes and xserver as the headline; both are clients of one MPS server (started and stopped by this leg)"}
+        out = {"hp_p50_us": hp["p50_us"], "hp_p99_us": hp["p99_us"], "hp_standalone_p50_us": hp_alone["p50_us"], "hp_standalone_p99_us": hp_alone["p99_us"],
+               "ratio": round(hp["p99_us"] / hp_alone["p99_us"], 3), "p50_ratio": round(hp["p50_us"] / hp_alone["p50_us"], 3),
+               "bg_kept_pct": round(100 * lp["rate"] / lp_alone["rate"], 2), "bg_tflops_standalone": lp_alone["rate"], "bit_exact": lp["bit_exact"],
+               "lp_iterations_verified": lp.get("verified_iters"), "requests": requests,
+               "note": "same two processes and xserver as the headline; both are clients of one MPS server (started and stopped by this leg)"}
+        try:        # workload configuration 3 (sort every 5 ms against the triad) under the same daemon
+            tri_kw = dict(kernel="triad", n=1 << 31, depth=2, threshold=2, batch=1)
+            sort_kw = dict(hp_kernel="sort", hp_n=1 << 24)
+            sort_alone = run_json(worker_cmd("hp", 0, level=2, prio=1, count=300, period_us=5000, **sort_kw), env_alone, 180)[-1]
+            tri_alone = run_json(worker_cmd("lp", 0, level=2, prio=0, duration_s=3, warmup_s=0.5, **tri_kw), env_alone, 180)[-1]
+            s_co, t_co = corun(0, mns, 2, 300, 20, False, 5000, tri_kw, extra_env=mps_env, hp_kw=sort_kw)
+            out["config3_triad_vs_sort"] = {"hp_sort_p99_us": s_co["p99_us"], "hp_sort_standalone_p99_us": sort_alone["p99_us"],
+                                            "hp_p99_ratio": round(s_co["p99_us"] / sort_alone["p99_us"], 3), "hp_p50_ratio": round(s_co["p50_us"] / sort_alone["p50_us"], 3),
+                                            "sort_sorted": s_co["verified"], "triad_kept_pct": round(100 * t_co["rate"] / tri_alone["rate"], 2),
+                                            "triad_bit_exact": t_co["bit_exact"]}
+        except Exception as e:
+            out["config3_triad_vs_sort"] = {"error": str(e)[:300]}
+        return out
     finally:
         if srv is not None:
             srv.send_signal(signal.SIGTERM)
@@ -1166,6 +1179,16 @@ def main() -> None:
         "config4_llf": cfg4,
     }
     line.update(extra)
+    # Where the three stated targets stand in this run (HP P99 within 1.2 x of standalone; level-2 preemption latency
+    # under 50 us; LP keeps at least 90 % of its standalone throughput), for the configuration of the headline with a
+    # GPU context per process and, where that leg ran, with both processes under one MPS server.
+    mps = extra.get("two_processes_under_mps") or {}
+    line["target_status"] = {
+        "hp_p99_ratio": {"target": 1.2, "context_per_process": line["value"], "under_mps": mps.get("ratio"),
+                         "one_process": (extra.get("one_process_two_queues") or {}).get("ratio")},
+        "preempt_latency_p99_us": {"target": 50, "measured": line["preempt_latency_us"]},
+        "bg_throughput_kept_pct": {"target": 90, "measured": line["bg_throughput_kept_pct"], "under_mps": mps.get("bg_kept_pct")},
+    }
     print(json.dumps(line))
 
 

@@ -449,6 +449,45 @@ def test_gemm_stops_on_the_relayed_host_word_alone(pk, ok, form):
     flag.destroy()
 
 
+def test_triad_stops_on_the_relayed_host_word_alone(pk, ok):
+    """The stream kernels relay the early-warning word too (one thread in each of the grid's first CTAs): a plain
+    host store, with the device flag never written, stops a running triad, and the resumed task gives the bytes of a
+    straight run."""
+    import time
+    n = 1 << 30                                   # 12.9 GB of traffic: about 2 ms per pass
+    g = torch.Generator(device="cuda").manual_seed(5)
+    b = torch.rand(n, device="cuda", generator=g) * 2 - 1
+    c = torch.rand(n, device="cuda", generator=g) * 2 - 1
+    want = torch.empty(n, device="cuda")
+    t0 = pk.Task.triad(want, b, c, 1.25, flags=pk.FLAG_NON_PREEMPTIBLE)
+    _run_to_completion(t0, pk)
+    t0.destroy()
+    flag = pk.Flag()
+    word = flag.attach_relay()
+    a = torch.zeros(n, device="cuda")
+    t = pk.Task.triad(a, b, c, 1.25, flag=flag)
+    stopped = 0
+    for _ in range(4):
+        t.launch(_stream())
+        time.sleep(0.0003)
+        word.value = 1
+        info = t.wait()
+        torch.cuda.synchronize()
+        if info.status == pk.STATUS_PREEMPTED:
+            stopped += 1
+            assert info.tiles_done < info.tiles_total
+        word.value = 0
+        flag.set(0)
+        torch.cuda.synchronize()
+        if info.status == pk.STATUS_COMPLETED:
+            t.reset(_stream())
+    assert stopped >= 1, "the relay never stopped the kernel"
+    _run_to_completion(t, pk)
+    assert torch.equal(a.view(torch.int32), want.view(torch.int32))
+    t.destroy()
+    flag.destroy()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_task_calls_from_a_thread_on_another_device(pk):
     """Launch / reset / flag writes switch to the task's device for the call: a worker thread that never chose a

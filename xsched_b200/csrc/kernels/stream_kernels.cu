@@ -77,6 +77,8 @@ __device__ __forceinline__ void stream_tile(float *__restrict__ out, const float
     }
 }
 
+constexpr unsigned kRelayCtas = 8;
+
 template <int OP, bool kPreemptible>
 __global__ void __launch_bounds__(kStreamThreads, 6)
 stream_kernel(Ctl *ctl, float *__restrict__ out, const float *__restrict__ x,
@@ -85,8 +87,19 @@ stream_kernel(Ctl *ctl, float *__restrict__ out, const float *__restrict__ x,
     unsigned long long done = 0;
     note_start(ctl);
     __shared__ unsigned long long s_tile;
+    // Relay of the host's early flag (see pk_common.cuh): in the grid's first kRelayCtas CTAs one thread of the second
+    // warp looks at the host word while thread 0 claims the next tile, and raises the device flag itself.  The
+    // kernel then stops even when the stream-ordered write of the flag is held up behind it (seen under MPS, where
+    // a client's streams can share a hardware queue).  Eight CTAs with ~27 us tiles look every ~3 us between them.
+    const uint32_t *relay_src = nullptr;
+    if constexpr (kPreemptible) {
+        if (blockIdx.x < kRelayCtas && threadIdx.x == 32) relay_src = flag_relay_source(ctl->flag);
+    }
     while (true) {
         if (threadIdx.x == 0) s_tile = claim_tile<kPreemptible>(ctl);
+        if constexpr (kPreemptible) {
+            if (relay_src != nullptr && ld_host_word(relay_src) != 0u) atomicExch(const_cast<uint32_t *>(ctl->flag), 1u);
+        }
         __syncthreads();
         const unsigned long long tile = s_tile;
         if (tile == kNoTile) break;
