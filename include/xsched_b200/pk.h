@@ -103,7 +103,7 @@ xpkResult xpkFlagSet(uint32_t *flag_dev, uint32_t value, void *ctrl_stream);
 /* A stream write needs 6-14 us to reach device memory.  A flag (256 bytes from xpkFlagCreate, or any zeroed
  * 16-byte-aligned block whose first word is the flag) can be given an early-warning word in mapped host memory:
  * the caller stores a non-zero value there (a plain host store, on the GPU within about 2 us) immediately before
- * xpkFlagSet(flag, 1, ..), and zero before lowering the flag.  Kernels that run a relay (the GEMM) copy the raised
+ * xpkFlagSet(flag, 1, ..), and zero before lowering the flag.  Kernels that run a relay (the GEMM, the triad and the vector add) copy the raised
  * word into the flag; every kernel still honours the flag itself.  The word is freed with the flag's owner
  * calling xpkFlagDetachRelay.                                                                          */
 xpkResult xpkFlagAttachRelay(uint32_t *flag_dev, volatile uint32_t **relay_host);

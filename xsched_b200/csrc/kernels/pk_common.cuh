@@ -90,7 +90,7 @@ __device__ __forceinline__ void note_start(Ctl *ctl) {
 // A preempt flag is the first word of a 16-byte block.  Bytes [8,16) of the block may hold the device address of a
 // word in mapped host memory that the host sets (with a plain store, visible to the GPU within a couple of
 // microseconds) just before it enqueues the write of the flag itself (which takes 6-14 us to land): a kernel that
-// runs a relay (the GEMM: one spare thread of its first CTA) copies a raised host word into the flag, so that the
+// runs a relay (the GEMM: one spare thread of its first CTA; the stream kernels: one thread in each of their first CTAs) copies a raised host word into the flag, so that the
 // tile loops, which only ever poll device memory, see it early.  0 = no such word.
 __device__ __forceinline__ const uint32_t *flag_relay_source(const uint32_t *flag) {
     return reinterpret_cast<const uint32_t *>(*reinterpret_cast<const unsigned long long *>(flag + 2));
