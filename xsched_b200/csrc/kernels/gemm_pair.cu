@@ -261,8 +261,7 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
         if (a != 0u) asm volatile("fence.acq_rel.cluster;" ::: "memory");
         return a;
     };
-    const ClaimCtx cc = load_claim_ctx(ctl);          // frozen while a launch runs
-    unsigned long long tiles_done = 0;     // counted by the leader's warp 2 lane 0
+    unsigned long long tiles_done = 0;     // counted by the leader's first epilogue warp
 
     if (warp == 0) {
         if (lane == 0 && leader) {
@@ -271,6 +270,7 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
             const uint32_t peer_permit = in_cta(&sh->permit, 1);
             const uint32_t peer_abort_kseq = in_cta(&sh->abort_kseq, 1), peer_abort_tile_seq = in_cta(&sh->abort_tile_seq, 1);
             const uint32_t my_full = smem_u32(&sh->full[0]);
+            const ClaimCtx cc = load_claim_ctx(ctl);          // frozen while a launch runs
             // The flag as the watcher (warp kRelayWarp) last saw it: a shared-memory read instead of a round trip
             // to L2 in the middle of the load stream.  The twin never looks.
             auto flag_up = [&]() -> bool {
@@ -356,10 +356,11 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                     unsigned long long t0 = 0;
                     while (((word = ld_relaxed_u64(&sh->tile_word[slot])) >> 40) != want) {
                         __nanosleep(64);
-                        if ((++it & 0xFu) != 0) continue;
-                        const uint32_t a = aborted();
-                        if (a == 2u || (a == 1u && tseq > *(volatile unsigned long long *)&sh->abort_tile_seq)) { live = false; break; }
-                        if ((it & 0xFFu) == 0) {
+                        if (*(volatile uint32_t *)&sh->abort != 0u) {
+                            const uint32_t a = aborted();
+                            if (a == 2u || (a == 1u && tseq > *(volatile unsigned long long *)&sh->abort_tile_seq)) { live = false; break; }
+                        }
+                        if ((++it & 0xFFu) == 0) {
                             const unsigned long long now = global_ns();
                             if (t0 == 0) t0 = now;
                             else if (now - t0 > kWaitLimitNs) { raise_in_both(cx, kErrProducer); live = false; break; }
@@ -382,10 +383,11 @@ gemm_bf16_pair_kernel(Ctl *ctl, const __grid_constant__ CUtensorMap map_a, const
                         unsigned long long t0 = 0;
                         while (ld_relaxed_u64(&sh->permit) <= kseq) {
                             __nanosleep(200);                      // a permit comes every kAbortPollEvery k-blocks (about a microsecond and a half)
-                            if ((++it & 0xFu) != 0) continue;
-                            const uint32_t a = aborted();
-                            if (a == 2u || (a == 1u && kseq >= *(volatile unsigned long long *)&sh->abort_kseq)) { live = false; break; }
-                            if ((it & 0xFFu) == 0) {
+                            if (*(volatile uint32_t *)&sh->abort != 0u) {
+                                const uint32_t a = aborted();
+                                if (a == 2u || (a == 1u && kseq >= *(volatile unsigned long long *)&sh->abort_kseq)) { live = false; break; }
+                            }
+                            if ((++it & 0xFFu) == 0) {
                                 const unsigned long long now = global_ns();
                                 if (t0 == 0) t0 = now;
                                 else if (now - t0 > kWaitLimitNs) { raise_in_both(cx, kErrPermit); live = false; break; }
