@@ -919,11 +919,15 @@ def main() -> None:
         # The standalone run once more after the co-run: a box that was still settling during the first one (slow
         # first seconds have been seen) must not flatter the ratio, so the run with the lower P99 is the reference.
         mark("standalone once more")
-        hp_alone_2 = standalone_hp(device, env_alone, max(2000, requests), warm_requests)
-        launches += hp_alone_2["xpk_launches"]
-        standalone_runs = [{"p50_us": round(r["p50_us"], 2), "p99_us": round(r["p99_us"], 2)} for r in (hp_alone, hp_alone_2)]
-        if hp_alone_2["p99_us"] < hp_alone["p99_us"]:
-            hp_alone = hp_alone_2
+        standalone_runs = [{"p50_us": round(hp_alone["p50_us"], 2), "p99_us": round(hp_alone["p99_us"], 2)}]
+        try:
+            hp_alone_2 = standalone_hp(device, env_alone, max(2000, requests), warm_requests)
+            launches += hp_alone_2["xpk_launches"]
+            standalone_runs.append({"p50_us": round(hp_alone_2["p50_us"], 2), "p99_us": round(hp_alone_2["p99_us"], 2)})
+            if hp_alone_2["p99_us"] < hp_alone["p99_us"]:
+                hp_alone = hp_alone_2
+        except Exception as e:          # the first run stands
+            standalone_runs.append({"error": str(e)[:200]})
         if pg:
             pg.barrier()
 
