@@ -69,3 +69,22 @@ def test_wire_record_sizes_match_the_reference_structs():
     assert len(so.ev_hint_priority(1, 2, 3)) == 16 + 24 and len(so.ev_hint_laxity(1, 2, 3, 4, 5)) == 16 + 32
     # operation header: {u64 id, i32 type, i32 pid, u64 size, u64 running, u64 suspended} then handles
     assert struct.calcsize("<Qii QQQ") == 40
+
+
+def test_pk_header_and_python_face_agree():
+    """Every symbol and every enumerator of include/xsched_b200/pk.h that the ctypes face names has the header's value:
+    the flags (including the two that choose the GEMM's form), the status and result codes, the exported functions."""
+    import re
+    from xsched_b200 import pk
+    text = (ROOT / "include" / "xsched_b200" / "pk.h").read_text()
+    enums = {m.group(1): int(m.group(2), 0) for m in re.finditer(r"\b(XPK_[A-Z0-9_]+)\s*=\s*(0x[0-9a-fA-F]+|\d+)", text)}
+    want = {"XPK_FLAG_NONE": pk.FLAG_NONE, "XPK_FLAG_NON_PREEMPTIBLE": pk.FLAG_NON_PREEMPTIBLE, "XPK_FLAG_ABORT_INFLIGHT": pk.FLAG_ABORT_INFLIGHT,
+            "XPK_FLAG_GEMM_ONE_CTA": pk.FLAG_GEMM_ONE_CTA, "XPK_FLAG_GEMM_CTA_PAIR": pk.FLAG_GEMM_CTA_PAIR,
+            "XPK_KIND_TRIAD": pk.KIND_TRIAD, "XPK_KIND_VECADD": pk.KIND_VECADD, "XPK_KIND_SORT": pk.KIND_SORT, "XPK_KIND_GEMM": pk.KIND_GEMM}
+    for name, value in want.items():
+        assert enums.get(name) == value, (name, enums.get(name), value)
+    assert pk.FLAG_GEMM_ONE_CTA & pk.FLAG_GEMM_CTA_PAIR == 0
+    declared = set(re.findall(r"\b(xpk[A-Z][A-Za-z0-9]+)\s*\(", text))
+    assert declared == set(pk.EXPORTS), declared ^ set(pk.EXPORTS)
+    for sym in pk.EXPORTS:
+        assert hasattr(pk.lib, sym), sym
